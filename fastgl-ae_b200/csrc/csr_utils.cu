@@ -1,0 +1,118 @@
+// Block-CSR helpers: id histogram and exclusive scan (replace cal_deg_cuda and exclusive_sum_cuda,
+// utilis.cu:17-79).  The fused sampler emits the block CSR itself; these stay for callers that build
+// it from a COO edge list the way GraphConv.py:93-96 does.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace fgl {
+
+constexpr int kScanThreads = 512;
+constexpr int kScanItems = 8;  // ints per thread per tile
+
+__global__ void __launch_bounds__(256) cal_deg_kernel(const int32_t* __restrict__ ids, int64_t n_ids,
+                                                      int32_t* __restrict__ deg, int32_t n_nodes) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_ids; i += stride) {
+        const int32_t v = ids[i];
+        if (v >= 0 && v < n_nodes) atomicAdd(deg + v, 1);  // utilis.cu:55-57
+    }
+}
+
+// Two-level scan in one cooperative launch: per-CTA totals, team barrier, per-CTA rescan with its base.
+__global__ void __launch_bounds__(kScanThreads) exclusive_sum_kernel(const int32_t* __restrict__ in, int64_t n,
+                                                                     int32_t* __restrict__ out,
+                                                                     unsigned long long* bar, int32_t* partial,
+                                                                     int32_t* status) {
+    __shared__ int s_scan[40];
+    __shared__ int s_flag;
+    constexpr int kTile = kScanThreads * kScanItems;
+    const int64_t n_tiles = (n + kTile - 1) / kTile;
+    const int64_t tiles_per = (n_tiles + gridDim.x - 1) / gridDim.x;
+    const int64_t t0 = min((long long)n_tiles, (long long)blockIdx.x * (long long)tiles_per);
+    const int64_t t1 = min((long long)n_tiles, (long long)(t0 + tiles_per));
+    const int64_t lo = t0 * kTile, hi = min((long long)n, (long long)(t1 * kTile));
+
+    int acc = 0;
+    for (int64_t i = lo + threadIdx.x; i < hi; i += kScanThreads) acc += in[i];
+    const int total = block_sum(acc, s_scan);
+    if (threadIdx.x == 0) __stcg(partial + blockIdx.x, total);
+
+    Team t;
+    t.rank = blockIdx.x;
+    t.size = gridDim.x;
+    t.epoch = 0;
+    t.bar = bar;
+    t.status = status;
+    if (!team_barrier(t, &s_flag)) return;
+
+    int a = 0, b = 0;
+    for (int q = threadIdx.x; q < (int)gridDim.x; q += kScanThreads) {
+        const int x = __ldcg(partial + q);
+        b += x;
+        if (q < (int)blockIdx.x) a += x;
+    }
+    int running = block_sum(a, s_scan);
+    const int grand = block_sum(b, s_scan);
+    if (blockIdx.x == 0 && threadIdx.x == 0) out[n] = grand;
+
+    for (int64_t tile = lo; tile < hi; tile += kTile) {
+        // each thread owns kScanItems consecutive entries
+        const int64_t base = tile + (int64_t)threadIdx.x * kScanItems;
+        int v[kScanItems];
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) {
+            v[k] = (base + k < hi) ? in[base + k] : 0;
+            sum += v[k];
+        }
+        int tile_total;
+        int excl = running + block_excl_scan(sum, s_scan, tile_total);
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) {
+            if (base + k < hi) out[base + k] = excl;
+            excl += v[k];
+        }
+        running += tile_total;
+    }
+}
+
+}  // namespace fgl
+
+using namespace fgl;
+
+extern "C" {
+
+int fgl_cal_deg(const int32_t* ids, int64_t n_ids, int32_t* deg, int32_t n_nodes, void* stream) {
+    if (n_ids < 0 || n_nodes < 0 || (n_ids > 0 && !ids) || (n_nodes > 0 && !deg)) return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_nodes > 0 && cudaMemsetAsync(deg, 0, sizeof(int32_t) * (size_t)n_nodes, st) != cudaSuccess) return FGL_ERR_CUDA;
+    if (n_ids == 0 || n_nodes == 0) return FGL_OK;
+    const int grid = (int)std::min<int64_t>((n_ids + 255) / 256, 148 * 16);
+    cal_deg_kernel<<<grid, 256, 0, st>>>(ids, n_ids, deg, n_nodes);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream) {
+    if (!ws || n < 0 || (n > 0 && !in) || !out) return FGL_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(ws->mu);
+    DeviceGuard guard(ws->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    int per_sm = 0;
+    FGL_CUDA_OK(ws, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, exclusive_sum_kernel, kScanThreads, 0));
+    const int64_t tiles = (n + kScanThreads * kScanItems - 1) / (kScanThreads * kScanItems);
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)per_sm * ws->sm_count, tiles));
+    const int64_t need = 128 + (int64_t)grid * 4;
+    int rc = ws_ensure(ws, 0, need);
+    if (rc != FGL_OK) return rc;
+    unsigned long long* bar = (unsigned long long*)ws->scratch;
+    int32_t* partial = (int32_t*)(ws->scratch + 128);
+    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, 128, st));
+    int32_t* status = ws->status;
+    void* args[] = {(void*)&in, (void*)&n, (void*)&out, (void*)&bar, (void*)&partial, (void*)&status};
+    FGL_CUDA_OK(ws, cudaLaunchCooperativeKernel((const void*)exclusive_sum_kernel, dim3(grid), dim3(kScanThreads), args, 0, st));
+    return FGL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,466 @@
+"""``fastgl`` -- drop-in replacement of the reference's PyTorch extension of the same name.
+
+The reference binds 19 ops with pybind11 (cuda_operators/aggregate_acc.cpp:601-621); the ones its
+Python callers use (FusedMapSampler.py:76,98; GraphConv.py:26,37,93-96,109,132) are re-exposed here
+with the same names, positional arguments, dtypes, return lists and error behaviour:
+
+    sample_node, transfer_edge_id, cal_deg, exclusive_sum,
+    forward_gcn, backward_gcn, forwaed_gin (sic), backward_gin
+
+Each op allocates its outputs with torch and calls the C ABI of ``libfastgl_b200.so``
+(include/fastgl_b200.h) with raw device pointers and torch's current CUDA stream.  The dense weight
+products stay in torch (cuBLAS), as the reference keeps them in ``torch::mm``.  There is no CPU path:
+importing this module without the built library raises ImportError, and every op raises
+RuntimeError for a tensor that is not CUDA or not contiguous (aggregate_acc.cpp:4-6).
+
+Additive ops (not in the reference): ``sample_node_csr``, ``aggregate`` / ``aggregate_backward``
+(sum | mean | symnorm, optional row map into a feature table), ``sample_map_fused`` (all hops of many
+mini-batches in one persistent kernel), ``set_sampling`` / ``seed``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+from . import _capi
+from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRIVAL_ORDER,
+                    FLAG_SAMPLE_REPLACE, FLAG_ZERO_DEG_PASSTHROUGH, MAX_HOPS, FusedArgs, lib)
+
+__all__ = [
+    "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
+    "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward",
+    "sample_map_fused", "fused_capacity", "set_sampling", "seed", "FusedBatch",
+    "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
+]
+
+_state_lock = threading.Lock()
+_workspaces: dict[int, ctypes.c_void_p] = {}
+_config = {"replace": False, "arrival_order": False, "rng_seed": 12345, "rng_ctr": 0}
+
+
+# ------------------------------------------------------------------------------------------------
+# plumbing
+# ------------------------------------------------------------------------------------------------
+def _check_input(t: torch.Tensor, name: str) -> None:
+    # CHECK_INPUT of the reference: CUDA and contiguous (aggregate_acc.cpp:4-6)
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _check_i32(t: torch.Tensor, name: str) -> None:
+    _check_input(t, name)
+    if t.dtype != torch.int32:
+        raise RuntimeError(f"{name} must be int32 (got {t.dtype})")
+
+
+def _check_f32(t: torch.Tensor, name: str) -> None:
+    _check_input(t, name)
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32 (got {t.dtype})")
+
+
+def _ws(device: torch.device) -> ctypes.c_void_p:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with _state_lock:
+        ws = _workspaces.get(idx)
+        if ws is None:
+            ws = ctypes.c_void_p()
+            rc = lib().fgl_ws_create(ctypes.c_int(idx), ctypes.byref(ws))
+            if rc != 0:
+                raise RuntimeError(f"fgl_ws_create(device={idx}) failed: {_capi.status_str(rc)}")
+            _workspaces[idx] = ws
+    return ws
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None or t.numel() == 0 else t.data_ptr())
+
+
+def _raise(rc: int, what: str, ws=None) -> None:
+    if rc != 0:
+        detail = ""
+        if ws is not None:
+            msg = lib().fgl_last_error(ws)
+            detail = f" ({msg.decode()})" if msg else ""
+        raise RuntimeError(f"{what} failed: {_capi.status_str(rc)}{detail}")
+
+
+class _on_device:
+    """Make ``device`` current for a library call that launches without a workspace."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.ctx = None
+
+    def __enter__(self):
+        if self.device.index is not None and self.device.index != torch.cuda.current_device():
+            self.ctx = torch.cuda.device(self.device)
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+
+
+def set_sampling(replace: bool | None = None, arrival_order: bool | None = None) -> None:
+    """Choose the sampler's behaviour for the drop-in ops.
+
+    ``replace=True`` reproduces the reference kernel for hubs (independent picks, duplicates
+    possible, sample.cu:88-94); the default draws a uniform k-subset.  ``arrival_order=True`` numbers
+    new nodes in atomic arrival order (id_map.cu:317-320); the default is first-occurrence order.
+    """
+    if replace is not None:
+        _config["replace"] = bool(replace)
+    if arrival_order is not None:
+        _config["arrival_order"] = bool(arrival_order)
+
+
+def seed(rng_seed: int, rng_ctr: int = 0) -> None:
+    """Key of the sampler's Philox generator and the counter the next ``sample_node`` call uses."""
+    _config["rng_seed"] = int(rng_seed) & 0xFFFFFFFFFFFFFFFF
+    _config["rng_ctr"] = int(rng_ctr) & 0xFFFFFFFFFFFFFFFF
+
+
+def _next_ctr() -> int:
+    with _state_lock:
+        c = _config["rng_ctr"]
+        _config["rng_ctr"] = (c + 1) & 0xFFFFFFFFFFFFFFFF
+    return c
+
+
+# ------------------------------------------------------------------------------------------------
+# a1  sampling
+# ------------------------------------------------------------------------------------------------
+def sample_node_csr(src_edges, edge_ptr, seed_nodes, neighbor_num, replace=None, rng_seed=None, rng_ctr=None,
+                    want_dst=True):
+    """Sample and also return the block CSR offsets: (src_out, dst_out | None, block_indptr, n_edges)."""
+    _check_i32(src_edges, "src_edges")
+    _check_input(edge_ptr, "edge_ptr")
+    _check_i32(seed_nodes, "seed_nodes")
+    if edge_ptr.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("edge_ptr must be int32 or int64")
+    dev = seed_nodes.device
+    S = seed_nodes.numel()
+    fanout = int(neighbor_num)
+    out_src = torch.empty(max(1, S * fanout), dtype=torch.int32, device=dev)
+    out_dst = torch.empty(max(1, S * fanout), dtype=torch.int32, device=dev) if want_dst else None
+    out_ptr = torch.empty(S + 1, dtype=torch.int32, device=dev)
+    flags = FLAG_SAMPLE_REPLACE if (_config["replace"] if replace is None else replace) else 0
+    n_edges = ctypes.c_int64(0)
+    ws = _ws(dev)
+    rc = lib().fgl_sample(ws, _ptr(edge_ptr), ctypes.c_int(1 if edge_ptr.dtype == torch.int64 else 0), _ptr(src_edges),
+                          ctypes.c_int64(edge_ptr.numel() - 1), _ptr(seed_nodes), ctypes.c_int32(S),
+                          ctypes.c_int32(fanout), ctypes.c_int32(flags),
+                          ctypes.c_uint64(_config["rng_seed"] if rng_seed is None else rng_seed),
+                          ctypes.c_uint64(_next_ctr() if rng_ctr is None else rng_ctr), _ptr(out_ptr), _ptr(out_src),
+                          _ptr(out_dst), ctypes.byref(n_edges), _stream(dev))
+    _raise(rc, "sample_node", ws)
+    E = int(n_edges.value)
+    return out_src[:E], (out_dst[:E] if want_dst else None), out_ptr, E
+
+
+def sample_node(src_edges, dst_edges, edge_ptr, seed_nodes, dst_nodes, neighbor_num):
+    """aggregate_acc.cpp:491-512 -> sample_node_cuda (sample.cu:102-203).
+
+    Returns ``[src_out, dst_out, edges_num]``: the global source id and the global seed id of every
+    sampled edge, grouped by seed in seed order, and the edge count as an int32[1] CUDA tensor.
+    ``dst_edges`` is accepted and ignored, like the reference (sample.cu:43 never reads it).
+    """
+    _check_input(dst_edges, "dst_edges")
+    if int(dst_nodes) < seed_nodes.numel():
+        raise RuntimeError("dst_nodes must cover seed_nodes")
+    src_out, dst_out, _, E = sample_node_csr(src_edges, edge_ptr, seed_nodes, neighbor_num)
+    edges_num = torch.tensor([E], dtype=torch.int32, device=seed_nodes.device)
+    return [src_out, dst_out, edges_num]
+
+
+# ------------------------------------------------------------------------------------------------
+# a2  Fused-Map
+# ------------------------------------------------------------------------------------------------
+def transfer_edge_id(src_edges, dst_edges, dst_edges_unique, dst_nodes, total_items, unique_num, edge_nums):
+    """aggregate_acc.cpp:467-489 -> transfer_edge_id_cuda (id_map.cu:386-493).
+
+    Rewrites ``src_edges`` / ``dst_edges`` in place with block-local ids and returns
+    ``[src_edges, dst_edges, unique_nodes]`` where ``unique_nodes`` = the seeds followed by every new
+    source once (first-occurrence order unless ``set_sampling(arrival_order=True)``).
+    """
+    _check_i32(src_edges, "src_edges")
+    _check_i32(dst_edges, "dst_edges")
+    _check_i32(dst_edges_unique, "dst_edges_unique")
+    dev = src_edges.device
+    S = min(int(dst_nodes), dst_edges_unique.numel())
+    E = int(edge_nums)
+    if E > src_edges.numel() or E > dst_edges.numel():
+        raise RuntimeError("edge_nums exceeds the edge arrays")
+    cap = S + max(0, min(int(unique_num), E))
+    unique = torch.empty(max(1, cap), dtype=torch.int32, device=dev)
+    n_unique = ctypes.c_int64(0)
+    flags = FLAG_MAP_ARRIVAL_ORDER if _config["arrival_order"] else 0
+    ws = _ws(dev)
+    rc = lib().fgl_map(ws, _ptr(src_edges), _ptr(dst_edges), _ptr(dst_edges_unique), ctypes.c_int32(S),
+                       ctypes.c_int64(E), _ptr(unique), ctypes.c_int64(cap), ctypes.c_int32(flags),
+                       ctypes.byref(n_unique), _stream(dev))
+    _raise(rc, "transfer_edge_id", ws)
+    return [src_edges, dst_edges, unique[: int(n_unique.value)]]
+
+
+# ------------------------------------------------------------------------------------------------
+# a3  block-CSR helpers
+# ------------------------------------------------------------------------------------------------
+def cal_deg(edges, nodes_num):
+    """aggregate_acc.cpp:522-529 -> cal_deg_cuda (utilis.cu:60-79): histogram of an id array."""
+    _check_i32(edges, "edges")
+    dev = edges.device
+    deg = torch.empty(int(nodes_num), dtype=torch.int32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_cal_deg(_ptr(edges), ctypes.c_int64(edges.numel()), _ptr(deg), ctypes.c_int32(int(nodes_num)),
+                               _stream(dev))
+    _raise(rc, "cal_deg")
+    return deg
+
+
+def exclusive_sum(in_degs):
+    """aggregate_acc.cpp:514-520 -> exclusive_sum_cuda (utilis.cu:17-41): int32[n+1] offsets."""
+    _check_i32(in_degs, "in_degs")
+    dev = in_degs.device
+    out = torch.empty(in_degs.numel() + 1, dtype=torch.int32, device=dev)
+    ws = _ws(dev)
+    rc = lib().fgl_exclusive_sum(ws, _ptr(in_degs), ctypes.c_int64(in_degs.numel()), _ptr(out), _stream(dev))
+    _raise(rc, "exclusive_sum", ws)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# a4-a7  aggregation
+# ------------------------------------------------------------------------------------------------
+def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=None, dst_norm_degs=None,
+              zero_deg_passthrough=True, row_map=None, out=None):
+    """out[d] = sum over the row's edges of w * input_feat[row(src)], w by ``mode`` (AGG_SUM | AGG_MEAN |
+    AGG_SYMNORM); ``row_map`` (int32) turns block-local ids into rows of ``input_feat``."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    _check_f32(input_feat, "input_feat")
+    if input_feat.dim() != 2:
+        raise RuntimeError("input_feat must be 2-D")
+    for t, n in ((src_norm_degs, "src_norm_degs"), (dst_norm_degs, "dst_norm_degs"), (row_map, "row_map")):
+        if t is not None:
+            _check_i32(t, n)
+    n_dst = int(dst_nodes)
+    if edge_ptr.numel() < n_dst + 1:
+        raise RuntimeError("edge_ptr is shorter than dst_nodes + 1")
+    dev = input_feat.device
+    dim = input_feat.size(1)
+    if out is None:
+        out = torch.empty((n_dst, dim), dtype=torch.float32, device=dev)
+    else:
+        _check_f32(out, "out")
+    with _on_device(dev):
+        rc = lib().fgl_agg_fwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                               _ptr(dst_norm_degs), _ptr(row_map), _ptr(input_feat), ctypes.c_int64(input_feat.stride(0)),
+                               ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+                               ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH if zero_deg_passthrough else 0), _ptr(out),
+                               ctypes.c_int64(out.stride(0)), _stream(dev))
+    _raise(rc, "aggregate")
+    return out
+
+
+def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None):
+    """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim]."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    _check_f32(d_out, "d_input")
+    for t, n in ((src_norm_degs, "src_norm_degs"), (dst_norm_degs, "dst_norm_degs")):
+        if t is not None:
+            _check_i32(t, n)
+    dev = d_out.device
+    n_dst, dim = d_out.size(0), d_out.size(1)
+    d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_agg_bwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                               _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), ctypes.c_int32(dim),
+                               ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
+                               ctypes.c_int64(d_x.stride(0)), _stream(dev))
+    _raise(rc, "aggregate_backward")
+    return d_x
+
+
+def forward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, input_feat, weight, neighbor_num, dst_nodes):
+    """aggregate_acc.cpp:133-160 -> computation_aware_forward_gcn_cuda (aggregate_acc_kernel.cu:223-331).
+
+    ``tmp = input_feat @ weight`` then the sym-normalised neighbour sum; a row without in-edges returns
+    ``tmp[row]``.  ``neighbor_num`` only sized the reference's shared memory and is not needed here."""
+    _check_f32(weight, "weight")
+    _check_f32(input_feat, "input_feat")
+    tmp = torch.mm(input_feat, weight)
+    return [aggregate(AGG_SYMNORM, edge_ptr, src_edges, tmp, dst_nodes, src_norm_degs, dst_norm_degs)]
+
+
+def backward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, d_input, weight, input_feat):
+    """aggregate_acc.cpp:349-376 -> computation_aware_backward_gcn_cuda (aggregate_acc_kernel.cu:430-517).
+
+    The third argument is indexed by the destination row and the fourth by the edge's source -- the
+    reference kernel reads them that way (:490,:508) and GraphConv.py:37 passes the degree tensors in
+    that (swapped) order.  Returns ``[d_x, d_w]``."""
+    _check_f32(weight, "weight")
+    _check_f32(input_feat, "input_feat")
+    d_out = aggregate_backward(AGG_SYMNORM, edge_ptr, src_edges, d_input, input_feat.size(0),
+                               src_norm_degs=dst_norm_degs, dst_norm_degs=src_norm_degs)
+    return [torch.mm(d_out, weight.t()), torch.mm(input_feat.t(), d_out)]
+
+
+def forwaed_gin(edge_ptr, src_edges, input_feat, weight, neighbor_num, dst_nodes):
+    """aggregate_acc.cpp:173-199 -> computation_aware_forward_gin_cuda (aggregate_acc_kernel.cu:333-427).
+
+    The name keeps the reference's spelling.  Returns ``[tmp @ weight, tmp]`` with ``tmp`` the plain
+    neighbour sum (a row without in-edges copies its own input row)."""
+    _check_f32(weight, "weight")
+    tmp = aggregate(AGG_SUM, edge_ptr, src_edges, input_feat, dst_nodes)
+    return [torch.mm(tmp, weight), tmp]
+
+
+def backward_gin(edge_ptr, src_edges, d_input, weight, input_feat, src_nodes):
+    """aggregate_acc.cpp:387-409 -> computation_aware_backward_gin_cuda (aggregate_acc_kernel.cu:519-596).
+
+    ``input_feat`` is the aggregated ``tmp`` saved by the forward pass (GraphConv.py:117).  Returns
+    ``[d_x, d_w]``."""
+    _check_f32(weight, "weight")
+    _check_f32(input_feat, "input_feat")
+    _check_f32(d_input, "d_input")
+    d_tmp = torch.mm(d_input, weight.t())
+    d_w = torch.mm(input_feat.t(), d_input)
+    return [aggregate_backward(AGG_SUM, edge_ptr, src_edges, d_tmp, src_nodes), d_w]
+
+
+# ------------------------------------------------------------------------------------------------
+# fused multi-hop, multi-mini-batch sampling + mapping
+# ------------------------------------------------------------------------------------------------
+def fused_capacity(n_nodes: int, max_seeds: int, fanouts) -> list[int]:
+    """cap_nodes[h] for h = 0 .. len(fanouts) (``fanouts`` in sampling order)."""
+    L = len(fanouts)
+    fan = (ctypes.c_int32 * L)(*[int(f) for f in fanouts])
+    cap = (ctypes.c_int64 * (L + 1))()
+    rc = lib().fgl_fused_capacity(ctypes.c_int64(n_nodes), ctypes.c_int32(max_seeds), ctypes.c_int32(L), fan, cap)
+    _raise(rc, "fused_capacity")
+    return [int(c) for c in cap]
+
+
+class FusedBatch:
+    """Device-resident result of ``sample_map_fused`` for ``n_batches`` mini-batches.
+
+    ``counts[b, h]`` (h = 0 .. L) is the number of nodes after hop h (``counts[b, 0]`` = seeds),
+    ``counts[b, 8 + h]`` the number of edges of hop h.  Hop h's block has ``counts[b, h]`` destination
+    rows and ``counts[b, h + 1]`` source nodes; ``nodes[b, :counts[b, L]]`` are the global ids, seeds
+    first, and the first ``counts[b, h]`` of them are the hop's destinations."""
+
+    def __init__(self, fanouts, nodes, counts, block_indptr, block_src, arena):
+        self.fanouts = list(fanouts)
+        self.nodes = nodes
+        self.counts = counts
+        self.block_indptr = block_indptr
+        self.block_src = block_src
+        self._arena = arena
+        self._counts_host = None
+
+    @property
+    def n_batches(self) -> int:
+        return self.nodes.size(0)
+
+    def counts_host(self) -> torch.Tensor:
+        if self._counts_host is None:
+            self._counts_host = self.counts.cpu()
+        return self._counts_host
+
+    def blocks(self, b: int):
+        """Blocks of mini-batch ``b``, input layer first (the order FusedMapSampler.sample_blocks returns):
+        a list of (indptr[n_dst+1], src_local[E], n_src, n_dst)."""
+        c = self.counts_host()[b].tolist()
+        L = len(self.fanouts)
+        out = []
+        for h in reversed(range(L)):
+            n_dst, n_src, E = c[h], c[h + 1], c[8 + h]
+            out.append((self.block_indptr[h][b, : n_dst + 1], self.block_src[h][b, :E], n_src, n_dst))
+        return out
+
+    def input_nodes(self, b: int) -> torch.Tensor:
+        return self.nodes[b, : int(self.counts_host()[b, len(self.fanouts)])]
+
+
+def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=None, arrival_order=None,
+                     rng_seed=None, rng_ctr=None, n_teams=0, out: FusedBatch | None = None) -> FusedBatch:
+    """All hops of ``seeds.size(0)`` mini-batches in one persistent kernel launch.
+
+    ``seeds`` int32[n_batches, seed_stride], ``seed_counts`` int32[n_batches]; ``fanouts`` in sampling
+    order (the reference walks ``reversed(self.fanouts)``, FusedMapSampler.py:72).  Nothing is copied to
+    the host; pass ``out`` (a previous result of the same geometry) to reuse its buffers."""
+    _check_i32(src_edges, "src_edges")
+    _check_input(edge_ptr, "edge_ptr")
+    _check_i32(seeds, "seeds")
+    _check_i32(seed_counts, "seed_counts")
+    if seeds.dim() != 2 or seed_counts.numel() != seeds.size(0):
+        raise RuntimeError("seeds must be [n_batches, seed_stride] with one count per batch")
+    if edge_ptr.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("edge_ptr must be int32 or int64")
+    L = len(fanouts)
+    if not 1 <= L <= MAX_HOPS:
+        raise RuntimeError(f"1..{MAX_HOPS} hops supported")
+    dev = seeds.device
+    nb, stride = seeds.size(0), seeds.size(1)
+    n_nodes = edge_ptr.numel() - 1
+    cap = fused_capacity(n_nodes, stride, fanouts)
+    if out is None:
+        sizes = [cap[L], COUNTS_STRIDE] + [cap[h] + 1 for h in range(L)] + [cap[h] * int(fanouts[h]) for h in range(L)]
+        sizes = [(s + 31) // 32 * 32 for s in sizes]  # 128-byte aligned rows
+        arena = torch.empty(nb * sum(sizes), dtype=torch.int32, device=dev)
+        views, off = [], 0
+        for s in sizes:
+            views.append(arena[off: off + nb * s].view(nb, s))
+            off += nb * s
+        out = FusedBatch(fanouts, views[0], views[1], views[2: 2 + L], views[2 + L: 2 + 2 * L], arena)
+    out._counts_host = None
+    a = FusedArgs()
+    a.indptr = edge_ptr.data_ptr()
+    a.indices = src_edges.data_ptr()
+    a.n_nodes = n_nodes
+    a.indptr_is_64 = 1 if edge_ptr.dtype == torch.int64 else 0
+    a.n_batches = nb
+    a.n_hops = L
+    for h in range(L):
+        a.fanout[h] = int(fanouts[h])
+        a.block_indptr[h] = out.block_indptr[h].data_ptr()
+        a.block_indptr_stride[h] = out.block_indptr[h].stride(0)
+        a.block_src[h] = out.block_src[h].data_ptr()
+        a.block_src_stride[h] = out.block_src[h].stride(0)
+    use_replace = _config["replace"] if replace is None else replace
+    use_arrival = _config["arrival_order"] if arrival_order is None else arrival_order
+    a.flags = (FLAG_SAMPLE_REPLACE if use_replace else 0) | (FLAG_MAP_ARRIVAL_ORDER if use_arrival else 0)
+    a.n_teams = int(n_teams)
+    a.rng_seed = _config["rng_seed"] if rng_seed is None else rng_seed
+    a.rng_ctr = _next_ctr() if rng_ctr is None else rng_ctr
+    a.seeds = seeds.data_ptr()
+    a.seed_stride = seeds.stride(0)
+    a.seed_counts = seed_counts.data_ptr()
+    a.nodes = out.nodes.data_ptr()
+    a.nodes_stride = out.nodes.stride(0)
+    a.counts = out.counts.data_ptr()
+    ws = _ws(dev)
+    rc = lib().fgl_sample_map_fused(ws, ctypes.byref(a), _stream(dev))
+    _raise(rc, "sample_map_fused", ws)
+    return out
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel of this device's workspace recorded an error."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _ws(dev)
+    _raise(lib().fgl_ws_check(ws, _stream(dev)), "device status", ws)

@@ -1,0 +1,160 @@
+/*
+ * fastgl_b200 -- C ABI of the B200 (sm_100a) implementation of FastGL's per-mini-batch hot path:
+ * CSR neighbour sampling, the Fused-Map id mapping, block-CSR helpers and sum / mean / sym-norm
+ * aggregation (forward and backward).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (a cudaStream_t passed as
+ * void*; NULL = the legacy default stream) and returns an int status (FGL_OK = 0).  Nothing here
+ * includes or names a PyTorch type.  All index arrays are int32 unless stated; feature matrices are
+ * fp32, row-major, with an explicit leading dimension in elements.  Unless a function says otherwise
+ * it only enqueues work on the stream and returns without synchronising.
+ *
+ * Each declaration cites the interface of the reference (cuda_operators/..., file:line) that it
+ * replaces.  The dense weight products that the reference performs inside its ops (torch::mm) are
+ * not part of this library; the host language keeps them (cuBLAS through PyTorch).
+ */
+#ifndef FASTGL_B200_H_
+#define FASTGL_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FGL_ABI_VERSION 1
+
+/* status codes */
+#define FGL_OK 0
+#define FGL_ERR_INVALID 1  /* bad argument (null pointer, negative size, unsupported fanout ...) */
+#define FGL_ERR_CUDA 2     /* a CUDA runtime call failed; see fgl_last_error() */
+#define FGL_ERR_NOMEM 3    /* workspace allocation failed */
+#define FGL_ERR_CAPACITY 4 /* an output buffer or the hashtable is too small for the result */
+#define FGL_ERR_PROBE 5    /* hashtable probe limit reached (table full or corrupted) */
+#define FGL_ERR_BOUNDS 6   /* a node id outside [0, n_nodes) was met on the device */
+#define FGL_ERR_TIMEOUT 7  /* a bounded device-side wait gave up */
+
+/* flags of fgl_sample / fgl_sample_map_fused */
+#define FGL_SAMPLE_REPLACE 1   /* hubs (deg > fanout): independent picks, duplicates possible (reference) */
+/* flags of fgl_map / fgl_sample_map_fused */
+#define FGL_MAP_ARRIVAL_ORDER 2 /* new ids in atomic arrival order (reference) instead of first occurrence */
+/* flags of fgl_agg_fwd */
+#define FGL_AGG_ZERO_DEG_PASSTHROUGH 1 /* a row without in-edges copies its own input row (reference) */
+
+/* aggregation modes */
+#define FGL_AGG_SUM 0     /* out[d] = sum_s x[s]                                  (GIN,  K10/K11) */
+#define FGL_AGG_MEAN 1    /* out[d] = sum_s x[s] / deg_in(d)                      (GraphSAGE-mean) */
+#define FGL_AGG_SYMNORM 2 /* out[d] = sum_s x[s] * rsqrt(dst_deg[d]) * rsqrt(src_deg[s]) (GCN, K8/K9) */
+
+#define FGL_MAX_HOPS 7
+#define FGL_COUNTS_STRIDE 16 /* per mini-batch: [0..7] node counts n_0..n_L, [8..15] edge counts per hop */
+#define FGL_MAX_FANOUT 512
+
+typedef struct fgl_ws fgl_ws; /* per-device workspace: hashtable, scan scratch, status words */
+
+int fgl_abi_version(void);
+int fgl_sizeof_fused_args(void); /* sizeof(struct fgl_fused_args), for bindings to check their layout */
+const char* fgl_status_str(int status);
+
+/* Workspace.  Replaces the per-call cudaMalloc / cudaFree of scratch in the reference
+ * (sample.cu:118,151,157,161-162,197; id_map.cu:45-58; utilis.cu:33,38).  Buffers grow on demand
+ * (never inside a stream capture: size the workspace with fgl_ws_reserve first) and are freed by
+ * fgl_ws_destroy.  A workspace belongs to one device and may be used from any host thread, one call
+ * at a time (calls lock it). */
+int fgl_ws_create(int device, fgl_ws** ws);
+int fgl_ws_destroy(fgl_ws* ws);
+int fgl_ws_reserve(fgl_ws* ws, int64_t table_slots, int64_t scratch_bytes);
+const char* fgl_last_error(fgl_ws* ws);
+/* Reads back (synchronising the stream) and clears the device status word set by the kernels of this
+ * workspace: FGL_OK or the first FGL_ERR_* a kernel recorded. */
+int fgl_ws_check(fgl_ws* ws, void* stream);
+
+/* Neighbour sampling; replaces sample_node_cuda (sample.cu:102-203; binding aggregate_acc.cpp:491-512).
+ * indptr has n_nodes + 1 entries of int32 (indptr_is_64 = 0, as the reference) or int64.  For seed i
+ * the k_i = min(deg, fanout) sampled sources land at out_src[out_indptr[i] .. out_indptr[i+1]); a seed
+ * with deg <= fanout gets its whole list in CSR order.  out_src needs n_seeds * fanout entries.
+ * out_dst (may be NULL) receives the seed's global id per edge, out_indptr (may be NULL only if the
+ * caller does not need the block CSR) the n_seeds + 1 offsets.  Random picks come from Philox4x32-10
+ * with key = rng_seed and counter = (pick slot, seed position, rng_ctr): the same arguments give the
+ * same edges.  If n_edges_host is not NULL the call synchronises the stream, stores the edge count
+ * there and returns the device status. */
+int fgl_sample(fgl_ws* ws, const void* indptr, int indptr_is_64, const int32_t* indices, int64_t n_nodes,
+               const int32_t* seeds, int32_t n_seeds, int32_t fanout, int32_t flags, uint64_t rng_seed,
+               uint64_t rng_ctr, int32_t* out_indptr, int32_t* out_src, int32_t* out_dst,
+               int64_t* n_edges_host, void* stream);
+
+/* Fused-Map id mapping; replaces transfer_edge_id_cuda (id_map.cu:386-493; binding
+ * aggregate_acc.cpp:467-489).  src (and dst, if not NULL) hold global ids on entry and block-local ids
+ * on return (in place, like the reference).  unique receives the n_seeds seeds followed by every
+ * source that is not a seed, each once: in first-occurrence order of src, or with
+ * FGL_MAP_ARRIVAL_ORDER in whatever order the inserting threads arrive (the reference's behaviour).
+ * unique_cap is the capacity of unique in entries.  If n_unique_host is not NULL the call
+ * synchronises, stores the total number of unique nodes and returns the device status. */
+int fgl_map(fgl_ws* ws, int32_t* src, int32_t* dst, const int32_t* seeds, int32_t n_seeds, int64_t n_edges,
+            int32_t* unique, int64_t unique_cap, int32_t flags, int64_t* n_unique_host, void* stream);
+
+/* Multi-hop, multi-mini-batch sampling + mapping in one persistent kernel; replaces the per-hop loop
+ * sample_node -> transfer_edge_id of FusedMapSampler.sample_blocks (FusedMapSampler.py:72-109) for
+ * n_batches independent mini-batches at once.  All pointers are device pointers. */
+typedef struct fgl_fused_args {
+    const void* indptr;         /* n_nodes + 1 entries */
+    const int32_t* indices;
+    int64_t n_nodes;
+    int32_t indptr_is_64;
+    int32_t n_batches;
+    int32_t n_hops;                /* 1 .. FGL_MAX_HOPS */
+    int32_t fanout[FGL_MAX_HOPS];  /* in sampling order: fanout[0] is applied to the seeds */
+    int32_t flags;                 /* FGL_SAMPLE_REPLACE | FGL_MAP_ARRIVAL_ORDER */
+    int32_t n_teams;               /* mini-batches in flight at once (0 = library default) */
+    uint64_t rng_seed;
+    uint64_t rng_ctr;              /* mini-batch b, hop h draws with counter rng_ctr + b * 8 + h */
+    const int32_t* seeds;          /* [n_batches][seed_stride] */
+    int64_t seed_stride;
+    const int32_t* seed_counts;    /* int32[n_batches], each <= seed_stride */
+    int32_t* nodes;                /* out [n_batches][nodes_stride]: unique global ids, seeds first; the
+                                      first counts[b][h] entries are the destination nodes of hop h */
+    int64_t nodes_stride;
+    int32_t* counts;               /* out [n_batches][FGL_COUNTS_STRIDE] */
+    int32_t* block_indptr[FGL_MAX_HOPS];     /* out, hop h: [n_batches][block_indptr_stride[h]] */
+    int64_t block_indptr_stride[FGL_MAX_HOPS];
+    int32_t* block_src[FGL_MAX_HOPS];        /* out, hop h: [n_batches][block_src_stride[h]] local ids */
+    int64_t block_src_stride[FGL_MAX_HOPS];
+} fgl_fused_args;
+
+/* Capacities a caller must allocate: cap_nodes[h] bounds counts[b][h] (h = 0 .. n_hops), the hop-h
+ * block needs cap_nodes[h] + 1 indptr entries and cap_nodes[h] * fanout[h] source entries. */
+int fgl_fused_capacity(int64_t n_nodes, int32_t max_seeds, int32_t n_hops, const int32_t* fanout,
+                       int64_t* cap_nodes /* n_hops + 1 */);
+int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* args, void* stream);
+
+/* Histogram of an id array; replaces cal_deg_cuda (utilis.cu:60-79; binding aggregate_acc.cpp:522-529).
+ * deg[0 .. n_nodes) is zeroed and then counts the occurrences of each id. */
+int fgl_cal_deg(const int32_t* ids, int64_t n_ids, int32_t* deg, int32_t n_nodes, void* stream);
+
+/* Exclusive scan with the total appended; replaces exclusive_sum_cuda (utilis.cu:17-41; binding
+ * aggregate_acc.cpp:514-520).  out has n + 1 entries. */
+int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream);
+
+/* Aggregation forward; replaces the gather kernels K8 / K10 of the reference
+ * (computation_aware_forward_gcn_cuda_kernel aggregate_acc_kernel.cu:271-331 and
+ * computation_aware_forward_gin_cuda_kernel :376-427).  out[d, 0..dim) = sum over e in
+ * [indptr[d], indptr[d+1]) of w * x[row(src[e]), 0..dim), with w by mode and row(i) = row_map[i] if
+ * row_map is not NULL (aggregation straight from a feature table by global id) else i.  src_deg /
+ * dst_deg are only read in FGL_AGG_SYMNORM. */
+int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                const int32_t* dst_deg, const int32_t* row_map, const float* x, int64_t ldx, int32_t dim,
+                int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream);
+
+/* Aggregation backward; replaces the scatter kernels K9 / K11
+ * (computation_aware_backward_gcn_cuda_kernel aggregate_acc_kernel.cu:468-517 and
+ * computation_aware_backward_gin_cuda_kernel :555-596).  dx[0 .. n_src) is zeroed, then
+ * dx[src[e], :] += w * dy[d, :] for every edge e of row d.  Rows without in-edges contribute nothing
+ * (as the reference, :498-500, :580-582). */
+int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                const int32_t* dst_deg, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst,
+                int32_t n_src, float* dx, int64_t ldx, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTGL_B200_H_ */

@@ -1,0 +1,78 @@
+"""CPU checks of the drop-in boundary: the C-ABI library loads without a GPU, exports every symbol the
+header declares, and the Python ops reject what the reference's CHECK_INPUT rejects."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fastgl_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fgl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from fastgl import _capi
+    handle = ctypes.CDLL(_capi.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(handle, name), name
+    assert sorted(_capi.EXPORTS) == names
+
+
+def test_abi_version_struct_layout_and_status_strings():
+    from fastgl import _capi
+    lib = _capi.lib()
+    assert lib.fgl_abi_version() == _capi.ABI_VERSION
+    assert lib.fgl_sizeof_fused_args() == ctypes.sizeof(_capi.FusedArgs)
+    assert _capi.status_str(0) == "ok"
+    assert "probe" in _capi.status_str(5)
+
+
+def test_capacity_helper_matches_the_hop_sizes():
+    import fastgl
+    # batch 1024, hops 5 / 10 / 15: 1024 -> 6144 -> 67584 -> 1081344 nodes at most
+    assert fastgl.fused_capacity(2_450_000, 1024, [5, 10, 15]) == [1024, 6144, 67584, 1081344]
+    # the node count caps the frontier
+    assert fastgl.fused_capacity(50_000, 1024, [5, 10, 15]) == [1024, 6144, 50000, 50000]
+    with pytest.raises(RuntimeError):
+        fastgl.fused_capacity(1000, 10, [0])
+
+
+def test_invalid_arguments_return_status_without_touching_a_device():
+    from fastgl import _capi
+    lib = _capi.lib()
+    assert lib.fgl_sample(None, None, 0, None, ctypes.c_int64(0), None, 0, 0, 0, ctypes.c_uint64(0), ctypes.c_uint64(0),
+                          None, None, None, None, None) == 1
+    assert lib.fgl_agg_fwd(9, None, None, None, None, None, None, ctypes.c_int64(4), 4, 1, 0, None, ctypes.c_int64(4),
+                           None) == 1
+    assert lib.fgl_ws_destroy(None) == 0
+
+
+def test_ops_reject_cpu_and_non_contiguous_tensors():
+    import fastgl
+    idx = torch.zeros(4, dtype=torch.int32)
+    feat = torch.zeros((4, 4))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fastgl.cal_deg(idx, 4)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fastgl.sample_node(idx, idx, idx, idx, 4, 2)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fastgl.transfer_edge_id(idx, idx, idx, 4, 8, 4, 4)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fastgl.forwaed_gin(idx, idx, feat, feat, 2, 4)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fastgl.forward_gcn(idx, idx, idx, idx, feat, feat, 2, 4)
+
+
+def test_reference_op_names_are_exposed():
+    import fastgl
+    for name in ("sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
+                 "forwaed_gin", "backward_gin"):
+        assert callable(getattr(fastgl, name))
