@@ -420,7 +420,8 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
     cap = fused_capacity(n_nodes, stride, fanouts)
     if out is None:
         sizes = [cap[L], COUNTS_STRIDE] + [cap[h] + 1 for h in range(L)] + [cap[h] * int(fanouts[h]) for h in range(L)]
-        sizes = [(s + 31) // 32 * 32 for s in sizes]  # 128-byte aligned rows
+        # 128-byte aligned rows, except the counts rows whose stride the ABI fixes
+        sizes = [s if i == 1 else (s + 31) // 32 * 32 for i, s in enumerate(sizes)]
         arena = torch.empty(nb * sum(sizes), dtype=torch.int32, device=dev)
         views, off = [], 0
         for s in sizes:

@@ -1,0 +1,389 @@
+"""GPU parity tests: the CUDA path, called through the ``fastgl`` ops (ctypes -> C ABI), against the CPU
+oracle on the same seeded inputs.  Integer results are compared bit for bit; fp32 aggregation within
+1e-5 relative to the largest reference magnitude (the tolerance stated for the path)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_graph
+from oracle import oracle_c as oc
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "hotpath_small.npz")
+AGG_RTOL = 1e-5
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def to_dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(dev())
+
+
+def rel_err(got, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(np.asarray(got, dtype=np.float64) - ref).max() / max(1e-30, np.abs(ref).max()))
+
+
+@pytest.fixture(scope="module")
+def fastgl():
+    import fastgl as mod
+    assert torch.cuda.is_available()
+    return mod
+
+
+@pytest.fixture(scope="module")
+def graph():
+    indptr, indices = make_graph(20000, 16, seed=21, hub=3000)
+    return indptr, indices
+
+
+# ----------------------------------------------------------------------------------------------
+# a3
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n_ids,n_nodes", [(0, 5), (1, 1), (1000, 37), (300000, 70000), (5_000_000, 1_000_000)])
+def test_cal_deg_and_exclusive_sum(fastgl, n_ids, n_nodes):
+    rng = np.random.default_rng(n_ids + 1)
+    ids = rng.integers(0, n_nodes, size=n_ids).astype(np.int32)
+    deg = fastgl.cal_deg(to_dev(ids), n_nodes)
+    ref = oc.cal_deg(ids, n_nodes)
+    assert np.array_equal(deg.cpu().numpy(), ref)
+    ptr = fastgl.exclusive_sum(deg)
+    assert np.array_equal(ptr.cpu().numpy(), oc.exclusive_sum(ref))
+
+
+def test_exclusive_sum_empty(fastgl):
+    out = fastgl.exclusive_sum(torch.zeros(0, dtype=torch.int32, device=dev()))
+    assert out.cpu().tolist() == [0]
+
+
+# ----------------------------------------------------------------------------------------------
+# a1
+# ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("ptr_dtype", [torch.int32, torch.int64])
+@pytest.mark.parametrize("replace", [False, True])
+@pytest.mark.parametrize("fanout", [1, 5, 10, 15, 25, 32, 33, 100])
+def test_sample_matches_oracle(fastgl, graph, ptr_dtype, replace, fanout):
+    indptr, indices = graph
+    rng = np.random.default_rng(fanout)
+    seeds = rng.choice(len(indptr) - 1, size=3000, replace=False).astype(np.int32)
+    seeds[0] = 0  # the hub
+    src, dst, ptr, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr, ptr_dtype), to_dev(seeds), fanout,
+                                              replace=replace, rng_seed=4242, rng_ctr=fanout)
+    rptr, rsrc, rdst = oc.sample(indptr, indices, seeds, fanout, replace, rng_seed=4242, rng_ctr=fanout)
+    assert E == len(rsrc)
+    assert np.array_equal(ptr.cpu().numpy(), rptr)
+    assert np.array_equal(src.cpu().numpy(), rsrc)
+    assert np.array_equal(dst.cpu().numpy(), rdst)
+
+
+def test_sample_node_drop_in_signature(fastgl, graph):
+    indptr, indices = graph
+    seeds = np.arange(100, 612, dtype=np.int32)
+    fastgl.seed(12345, 7)
+    fastgl.set_sampling(replace=False)
+    d_idx = to_dev(indices)
+    out = fastgl.sample_node(d_idx, d_idx, to_dev(indptr, torch.int32), to_dev(seeds), len(seeds), 10)
+    assert len(out) == 3 and out[2].dtype == torch.int32 and out[2].numel() == 1
+    rptr, rsrc, rdst = oc.sample(indptr, indices, seeds, 10, False, rng_seed=12345, rng_ctr=7)
+    assert int(out[2].item()) == len(rsrc) == out[0].numel() == out[1].numel()
+    assert np.array_equal(out[0].cpu().numpy(), rsrc) and np.array_equal(out[1].cpu().numpy(), rdst)
+
+
+def test_full_neighbourhood_mode_is_the_csr_itself(fastgl, graph):
+    indptr, indices = graph
+    deg = np.diff(indptr)
+    fan = 100
+    seeds = np.nonzero(deg <= fan)[0].astype(np.int32)  # fanout >= degree for every seed
+    assert len(seeds) > 15000
+    src, _, ptr, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(seeds), fan, want_dst=False)
+    ref = np.concatenate([indices[indptr[s]:indptr[s + 1]] for s in seeds])
+    assert np.array_equal(np.diff(ptr.cpu().numpy()), deg[seeds])
+    assert np.array_equal(src.cpu().numpy(), ref)
+
+
+def test_sample_empty_and_isolated_seeds(fastgl):
+    indptr = np.array([0, 0, 2, 2], dtype=np.int64)
+    indices = np.array([0, 2], dtype=np.int32)
+    src, dst, ptr, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(np.array([0, 2, 1, 0], dtype=np.int32)), 4)
+    assert E == 2 and ptr.cpu().tolist() == [0, 0, 0, 2, 2]
+    assert src.cpu().tolist() == [0, 2] and dst.cpu().tolist() == [1, 1]
+    src, dst, ptr, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), torch.zeros(0, dtype=torch.int32, device=dev()), 4)
+    assert E == 0 and ptr.cpu().tolist() == [0]
+
+
+def test_selection_frequency_chi_square_on_gpu(fastgl):
+    deg, fanout, trials = 40, 8, 6000
+    indptr = np.array([0, deg] + [deg] * deg, dtype=np.int64)
+    indices = np.arange(1, deg + 1, dtype=np.int32)
+    seeds = np.zeros(trials, dtype=np.int32)
+    for replace in (False, True):
+        src, _, _, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(seeds), fanout, replace=replace,
+                                              rng_seed=777, rng_ctr=1, want_dst=False)
+        src = src.cpu().numpy()
+        assert E == trials * fanout
+        counts = np.bincount(src, minlength=deg + 1)[1:]
+        expected = trials * fanout / deg
+        assert float(((counts - expected) ** 2 / expected).sum()) < 72.1  # chi-square(39), p = 0.001
+        if not replace:
+            per_seed = src.reshape(trials, fanout)
+            assert all(len(set(r.tolist())) == fanout for r in per_seed[:500])
+
+
+def test_out_of_range_seed_is_reported(fastgl, graph):
+    indptr, indices = graph
+    seeds = np.array([1, 2, len(indptr) + 5], dtype=np.int32)
+    with pytest.raises(RuntimeError, match="out of range"):
+        fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(seeds), 5)
+    # the workspace stays usable
+    src, _, _, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(seeds[:2]), 5)
+    assert E == src.numel()
+
+
+# ----------------------------------------------------------------------------------------------
+# a2
+# ----------------------------------------------------------------------------------------------
+def check_map_invariants(src_g, dst_g, seeds, src_l, dst_l, uniq):
+    S = len(seeds)
+    assert np.array_equal(uniq[:S], seeds)                                   # (i)
+    pos = {int(v): i for i, v in enumerate(seeds)}
+    assert np.array_equal(dst_l, np.array([pos[int(v)] for v in dst_g], dtype=np.int32))  # (ii)
+    assert np.array_equal(uniq[src_l], src_g)                                # (iv)
+    new = uniq[S:]
+    assert len(set(new.tolist())) == len(new) and not (set(new.tolist()) & set(seeds.tolist()))  # (v)
+    assert set(new.tolist()) == set(src_g.tolist()) - set(seeds.tolist())
+
+
+@pytest.mark.parametrize("n_seeds,fanout", [(1, 3), (64, 5), (1024, 5), (6000, 10), (60000, 15)])
+def test_map_matches_oracle_first_occurrence_order(fastgl, n_seeds, fanout):
+    indptr, indices = make_graph(max(4000, n_seeds * 3), 14, seed=n_seeds, hub=500)
+    rng = np.random.default_rng(n_seeds)
+    seeds = rng.choice(len(indptr) - 1, size=n_seeds, replace=False).astype(np.int32)
+    _, src_g, dst_g = oc.sample(indptr, indices, seeds, fanout, False, rng_seed=3, rng_ctr=1)
+    rs, rd, ru = oc.map_edges(src_g, dst_g, seeds)
+    fastgl.set_sampling(arrival_order=False)
+    d_src, d_dst = to_dev(src_g), to_dev(dst_g)
+    out = fastgl.transfer_edge_id(d_src, d_dst, to_dev(seeds), n_seeds, n_seeds + len(src_g),
+                                  min(len(indptr) - 1, fanout * n_seeds), len(src_g))
+    assert out[0].data_ptr() == d_src.data_ptr() and out[1].data_ptr() == d_dst.data_ptr()  # in place
+    assert np.array_equal(out[2].cpu().numpy(), ru)       # (vi) element for element
+    assert np.array_equal(out[0].cpu().numpy(), rs)
+    assert np.array_equal(out[1].cpu().numpy(), rd)
+
+
+@pytest.mark.parametrize("n_seeds,fanout", [(64, 5), (6000, 10)])
+def test_map_arrival_order_keeps_the_invariants(fastgl, n_seeds, fanout):
+    indptr, indices = make_graph(20000, 14, seed=5, hub=500)
+    rng = np.random.default_rng(1)
+    seeds = rng.choice(len(indptr) - 1, size=n_seeds, replace=False).astype(np.int32)
+    _, src_g, dst_g = oc.sample(indptr, indices, seeds, fanout, False, rng_seed=3, rng_ctr=1)
+    _, _, ru = oc.map_edges(src_g, dst_g, seeds)
+    fastgl.set_sampling(arrival_order=True)
+    try:
+        out = fastgl.transfer_edge_id(to_dev(src_g), to_dev(dst_g), to_dev(seeds), n_seeds, n_seeds + len(src_g),
+                                      fanout * n_seeds, len(src_g))
+    finally:
+        fastgl.set_sampling(arrival_order=False)
+    uniq = out[2].cpu().numpy()
+    assert len(uniq) == len(ru)
+    check_map_invariants(src_g, dst_g, seeds, out[0].cpu().numpy(), out[1].cpu().numpy(), uniq)
+
+
+def test_map_without_edges_and_with_repeated_sources(fastgl):
+    seeds = np.array([5, 9], dtype=np.int32)
+    e = torch.zeros(0, dtype=torch.int32, device=dev())
+    out = fastgl.transfer_edge_id(e, e.clone(), to_dev(seeds), 2, 2, 10, 0)
+    assert out[2].cpu().tolist() == [5, 9] and out[0].numel() == 0
+    src = np.array([7, 7, 7, 5, 7, 11, 11], dtype=np.int32)
+    dst = np.array([5, 5, 9, 9, 9, 9, 5], dtype=np.int32)
+    out = fastgl.transfer_edge_id(to_dev(src), to_dev(dst), to_dev(seeds), 2, 9, 7, 7)
+    assert out[2].cpu().tolist() == [5, 9, 7, 11]
+    assert out[0].cpu().tolist() == [2, 2, 2, 0, 2, 3, 3] and out[1].cpu().tolist() == [0, 0, 1, 1, 1, 1, 0]
+
+
+# ----------------------------------------------------------------------------------------------
+# fused multi-hop, multi-mini-batch
+# ----------------------------------------------------------------------------------------------
+def run_fused_and_compare(fastgl, indptr, indices, seed_lists, fanouts_sampling, replace, n_teams, ptr_dtype=torch.int64):
+    nb = len(seed_lists)
+    stride = max(len(s) for s in seed_lists)
+    seeds = np.zeros((nb, stride), dtype=np.int32)
+    counts = np.zeros(nb, dtype=np.int32)
+    for b, s in enumerate(seed_lists):
+        seeds[b, :len(s)] = s
+        counts[b] = len(s)
+    fb = fastgl.sample_map_fused(to_dev(indptr, ptr_dtype), to_dev(indices), to_dev(seeds), to_dev(counts),
+                                 fanouts_sampling, replace=replace, arrival_order=False, rng_seed=31337, rng_ctr=800,
+                                 n_teams=n_teams)
+    fastgl.check_status()
+    L = len(fanouts_sampling)
+    for b, s in enumerate(seed_lists):
+        # the oracle takes the fanouts input-layer first and walks them reversed (FusedMapSampler.py:72)
+        inputs, _, blocks = oc.sample_blocks(indptr, indices, np.asarray(s, dtype=np.int32), list(reversed(fanouts_sampling)),
+                                             replace, rng_seed=31337, rng_ctr=800 + 8 * b)
+        got_blocks = fb.blocks(b)
+        assert np.array_equal(fb.input_nodes(b).cpu().numpy(), inputs), f"batch {b} node list"
+        assert len(got_blocks) == L
+        for (gptr, gsrc, n_src, n_dst), ref in zip(got_blocks, blocks):
+            assert (n_src, n_dst) == (ref["n_src"], ref["n_dst"])
+            assert np.array_equal(gptr.cpu().numpy(), ref["indptr"])
+            assert np.array_equal(gsrc.cpu().numpy(), ref["src_local"])
+    return fb
+
+
+@pytest.mark.parametrize("replace", [False, True])
+@pytest.mark.parametrize("n_teams", [1, 3])
+def test_fused_matches_oracle(fastgl, graph, replace, n_teams):
+    indptr, indices = graph
+    rng = np.random.default_rng(17)
+    seed_lists = [rng.choice(len(indptr) - 1, size=n, replace=False).astype(np.int32) for n in (256, 256, 100, 1, 256)]
+    seed_lists[0][0] = 0
+    run_fused_and_compare(fastgl, indptr, indices, seed_lists, [5, 10, 15], replace, n_teams)
+
+
+def test_fused_int32_indptr_single_batch_two_hops(fastgl, graph):
+    indptr, indices = graph
+    seeds = [np.arange(50, 1074, dtype=np.int32)]
+    run_fused_and_compare(fastgl, indptr, indices, seeds, [10, 25], False, 0, ptr_dtype=torch.int32)
+
+
+def test_fused_frontier_saturates_small_graph(fastgl):
+    # the frontier reaches every node: capacities are clamped by the node count
+    indptr, indices = make_graph(600, 10, seed=2, hub=100)
+    seeds = [np.arange(0, 128, dtype=np.int32), np.arange(300, 428, dtype=np.int32)]
+    run_fused_and_compare(fastgl, indptr, indices, seeds, [5, 10, 15], False, 2)
+
+
+def test_fused_empty_batch_list_and_empty_batch(fastgl, graph):
+    indptr, indices = graph
+    run_fused_and_compare(fastgl, indptr, indices, [np.zeros(0, dtype=np.int32), np.arange(10, dtype=np.int32)], [3, 3], False, 0)
+
+
+def test_fused_arrival_order_invariants(fastgl, graph):
+    indptr, indices = graph
+    rng = np.random.default_rng(4)
+    seeds = rng.choice(len(indptr) - 1, size=(3, 512), replace=False).astype(np.int32)
+    counts = np.full(3, 512, dtype=np.int32)
+    fan = [5, 10, 15]
+    fb = fastgl.sample_map_fused(to_dev(indptr), to_dev(indices), to_dev(seeds), to_dev(counts), fan, replace=False,
+                                 arrival_order=True, rng_seed=5, rng_ctr=0)
+    fastgl.check_status()
+    for b in range(3):
+        nodes = fb.input_nodes(b).cpu().numpy()
+        assert len(set(nodes.tolist())) == len(nodes)
+        cur = seeds[b]
+        for h, (gptr, gsrc, n_src, n_dst) in enumerate(reversed(fb.blocks(b))):
+            rptr, rsrc, _ = oc.sample(indptr, indices, cur, fan[h], False, rng_seed=5, rng_ctr=8 * b + h)
+            assert n_dst == len(cur) and np.array_equal(gptr.cpu().numpy(), rptr)
+            assert np.array_equal(nodes[gsrc.cpu().numpy()], rsrc)      # every edge maps back to its global source
+            assert np.array_equal(nodes[:n_dst], cur)
+            cur = nodes[:n_src]
+
+
+# ----------------------------------------------------------------------------------------------
+# a4-a7
+# ----------------------------------------------------------------------------------------------
+def random_block(rng, n_dst, n_src, max_deg, zero_frac=0.1):
+    deg = rng.integers(1, max_deg + 1, size=n_dst)
+    deg[rng.random(n_dst) < zero_frac] = 0
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    src = rng.integers(0, n_src, size=int(indptr[-1])).astype(np.int32)
+    return indptr, src
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("dim", [1, 47, 100, 128, 256, 602, 1024])
+def test_aggregate_forward_backward(fastgl, mode, dim):
+    rng = np.random.default_rng(dim * 3 + mode)
+    n_dst, n_src = 700, 2500
+    indptr, src = random_block(rng, n_dst, n_src, 40 if dim < 600 else 15)
+    x = rng.standard_normal((n_src, dim)).astype(np.float32)
+    dy = rng.standard_normal((n_dst, dim)).astype(np.float32)
+    sdeg = np.maximum(oc.cal_deg(src, n_src), 1)
+    ddeg = np.maximum(np.diff(indptr), 1).astype(np.int32)
+    out = fastgl.aggregate(mode, to_dev(indptr), to_dev(src), to_dev(x), n_dst, to_dev(sdeg), to_dev(ddeg))
+    ref = oc.aggregate_fwd(mode, indptr, src, x, n_dst, sdeg, ddeg)
+    assert rel_err(out.cpu().numpy(), ref) <= AGG_RTOL
+    dx = fastgl.aggregate_backward(mode, to_dev(indptr), to_dev(src), to_dev(dy), n_src, to_dev(sdeg), to_dev(ddeg))
+    refb = oc.aggregate_bwd(mode, indptr, src, dy, n_src, sdeg, ddeg)
+    assert rel_err(dx.cpu().numpy(), refb) <= AGG_RTOL
+
+
+def test_aggregate_high_degree_rows_and_row_map(fastgl):
+    rng = np.random.default_rng(9)
+    n_dst, n_src, dim = 64, 30000, 100
+    deg = np.array([20000, 0, 33, 1] * 16)
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    src = rng.integers(0, n_src, size=int(indptr[-1])).astype(np.int32)
+    table = rng.standard_normal((50000, dim)).astype(np.float32)
+    row_map = rng.choice(50000, size=n_src, replace=False).astype(np.int32)
+    out = fastgl.aggregate(1, to_dev(indptr), to_dev(src), to_dev(table), n_dst, row_map=to_dev(row_map),
+                           zero_deg_passthrough=False)
+    ref = oc.aggregate_fwd(1, indptr, src, table, n_dst, zero_deg_passthrough=False, row_map=row_map)
+    assert rel_err(out.cpu().numpy(), ref) <= AGG_RTOL
+    assert not out[1].any()
+
+
+def test_gcn_ops_match_oracle(fastgl):
+    from oracle import oracle_np as on
+    rng = np.random.default_rng(12)
+    n_dst, n_src, din, dout = 300, 900, 100, 47
+    indptr, src = random_block(rng, n_dst, n_src, 12)
+    x = rng.standard_normal((n_src, din)).astype(np.float32)
+    w = (rng.standard_normal((din, dout)) / 10).astype(np.float32)
+    g = rng.standard_normal((n_dst, dout)).astype(np.float32)
+    sdeg = np.maximum(oc.cal_deg(src, n_src), 1)
+    ddeg = np.maximum(np.diff(indptr), 1).astype(np.int32)
+    t = [to_dev(a) for a in (indptr, src, sdeg, ddeg, x, w, g)]
+    out = fastgl.forward_gcn(t[0], t[1], t[2], t[3], t[4], t[5], 12, n_dst)[0]
+    assert rel_err(out.cpu().numpy(), on.forward_gcn(indptr, src, sdeg, ddeg, x, w, n_dst)) <= 5e-5  # includes the tf32-free mm
+    d_x, d_w = fastgl.backward_gcn(t[0], t[1], t[3], t[2], t[6], t[5], t[4])  # swapped degrees, GraphConv.py:37
+    rx, rw = on.backward_gcn(indptr, src, ddeg, sdeg, g, w, x)
+    assert rel_err(d_x.cpu().numpy(), rx) <= 5e-5 and rel_err(d_w.cpu().numpy(), rw) <= 5e-5
+
+
+def test_gin_ops_match_oracle(fastgl):
+    from oracle import oracle_np as on
+    rng = np.random.default_rng(13)
+    n_dst, n_src, din, dout = 300, 900, 128, 256
+    indptr, src = random_block(rng, n_dst, n_src, 10)
+    x = rng.standard_normal((n_src, din)).astype(np.float32)
+    w = (rng.standard_normal((din, dout)) / 10).astype(np.float32)
+    g = rng.standard_normal((n_dst, dout)).astype(np.float32)
+    t = [to_dev(a) for a in (indptr, src, x, w, g)]
+    out, tmp = fastgl.forwaed_gin(t[0], t[1], t[2], t[3], 10, n_dst)
+    rout, rtmp = on.forward_gin(indptr, src, x, w, n_dst)
+    assert rel_err(tmp.cpu().numpy(), rtmp) <= AGG_RTOL and rel_err(out.cpu().numpy(), rout) <= 5e-5
+    d_x, d_w = fastgl.backward_gin(t[0], t[1], t[4], t[3], tmp, n_src)
+    rx, rw = on.backward_gin(indptr, src, g, w, rtmp, n_src)
+    assert rel_err(d_x.cpu().numpy(), rx) <= 5e-5 and rel_err(d_w.cpu().numpy(), rw) <= 5e-5
+
+
+def test_golden_fixtures_on_gpu(fastgl):
+    g = np.load(GOLDEN)
+    indptr, indices, seeds = g["indptr"], g["indices"], g["seeds"]
+    for name, replace in (("norep", False), ("rep", True)):
+        src, dst, ptr, E = fastgl.sample_node_csr(to_dev(indices), to_dev(indptr), to_dev(seeds), 5, replace=replace,
+                                                  rng_seed=12345, rng_ctr=3)
+        assert np.array_equal(src.cpu().numpy(), g[f"{name}_src"]) and np.array_equal(ptr.cpu().numpy(), g[f"{name}_ptr"])
+        src = src.contiguous().clone()
+        dst = dst.contiguous().clone()
+        out = fastgl.transfer_edge_id(src, dst, to_dev(seeds), len(seeds), len(seeds) + E, 5 * len(seeds), E)
+        assert np.array_equal(out[0].cpu().numpy(), g[f"{name}_src_local"])
+        assert np.array_equal(out[1].cpu().numpy(), g[f"{name}_dst_local"])
+        assert np.array_equal(out[2].cpu().numpy(), g[f"{name}_unique"])
+    x, dy = to_dev(g["x"]), to_dev(g["dy"])
+    ptr0, src0 = to_dev(g["mh_ptr0"]), to_dev(g["mh_src0"])
+    for mode, tag in ((0, "sum"), (1, "mean"), (2, "sym")):
+        f = fastgl.aggregate(mode, ptr0, src0, x, ptr0.numel() - 1, to_dev(g["src_deg"]), to_dev(g["dst_deg"]))
+        b = fastgl.aggregate_backward(mode, ptr0, src0, dy, x.size(0), to_dev(g["src_deg"]), to_dev(g["dst_deg"]))
+        assert rel_err(f.cpu().numpy(), g[f"fwd_{tag}"]) <= AGG_RTOL and rel_err(b.cpu().numpy(), g[f"bwd_{tag}"]) <= AGG_RTOL
