@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the FastGL per-mini-batch hot path on B200: sample -> Fused-Map -> 3-layer GraphSAGE-mean
+forward / backward / Adam, on a seeded synthetic R-MAT graph with the shape of the single-GPU configuration
+(2.45 M nodes, ~124 M directed edges, 100-d fp32 features, 47 classes, 8 % train seeds, fanout [15,10,5],
+batch 1024 per GPU).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl fastgl|reference]
+
+One "step" is one data-parallel training step: every rank samples, maps and trains one mini-batch of 1024
+seeds (windows of ``--window`` mini-batches are sampled by one kernel launch inside the timed region).
+Rank 0 prints one JSON line.  ``--impl reference`` times the CPU restatement of the same step (the reference
+itself has no CPU code path and is CUDA-only for sm_80) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "fastgl-ae_b200"))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+CONFIGS = {
+    # name: nodes, avg directed degree, feature dim, classes, train fraction, fanouts (input layer first)
+    "products-like": dict(n_nodes=2_450_000, avg_degree=50.6, feat_dim=100, n_classes=47, train_frac=0.08,
+                          fanouts=[15, 10, 5], hidden=256, batch=1024),
+    "small": dict(n_nodes=100_000, avg_degree=20.0, feat_dim=128, n_classes=10, train_frac=0.10,
+                  fanouts=[15, 10, 5], hidden=256, batch=1024),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons = [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9 or not f[1].isdigit():
+                    continue
+                sm.append(int(f[1]))
+                out["sm_max_mhz"] = int(f[2])
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+def build_inputs(cfg, device):
+    from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
+    indptr, indices = rmat_graph(cfg["n_nodes"], cfg["avg_degree"], seed=12345, device=device)
+    feat, labels, train = synthetic_node_data(cfg["n_nodes"], cfg["feat_dim"], cfg["n_classes"], cfg["train_frac"],
+                                              seed=12345, device=device)
+    return indptr, indices, feat, labels, train
+
+
+# ----------------------------------------------------------------------------------------------------------
+# CPU restatement of one training step (oracle sampling / mapping / aggregation + torch CPU dense algebra)
+# ----------------------------------------------------------------------------------------------------------
+def make_cpu_stepper(cfg, indptr, indices, feat, labels, train):
+    from oracle import oracle_c as oc
+    import torch.nn.functional as F
+
+    oc.set_threads(os.cpu_count() or 1)
+    torch.set_num_threads(os.cpu_count() or 1)
+    ip, ix = indptr.cpu().numpy(), indices.cpu().numpy()
+    feat_c, labels_c, train_c = feat.cpu(), labels.cpu(), train.cpu().numpy()
+    feat_np = feat_c.numpy()
+
+    class MeanAgg(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, blk, row_map):
+            ctx.blk = blk
+            ctx.n_src = x.shape[0]
+            out = oc.aggregate_fwd(oc.MODE_MEAN, blk["indptr"], blk["src_local"], x.detach().numpy(), blk["n_dst"],
+                                   zero_deg_passthrough=False, row_map=row_map)
+            return torch.from_numpy(out)
+
+        @staticmethod
+        def backward(ctx, dy):
+            if not ctx.needs_input_grad[0]:
+                return None, None, None
+            blk = ctx.blk
+            dx = oc.aggregate_bwd(oc.MODE_MEAN, blk["indptr"], blk["src_local"], dy.contiguous().numpy(), ctx.n_src)
+            return torch.from_numpy(dx), None, None
+
+    torch.manual_seed(0)
+    dims = [cfg["feat_dim"]] + [cfg["hidden"]] * (len(cfg["fanouts"]) - 1) + [cfg["n_classes"]]
+    params = []
+    for i in range(len(dims) - 1):
+        params += [torch.nn.Parameter(torch.randn(dims[i], dims[i + 1]) * 0.05),
+                   torch.nn.Parameter(torch.randn(dims[i], dims[i + 1]) * 0.05),
+                   torch.nn.Parameter(torch.zeros(dims[i + 1]))]
+    opt = torch.optim.Adam(params, lr=0.01, weight_decay=5e-4)
+    rng = np.random.default_rng(12345)
+    state = {"ctr": 0}
+
+    def step():
+        seeds = rng.choice(train_c, size=cfg["batch"], replace=False).astype(np.int32)
+        inputs, _, blocks = oc.sample_blocks(ip, ix, seeds, cfg["fanouts"], False, rng_seed=12345, rng_ctr=state["ctr"])
+        state["ctr"] += 8
+        h = None
+        for i, blk in enumerate(blocks):
+            ws, wn, b = params[3 * i: 3 * i + 3]
+            if i == 0:
+                neigh = MeanAgg.apply(feat_c, blk, inputs)
+                h_self = torch.from_numpy(feat_np[inputs[: blk["n_dst"]]])
+            else:
+                h = torch.relu(h)
+                neigh = MeanAgg.apply(h, blk, None)
+                h_self = h[: blk["n_dst"]]
+            h = torch.addmm(b, h_self, ws) + neigh @ wn
+        loss = F.cross_entropy(h, labels_c[torch.from_numpy(seeds.astype(np.int64))])
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return sum(len(blk["src_local"]) for blk in blocks), float(loss.detach())
+
+    return step, oc.max_threads()
+
+
+def time_cpu_steps(step, n_steps):
+    edges = 0
+    t0 = time.perf_counter()
+    for _ in range(n_steps):
+        e, _ = step()
+        edges += e
+    dt = time.perf_counter() - t0
+    return edges, dt
+
+
+# ----------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="fastgl", choices=["fastgl", "reference"])
+    ap.add_argument("--config", default="products-like", choices=sorted(CONFIGS))
+    ap.add_argument("--window", type=int, default=8, help="mini-batches sampled per kernel launch")
+    ap.add_argument("--teams", type=int, default=0)
+    ap.add_argument("--reorder", action="store_true", help="Match-Reorder each window")
+    ap.add_argument("--cpu-steps", type=int, default=3, help="mini-batches of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    args.warmup = max(args.warmup, 3) if args.impl == "fastgl" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config_json = {"workload": f"{args.config}: seeded R-MAT {cfg['n_nodes']} nodes x avg degree {cfg['avg_degree']} "
+                               f"(symmetrised), {cfg['feat_dim']}-d fp32 features resident in HBM, {cfg['n_classes']} classes, "
+                               f"3-layer GraphSAGE-mean hidden {cfg['hidden']}, fanout {cfg['fanouts']}, batch {cfg['batch']} per GPU",
+                   "window": args.window, "parallelism": f"dp{world}", "global_batch": cfg["batch"] * world,
+                   "l2": "inputs larger than L2: 392 MB feature table + 0.5 GB adjacency are gathered at random each step"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+        indptr, indices, feat, labels, train = build_inputs(cfg, device)
+        step, cores = make_cpu_stepper(cfg, indptr, indices, feat, labels, train)
+        for _ in range(args.warmup):
+            step()
+        edges, dt = time_cpu_steps(step, args.steps)
+        val = edges / dt
+        line = {"impl": "reference", "metric": "sampled_edges_per_s", "value": val, "unit": "edges/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / max(1, args.steps),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config_json, "gpu_launches": 0,
+                "cpu_baseline": {"value": val, "unit": "edges/s", "cores": cores, "kind": "port",
+                                 "sample": f"{args.steps} mini-batches of {cfg['batch']} seeds: C oracle sampling + mapping + "
+                                           "aggregation, torch CPU dense layers and Adam"},
+                "e2e": {"value": val, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fastgl ops have no CPU path")
+    import fastgl
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    torch.manual_seed(12345)
+    indptr, indices, feat, labels, train = build_inputs(cfg, device)
+    model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
+    model.train()
+    tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
+                 reorder=args.reorder, rank=rank, world=world, n_teams=args.teams)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    # --- warm-up, then the device-resident timed region ---------------------------------------------------
+    tr.run_steps(args.warmup)
+    fastgl.check_status(device)
+    barrier()
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    tr.sampled_edges = 0
+    tr.time_layer0 = True
+    tr.layer0_events.clear()
+    counter_at_start = tr.sampler.batch_counter
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    tr.run_steps(args.steps)
+    ev1.record()
+    barrier()
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
+    edges_all = sum_over_ranks(float(tr.sampled_edges))
+    tr.time_layer0 = False
+    value = edges_all / (ms * 1e-3)
+    fastgl.check_status(device)
+
+    # --- roofline of the dominant kernel: first-layer mean aggregation straight from the feature table ----
+    agg_ms = [s.elapsed_time(e) for s, e, _ in tr.layer0_events]
+    D = cfg["feat_dim"]
+    alg_bytes = []
+    last_window = (args.steps % args.window) or args.window
+    for _, _, blk in tr.layer0_events[-last_window:]:  # the last window's blocks are still in the buffers
+        r_src = int(torch.unique(blk.src).numel())
+        alg_bytes.append(4 * D * (r_src + blk.n_dst) + 4 * blk.num_edges() + 4 * (blk.n_dst + 1) + 4 * r_src)
+    peak, peak_kind = load_peaks()
+    mean_agg_ms = statistics.mean(agg_ms) if agg_ms else float("nan")
+    mean_bytes = statistics.mean(alg_bytes) if alg_bytes else 0.0
+    achieved = mean_bytes / (mean_agg_ms * 1e-3) / 1e9 if agg_ms else None
+    roofline = {"kernel": "agg_fwd_kernel<4, MEAN, row_map> (layer 0)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "algorithmic_bytes_per_launch": mean_bytes, "launch_ms": mean_agg_ms, "launches_timed": len(agg_ms)}
+
+    # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
+    host_rows, host_counts = [], []
+    for _ in range(args.steps):
+        s, c = tr._next_window_seeds(1)
+        host_rows.append(s.cpu())
+        host_counts.append(c)
+    seeds_h = torch.cat(host_rows).pin_memory()
+    counts_h = torch.cat(host_counts).pin_memory()
+    tr.sampled_edges = 0
+    barrier()
+    ev0.record()
+    losses = tr.run_steps(args.steps, host_seeds=(seeds_h, counts_h), read_loss_each_step=True)
+    ev1.record()
+    barrier()
+    ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
+    e2e_edges = sum_over_ranks(float(tr.sampled_edges))
+    clock_info = clocks.stop() if rank == 0 else None
+    fastgl.check_status(device)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        step, cores = make_cpu_stepper(cfg, indptr, indices, feat, labels, train)
+        step()
+        edges, dt = time_cpu_steps(step, args.cpu_steps)
+        cpu_baseline = {"value": edges / dt, "unit": "edges/s", "cores": cores, "kind": "port",
+                        "sample": f"{args.cpu_steps} mini-batches of {cfg['batch']} seeds (after 1 warm-up): C oracle sampling + "
+                                  "mapping + aggregation, torch CPU dense layers and Adam", "ms_per_step": 1e3 * dt / args.cpu_steps}
+
+    if rank == 0:
+        steps_per_epoch = tr.steps_per_epoch()
+        # kernels of this library per step: 1/window fused sampling launches + 3 forward + 2 backward aggregations
+        launches = args.steps * (len(cfg["fanouts"]) * 2 - 1) + (args.steps + args.window - 1) // args.window
+        line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_json,
+                "per_gpu_value": value / world, "epoch_time_s": steps_per_epoch * ms / args.steps * 1e-3,
+                "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
+                "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
+                        "h2d_bytes_per_step": cfg["batch"] * 4 + 4, "d2h_bytes_per_step": 4 + 64},
+                "gpu_launches": launches * world, "roofline": roofline, "clocks": clock_info}
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,199 @@
+"""GNN layers over the ``fastgl`` aggregation ops.
+
+``MA_Function`` / ``MA_Function_GIN``, ``GCNConv`` / ``GINConv`` and ``GCN`` / ``GIN`` keep the interface and
+the arithmetic of the reference's GraphConv.py (:19-40, :102-135, :42-99, :138-195): update-then-aggregate for
+GCN, aggregate-then-update for GIN, dropout between layers, no bias and no activation.  ``SAGEConv`` /
+``GraphSAGE`` add the mean aggregator that the benchmark configurations name (the reference has none): 
+``h' = h_dst W_self + mean_{s in N(d)} h_s W_neigh + b``, with the first layer aggregating straight from the
+HBM-resident feature table through the block's global ids, so the gathered input matrix is never built.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+import fastgl
+
+
+def block_csr(block):
+    """(edge_ptr, src_edges) of a block.  A block from this package carries its CSR; for any other object
+    with the reference's block interface the CSR is rebuilt the way GraphConv.py:92-94 does."""
+    if hasattr(block, "indptr"):
+        return block.indptr, block.src
+    src, dst = block.edges()
+    deg = fastgl.cal_deg(dst.int().contiguous(), block.num_dst_nodes())
+    return fastgl.exclusive_sum(deg), src.int().contiguous()
+
+
+class MA_Function(torch.autograd.Function):
+    """GraphConv.py:19-40."""
+
+    @staticmethod
+    def forward(ctx, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, weight, neighbor_num):
+        ctx.save_for_backward(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat)
+        return fastgl.forward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, input_feat, weight, neighbor_num,
+                                  dst_nodes)[0]
+
+    @staticmethod
+    def backward(ctx, d_input):
+        edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat = ctx.saved_tensors
+        # destination degrees third, source degrees fourth: GraphConv.py:37
+        d_x, d_w = fastgl.backward_gcn(edge_ptr, src_edges, dst_norm_degs, src_norm_degs, d_input.contiguous(), weight,
+                                       input_feat)
+        return None, None, None, None, None, d_x, d_w, None
+
+
+class MA_Function_GIN(torch.autograd.Function):
+    """GraphConv.py:102-135."""
+
+    @staticmethod
+    def forward(ctx, edge_ptr, src_edges, dst_nodes, input_feat, weight, neighbor_num):
+        out, tmp = fastgl.forwaed_gin(edge_ptr, src_edges, input_feat, weight, neighbor_num, dst_nodes)
+        ctx.src_nodes = input_feat.size(0)
+        ctx.save_for_backward(edge_ptr, src_edges, weight, tmp)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_input):
+        edge_ptr, src_edges, weight, tmp = ctx.saved_tensors
+        d_x, d_w = fastgl.backward_gin(edge_ptr, src_edges, d_input.contiguous(), weight, tmp, ctx.src_nodes)
+        return None, None, None, d_x, d_w, None
+
+
+class _Conv(nn.Module):
+    def __init__(self, input_dim, output_dim):
+        super().__init__()
+        self.weights = nn.Parameter(torch.empty(input_dim, output_dim))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        stdv = 1.0 / math.sqrt(self.weights.size(1))  # GraphConv.py:50-53
+        with torch.no_grad():
+            self.weights.uniform_(-stdv, stdv)
+
+
+class GCNConv(_Conv):
+    def forward(self, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, neighbor_num):
+        return MA_Function.apply(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, self.weights,
+                                 neighbor_num)
+
+
+class GINConv(_Conv):
+    def forward(self, edge_ptr, src_edges, dst_nodes, input_feat, neighbor_num):
+        return MA_Function_GIN.apply(edge_ptr, src_edges, dst_nodes, input_feat, self.weights, neighbor_num)
+
+
+class _Stack(nn.Module):
+    conv = None
+
+    def __init__(self, in_feats, n_hidden, n_classes, n_layers, activation=None, weight=True, dropout=0.5):
+        super().__init__()
+        dims = [in_feats] + [n_hidden] * (n_layers - 1) + [n_classes]
+        self.layers = nn.ModuleList([self.conv(dims[i], dims[i + 1]) for i in range(n_layers)])
+        self.dropout = nn.Dropout(p=dropout)
+
+
+class GCN(_Stack):
+    """GraphConv.py:63-99: a linear stack (the reference accepts ``activation`` and never applies it)."""
+    conv = GCNConv
+
+    def forward(self, blocks, features, neighbor_list=(5, 10, 15)):
+        h = features
+        for i, layer in enumerate(self.layers):
+            if i != 0:
+                h = self.dropout(h)
+            block = blocks[i]
+            n_dst = block.num_dst_nodes()
+            edge_ptr, src_edges = block_csr(block)
+            dst_norm_degs = (edge_ptr[1: n_dst + 1] - edge_ptr[:n_dst]).clamp(min=1)         # GraphConv.py:93,97
+            src_norm_degs = fastgl.cal_deg(src_edges, block.num_src_nodes()).clamp(min=1)    # GraphConv.py:96
+            h = layer(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, n_dst, h, neighbor_list[i])
+        return h
+
+
+class GIN(_Stack):
+    """GraphConv.py:159-195."""
+    conv = GINConv
+
+    def forward(self, blocks, features, neighbor_list=(5, 10, 15)):
+        h = features
+        for i, layer in enumerate(self.layers):
+            if i != 0:
+                h = self.dropout(h)
+            block = blocks[i]
+            edge_ptr, src_edges = block_csr(block)
+            h = layer(edge_ptr, src_edges, block.num_dst_nodes(), h, neighbor_list[i])
+        return h
+
+
+class MeanAggregate(torch.autograd.Function):
+    """mean over in-neighbours (rows without in-edges give zeros); optional row map into a feature table."""
+
+    @staticmethod
+    def forward(ctx, x, edge_ptr, src_edges, n_dst, row_map):
+        ctx.save_for_backward(edge_ptr, src_edges)
+        ctx.n_src = x.size(0)
+        ctx.mapped = row_map is not None
+        return fastgl.aggregate(fastgl.AGG_MEAN, edge_ptr, src_edges, x, n_dst, zero_deg_passthrough=False, row_map=row_map)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        d_x = None
+        if ctx.needs_input_grad[0]:
+            if ctx.mapped:
+                raise RuntimeError("no gradient flows into a feature table that is aggregated through a row map")
+            edge_ptr, src_edges = ctx.saved_tensors
+            d_x = fastgl.aggregate_backward(fastgl.AGG_MEAN, edge_ptr, src_edges, d_out.contiguous(), ctx.n_src)
+        return d_x, None, None, None, None
+
+
+class SAGEConv(nn.Module):
+    def __init__(self, input_dim, output_dim):
+        super().__init__()
+        self.w_self = nn.Parameter(torch.empty(input_dim, output_dim))
+        self.w_neigh = nn.Parameter(torch.empty(input_dim, output_dim))
+        self.bias = nn.Parameter(torch.zeros(output_dim))
+        gain = math.sqrt(2.0)
+        bound = gain * math.sqrt(6.0 / (input_dim + output_dim))
+        with torch.no_grad():
+            self.w_self.uniform_(-bound, bound)
+            self.w_neigh.uniform_(-bound, bound)
+
+    def forward(self, block, h, row_map=None, timer=None):
+        """``h``: float32[n_src, in] -- or, with ``row_map`` (the block's global ids), the whole feature table.
+        ``timer`` (a list) receives (start_event, end_event, block) around the aggregation kernel."""
+        n_dst = block.num_dst_nodes()
+        edge_ptr, src_edges = block_csr(block)
+        if timer is not None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        h_neigh = MeanAggregate.apply(h, edge_ptr, src_edges, n_dst, row_map)
+        if timer is not None:
+            end.record()
+            timer.append((start, end, block))
+        h_self = h[:n_dst] if row_map is None else torch.index_select(h, 0, row_map[:n_dst].long())
+        return torch.addmm(self.bias, h_self, self.w_self) + torch.mm(h_neigh, self.w_neigh)
+
+
+class GraphSAGE(nn.Module):
+    """3-layer GraphSAGE-mean of the benchmark configurations: ReLU and dropout between layers."""
+
+    def __init__(self, in_feats, n_hidden, n_classes, n_layers, dropout=0.5):
+        super().__init__()
+        dims = [in_feats] + [n_hidden] * (n_layers - 1) + [n_classes]
+        self.layers = nn.ModuleList([SAGEConv(dims[i], dims[i + 1]) for i in range(n_layers)])
+        self.dropout = nn.Dropout(p=dropout)
+        self.layer0_timer = None  # set to a list to time the first layer's aggregation kernel
+
+    def forward(self, blocks, features, input_nodes=None):
+        """``features``: the gathered input rows float32[n_src_0, in]; or, with ``input_nodes`` (int32 global
+        ids of block 0's sources), the full feature table, read in place by the first layer."""
+        h = features
+        for i, layer in enumerate(self.layers):
+            if i != 0:
+                h = self.dropout(torch.relu(h))
+            h = layer(blocks[i], h, row_map=input_nodes if i == 0 else None,
+                      timer=self.layer0_timer if i == 0 else None)
+        return h
