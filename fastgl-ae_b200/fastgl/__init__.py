@@ -241,6 +241,21 @@ def exclusive_sum(in_degs):
     return out
 
 
+def exclusive_sum_noalloc(in_degs, out):
+    """``exclusive_sum`` into a caller-provided ``out`` (int32[n+1]) through the entry point that allocates
+    nothing on the device: for callers that run under a fixed memory budget or cannot afford an allocation's
+    device synchronisation.  At most 2**27 entries; calls on different streams must not overlap."""
+    _check_i32(in_degs, "in_degs")
+    _check_i32(out, "out")
+    if out.numel() < in_degs.numel() + 1:
+        raise RuntimeError("out needs in_degs.numel() + 1 entries")
+    dev = in_degs.device
+    with _on_device(dev):
+        rc = lib().fgl_exclusive_sum_noalloc(_ptr(in_degs), ctypes.c_int64(in_degs.numel()), _ptr(out), _stream(dev))
+    _raise(rc, "exclusive_sum_noalloc")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # a4-a7  aggregation
 # ------------------------------------------------------------------------------------------------

@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfastgl_b
 EXPORTS = (
     "fgl_abi_version", "fgl_sizeof_fused_args", "fgl_status_str", "fgl_ws_create", "fgl_ws_destroy", "fgl_ws_reserve", "fgl_last_error",
     "fgl_ws_check", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
-    "fgl_exclusive_sum", "fgl_agg_fwd", "fgl_agg_bwd",
+    "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_agg_fwd", "fgl_agg_bwd",
 )
 
 

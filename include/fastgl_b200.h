@@ -135,6 +135,18 @@ int fgl_cal_deg(const int32_t* ids, int64_t n_ids, int32_t* deg, int32_t n_nodes
  * aggregate_acc.cpp:514-520).  out has n + 1 entries. */
 int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream);
 
+/* The same scan for callers that cannot allocate device memory (a plugin under a framework allocator's
+ * fixed budget, a process whose HBM is fully handed out to other pools, a loop that cannot take
+ * cudaMalloc's device synchronisation).  No counterpart in the reference, which allocates scratch in every
+ * call.  The scratch (one barrier counter and one partial sum per CTA, about 4.5 KB) lives in a __device__
+ * array of the library, held by every GPU that loads it; the call takes no workspace and calls no allocating routine.  n may not exceed
+ * FGL_NOALLOC_MAX_N (else FGL_ERR_CAPACITY).  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress) and should come before any stream capture.  All calls on a device share
+ * the array: calls whose kernels overlap on the GPU (different streams) race.  Launches on the current
+ * device. */
+#define FGL_NOALLOC_MAX_N (1LL << 27)
+int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* stream);
+
 /* Aggregation forward; replaces the gather kernels K8 / K10 of the reference
  * (computation_aware_forward_gcn_cuda_kernel aggregate_acc_kernel.cu:271-331 and
  * computation_aware_forward_gin_cuda_kernel :376-427).  out[d, 0..dim) = sum over e in
