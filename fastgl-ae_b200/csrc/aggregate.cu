@@ -3,7 +3,14 @@
 // The work is HBM-bound (one FMA per 4 bytes read), so no tensor cores: a warp owns one destination row,
 // its lanes sweep the feature dimension with 128-bit loads (64- or 32-bit when the row stride is not a
 // multiple of 16 bytes, e.g. 602 floats), the neighbour ids of the row are read once, coalesced, and handed
-// round by shuffle, and the row's sum stays in registers until one coalesced store.
+// round by shuffle, the loads of several neighbours are issued before the first FMA, the ids of the warp's
+// next row are fetched while the current row is summed, and the row's sum stays in registers until one
+// coalesced store.  The number of accumulators is a template parameter chosen from
+// the row width, so narrow rows (100 / 128 floats) run with few registers and full occupancy.
+//
+// The forward kernel also runs over a whole window of mini-batches (per-batch strides, rows in batch-major
+// order), so the first layer of the window -- which reads only the feature table and does not depend on the
+// weights -- is one launch that is long enough to reach a steady state.
 //
 // Replaces K8 / K10 (aggregate_acc_kernel.cu:271-331, :376-427: 8 rows x 4 floats per warp, shared-memory
 // read-modify-write per neighbour) and K9 / K11 (:468-517, :555-596: scalar atomics, the GCN one built from
@@ -16,7 +23,12 @@ namespace fgl {
 
 constexpr int kAggThreads = 256;
 constexpr int kAggWarps = kAggThreads / 32;
-constexpr int kAcc = 4;  // vector accumulators per lane per pass: 32 lanes x 4 x VEC floats per pass
+#ifndef FGL_AGG_UNR1
+#define FGL_AGG_UNR1 8  // neighbour rows in flight per lane for rows of up to 32 vectors
+#endif
+#ifndef FGL_AGG_MIN_CTAS
+#define FGL_AGG_MIN_CTAS 3
+#endif
 
 template <int VEC>
 struct Vec;
@@ -58,61 +70,129 @@ struct AggParams {
     const int32_t* row_map;
     const float* x;  // forward: input rows; backward: dy
     float* out;      // forward: out; backward: dx
-    int64_t ldx, ldo;
+    float* self_out; // forward, optional: copy of the row's own input row x[row(d)]
+    int64_t ldx, ldo, ld_self;
     int32_t dim, n_dst, n_src;
     int32_t passthrough;
+    // window forward: all zero / NULL for a single block
+    int64_t indptr_stride, src_stride, row_map_stride;
+    int32_t n_batches;
+    const int64_t* out_row_off;  // [n_batches + 1]: first output row of batch b, then the total
 };
 
 // Forward: out[d,:] = scale_d * sum_e w_e * x[row(src[e]),:]
-template <int VEC, int MODE, bool HAS_MAP>
-__global__ void __launch_bounds__(kAggThreads) agg_fwd_kernel(const AggParams p) {
+// NACC vector accumulators per lane cover 32 * NACC * VEC floats per pass; UNR neighbours' loads are in
+// flight before their FMAs.  In window mode (out_row_off != NULL) the rows of all mini-batches form one
+// sequence in batch-major order and the grid sweeps it front to back, so that at any moment the CTAs work
+// on one or two mini-batches and the rows those batches re-read stay in L2.
+template <int VEC, int MODE, bool HAS_MAP, int NACC, int UNR>
+__global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(const AggParams p) {
     using V = Vec<VEC>;
     using T = typename V::T;
     const int lane = threadIdx.x & 31;
     const int warp_global = blockIdx.x * kAggWarps + (threadIdx.x >> 5);
     const int n_warps = gridDim.x * kAggWarps;
     const int chunks = p.dim / VEC;  // dim % VEC == 0 by dispatch
+    const bool window = p.out_row_off != nullptr;
+    const int64_t total = window ? __ldg(p.out_row_off + p.n_batches) : (int64_t)p.n_dst;
 
-    for (int d = warp_global; d < p.n_dst; d += n_warps) {
-        const int a = __ldg(p.indptr + d), b = __ldg(p.indptr + d + 1);
-        T* orow = reinterpret_cast<T*>(p.out + (int64_t)d * p.ldo);
-        if (a >= b) {  // aggregate_acc_kernel.cu:307-308, :405-406
-            const int64_t r = HAS_MAP ? (int64_t)__ldg(p.row_map + d) : (int64_t)d;
-            const T* xr = reinterpret_cast<const T*>(p.x + r * p.ldx);
+    // State of the row after the current one.  Its ids are fetched one row ahead so that the dependent chain
+    // indptr -> src -> row_map is off the critical path.
+    int b_n = 0, d_n = 0, a_n = 0, e_n = 0;
+    int64_t lo_n = 0, hi_n = window ? __ldg(p.out_row_off + 1) : total;
+    int64_t row_n = 0, self_n = 0;
+    float w_n = 1.0f;
+    auto prefetch = [&](int64_t g) {
+        a_n = 0;
+        e_n = 0;
+        row_n = 0;
+        w_n = 1.0f;
+        if (g >= total) return;
+        while (g >= hi_n) {  // window mode only: step to the mini-batch that holds row g
+            ++b_n;
+            lo_n = hi_n;
+            hi_n = __ldg(p.out_row_off + b_n + 1);
+        }
+        d_n = (int)(g - lo_n);
+        const int32_t* indptr = p.indptr + (int64_t)b_n * p.indptr_stride;
+        const int32_t* src = p.src + (int64_t)b_n * p.src_stride;
+        const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b_n * p.row_map_stride : nullptr;
+        a_n = __ldg(indptr + d_n);
+        e_n = __ldg(indptr + d_n + 1);
+        if (lane < e_n - a_n) {
+            const int s = __ldg(src + a_n + lane);
+            row_n = HAS_MAP ? (int64_t)__ldg(row_map + s) : (int64_t)s;
+            if (MODE == FGL_AGG_SYMNORM) w_n = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+        }
+        self_n = HAS_MAP ? (int64_t)__ldg(row_map + d_n) : (int64_t)d_n;
+    };
+    prefetch(warp_global);
+
+    for (int64_t g = warp_global; g < total; g += n_warps) {
+        const int b = b_n, d = d_n, a = a_n, e_end = e_n;
+        const int64_t first_row = row_n, self_row = self_n;  // neighbours a .. a+31 and the row's own source
+        const float first_w = w_n;
+        prefetch(g + n_warps);
+        const int32_t* src = p.src + (int64_t)b * p.src_stride;
+        const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b * p.row_map_stride : nullptr;
+        T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
+        if (p.self_out) {
+            const T* xr = reinterpret_cast<const T*>(p.x + self_row * p.ldx);
+            T* srow = reinterpret_cast<T*>(p.self_out + g * p.ld_self);
+            for (int c = lane; c < chunks; c += 32) srow[c] = __ldg(xr + c);
+        }
+        if (a >= e_end) {  // aggregate_acc_kernel.cu:307-308, :405-406
+            const T* xr = reinterpret_cast<const T*>(p.x + self_row * p.ldx);
             for (int c = lane; c < chunks; c += 32) orow[c] = p.passthrough ? __ldg(xr + c) : V::zero();
             continue;
         }
         float scale = 1.0f;
-        if (MODE == FGL_AGG_MEAN) scale = 1.0f / (float)(b - a);
+        if (MODE == FGL_AGG_MEAN) scale = 1.0f / (float)(e_end - a);
         if (MODE == FGL_AGG_SYMNORM) scale = 1.0f / sqrtf((float)__ldg(p.dst_deg + d));
 
-        for (int c0 = 0; c0 < chunks; c0 += 32 * kAcc) {
-            T acc[kAcc];
+        for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
+            T acc[NACC];
 #pragma unroll
-            for (int k = 0; k < kAcc; ++k) acc[k] = V::zero();
-            for (int e0 = a; e0 < b; e0 += 32) {
-                const int cnt = min(32, b - e0);
-                int64_t my_row = 0;
-                float my_w = 1.0f;
-                if (lane < cnt) {
-                    const int s = __ldg(p.src + e0 + lane);
-                    my_row = HAS_MAP ? (int64_t)__ldg(p.row_map + s) : (int64_t)s;
-                    if (MODE == FGL_AGG_SYMNORM) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+            for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
+            for (int e0 = a; e0 < e_end; e0 += 32) {
+                const int cnt = min(32, e_end - e0);
+                int64_t my_row = first_row;
+                float my_w = first_w;
+                if (e0 != a) {
+                    my_row = 0;
+                    my_w = 1.0f;
+                    if (lane < cnt) {
+                        const int s = __ldg(src + e0 + lane);
+                        my_row = HAS_MAP ? (int64_t)__ldg(row_map + s) : (int64_t)s;
+                        if (MODE == FGL_AGG_SYMNORM) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+                    }
                 }
-#pragma unroll 4
-                for (int j = 0; j < cnt; ++j) {
-                    const int64_t r = __shfl_sync(0xffffffffu, my_row, j);
-                    const float w = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, j) : 1.0f;
-                    const T* xr = reinterpret_cast<const T*>(p.x + r * p.ldx);
+                for (int j0 = 0; j0 < cnt; j0 += UNR) {
+                    T v[UNR][NACC];
+                    float w[UNR];
 #pragma unroll
-                    for (int k = 0; k < kAcc; ++k) {
-                        const int c = c0 + k * 32 + lane;
-                        if (c < chunks) V::fma(acc[k], w, __ldg(xr + c));
+                    for (int u = 0; u < UNR; ++u) {
+                        const int j = min(j0 + u, cnt - 1);  // past the end: reload the last row, skip its FMA
+                        const int64_t r = __shfl_sync(0xffffffffu, my_row, j);
+                        w[u] = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, j) : 1.0f;
+                        const T* xr = reinterpret_cast<const T*>(p.x + r * p.ldx);
+#pragma unroll
+                        for (int k = 0; k < NACC; ++k) {
+                            const int c = c0 + k * 32 + lane;
+                            v[u][k] = (c < chunks) ? __ldg(xr + c) : V::zero();
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+                        if (j0 + u < cnt) {  // warp-uniform
+#pragma unroll
+                            for (int k = 0; k < NACC; ++k) V::fma(acc[k], w[u], v[u][k]);
+                        }
                     }
                 }
             }
 #pragma unroll
-            for (int k = 0; k < kAcc; ++k) {
+            for (int k = 0; k < NACC; ++k) {
                 const int c = c0 + k * 32 + lane;
                 if (c < chunks) orow[c] = (MODE == FGL_AGG_SUM) ? acc[k] : V::scale(acc[k], scale);
             }
@@ -125,7 +205,7 @@ __device__ __forceinline__ void red_add(float2* addr, const float2& v) { atomicA
 __device__ __forceinline__ void red_add(float* addr, const float& v) { atomicAdd(addr, v); }
 
 // Backward: dx[src[e],:] += w_e * scale_d * dy[d,:]; vector reductions (red.global.add.v4.f32 on sm_100a)
-template <int VEC, int MODE>
+template <int VEC, int MODE, int NACC>
 __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p) {
     using V = Vec<VEC>;
     using T = typename V::T;
@@ -142,10 +222,10 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
         if (MODE == FGL_AGG_SYMNORM) scale = 1.0f / sqrtf((float)__ldg(p.dst_deg + d));
         const T* grow = reinterpret_cast<const T*>(p.x + (int64_t)d * p.ldx);
 
-        for (int c0 = 0; c0 < chunks; c0 += 32 * kAcc) {
-            T g[kAcc];
+        for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
+            T g[NACC];
 #pragma unroll
-            for (int k = 0; k < kAcc; ++k) {
+            for (int k = 0; k < NACC; ++k) {
                 const int c = c0 + k * 32 + lane;
                 g[k] = (c < chunks) ? V::scale(__ldg(grow + c), scale) : V::zero();
             }
@@ -163,7 +243,7 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
                     if (s < 0 || s >= p.n_src) continue;  // warp-uniform
                     T* xr = reinterpret_cast<T*>(p.out + (int64_t)s * p.ldo);
 #pragma unroll
-                    for (int k = 0; k < kAcc; ++k) {
+                    for (int k = 0; k < NACC; ++k) {
                         const int c = c0 + k * 32 + lane;
                         if (c < chunks) red_add(xr + c, (MODE == FGL_AGG_SYMNORM) ? V::scale(g[k], w) : g[k]);
                     }
@@ -173,42 +253,77 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
     }
 }
 
-static int pick_vec(const void* a, int64_t lda, const void* b, int64_t ldb, int dim) {
+static bool aligned_for(int v, const void* a, int64_t lda) { return lda % v == 0 && ((uintptr_t)a % (4 * v)) == 0; }
+
+static int pick_vec(int dim, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c = nullptr, int64_t ldc = 4) {
     auto ok = [&](int v) {
-        return dim % v == 0 && lda % v == 0 && ldb % v == 0 && ((uintptr_t)a % (4 * v)) == 0 && ((uintptr_t)b % (4 * v)) == 0;
+        return dim % v == 0 && aligned_for(v, a, lda) && aligned_for(v, b, ldb) && (!c || aligned_for(v, c, ldc));
     };
     if (ok(4)) return 4;
     if (ok(2)) return 2;
     return 1;
 }
 
-static int agg_grid(int n_rows) {
+static int agg_grid_x(int n_rows, int n_batches) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t want = ((int64_t)n_rows + kAggWarps - 1) / kAggWarps;
-    return (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)sms * 8));
+    const int64_t cap = std::max<int64_t>(1, ((int64_t)sms * 8 + n_batches - 1) / n_batches);
+    return (int)std::max<int64_t>(1, std::min<int64_t>(want, cap));
+}
+
+template <int VEC, int MODE, int NACC, int UNR>
+static void launch_fwd(const AggParams& p, dim3 grid, cudaStream_t st) {
+    if (p.row_map)
+        agg_fwd_kernel<VEC, MODE, true, NACC, UNR><<<grid, kAggThreads, 0, st>>>(p);
+    else
+        agg_fwd_kernel<VEC, MODE, false, NACC, UNR><<<grid, kAggThreads, 0, st>>>(p);
 }
 
 template <int VEC, int MODE>
-static void launch_fwd(const AggParams& p, int grid, cudaStream_t st) {
-    if (p.row_map)
-        agg_fwd_kernel<VEC, MODE, true><<<grid, kAggThreads, 0, st>>>(p);
+static void launch_fwd_nacc(const AggParams& p, dim3 grid, cudaStream_t st) {
+    const int chunks = p.dim / VEC;
+    if (chunks <= 32)
+        launch_fwd<VEC, MODE, 1, FGL_AGG_UNR1>(p, grid, st);
+    else if (chunks <= 64)
+        launch_fwd<VEC, MODE, 2, 4>(p, grid, st);
     else
-        agg_fwd_kernel<VEC, MODE, false><<<grid, kAggThreads, 0, st>>>(p);
+        launch_fwd<VEC, MODE, 4, 2>(p, grid, st);
 }
 
 template <int VEC>
-static void launch_fwd_mode(int mode, const AggParams& p, int grid, cudaStream_t st) {
-    if (mode == FGL_AGG_SUM) launch_fwd<VEC, FGL_AGG_SUM>(p, grid, st);
-    if (mode == FGL_AGG_MEAN) launch_fwd<VEC, FGL_AGG_MEAN>(p, grid, st);
-    if (mode == FGL_AGG_SYMNORM) launch_fwd<VEC, FGL_AGG_SYMNORM>(p, grid, st);
+static void launch_fwd_mode(int mode, const AggParams& p, dim3 grid, cudaStream_t st) {
+    if (mode == FGL_AGG_SUM) launch_fwd_nacc<VEC, FGL_AGG_SUM>(p, grid, st);
+    if (mode == FGL_AGG_MEAN) launch_fwd_nacc<VEC, FGL_AGG_MEAN>(p, grid, st);
+    if (mode == FGL_AGG_SYMNORM) launch_fwd_nacc<VEC, FGL_AGG_SYMNORM>(p, grid, st);
+}
+
+static int launch_fwd_any(int mode, const AggParams& p, dim3 grid, int vec, cudaStream_t st) {
+    switch (vec) {
+        case 4: launch_fwd_mode<4>(mode, p, grid, st); break;
+        case 2: launch_fwd_mode<2>(mode, p, grid, st); break;
+        default: launch_fwd_mode<1>(mode, p, grid, st); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+
+template <int VEC, int MODE>
+static void launch_bwd_nacc(const AggParams& p, int grid, cudaStream_t st) {
+    const int chunks = p.dim / VEC;
+    if (chunks <= 32)
+        agg_bwd_kernel<VEC, MODE, 1><<<grid, kAggThreads, 0, st>>>(p);
+    else if (chunks <= 64)
+        agg_bwd_kernel<VEC, MODE, 2><<<grid, kAggThreads, 0, st>>>(p);
+    else
+        agg_bwd_kernel<VEC, MODE, 4><<<grid, kAggThreads, 0, st>>>(p);
 }
 
 template <int VEC>
 static void launch_bwd_mode(int mode, const AggParams& p, int grid, cudaStream_t st) {
-    if (mode == FGL_AGG_SUM) agg_bwd_kernel<VEC, FGL_AGG_SUM><<<grid, kAggThreads, 0, st>>>(p);
-    if (mode == FGL_AGG_MEAN) agg_bwd_kernel<VEC, FGL_AGG_MEAN><<<grid, kAggThreads, 0, st>>>(p);
-    if (mode == FGL_AGG_SYMNORM) agg_bwd_kernel<VEC, FGL_AGG_SYMNORM><<<grid, kAggThreads, 0, st>>>(p);
+    if (mode == FGL_AGG_SUM) launch_bwd_nacc<VEC, FGL_AGG_SUM>(p, grid, st);
+    if (mode == FGL_AGG_MEAN) launch_bwd_nacc<VEC, FGL_AGG_MEAN>(p, grid, st);
+    if (mode == FGL_AGG_SYMNORM) launch_bwd_nacc<VEC, FGL_AGG_SYMNORM>(p, grid, st);
 }
 
 }  // namespace fgl
@@ -224,16 +339,50 @@ int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
     if (n_dst == 0) return FGL_OK;
     if (!indptr || !x || !out) return FGL_ERR_INVALID;
     if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
-    cudaStream_t st = (cudaStream_t)stream;
-    AggParams p{indptr, src, src_deg, dst_deg, row_map, x, out, ldx, ldo, dim, n_dst, 0,
-                (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0};
-    const int grid = agg_grid(n_dst);
-    switch (pick_vec(x, ldx, out, ldo, dim)) {
-        case 4: launch_fwd_mode<4>(mode, p, grid, st); break;
-        case 2: launch_fwd_mode<2>(mode, p, grid, st); break;
-        default: launch_fwd_mode<1>(mode, p, grid, st); break;
-    }
-    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.src_deg = src_deg;
+    p.dst_deg = dst_deg;
+    p.row_map = row_map;
+    p.x = x;
+    p.out = out;
+    p.ldx = ldx;
+    p.ldo = ldo;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
+    return launch_fwd_any(mode, p, dim3(agg_grid_x(n_dst, 1), 1), pick_vec(dim, x, ldx, out, ldo), (cudaStream_t)stream);
+}
+
+int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride, const int32_t* src,
+                       int64_t src_stride, const int32_t* row_map, int64_t row_map_stride, const int64_t* out_row_off,
+                       int64_t total_rows, const float* x, int64_t ldx, int32_t dim, int32_t flags, float* out, int64_t ldo,
+                       float* self_out, int64_t ld_self, void* stream) {
+    if ((mode != FGL_AGG_SUM && mode != FGL_AGG_MEAN) || n_batches < 0 || total_rows < 0 || total_rows > 0x7fffffffLL ||
+        dim < 1 || ldx < dim || ldo < dim || (self_out && ld_self < dim))
+        return FGL_ERR_INVALID;
+    if (n_batches == 0 || total_rows == 0) return FGL_OK;
+    if (!indptr || !src || !out_row_off || !x || !out) return FGL_ERR_INVALID;
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.row_map = row_map;
+    p.x = x;
+    p.out = out;
+    p.self_out = self_out;
+    p.ldx = ldx;
+    p.ldo = ldo;
+    p.ld_self = ld_self;
+    p.dim = dim;
+    p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
+    p.indptr_stride = indptr_stride;
+    p.src_stride = src_stride;
+    p.row_map_stride = row_map_stride;
+    p.n_batches = n_batches;
+    p.out_row_off = out_row_off;
+    const int vec = pick_vec(dim, x, ldx, out, ldo, self_out, self_out ? ld_self : 4);
+    return launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
 }
 
 int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
@@ -249,9 +398,20 @@ int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
     if (n_dst == 0) return FGL_OK;
     if (!indptr || !dy) return FGL_ERR_INVALID;
     if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
-    AggParams p{indptr, src, src_deg, dst_deg, nullptr, dy, dx, ldy, ldx, dim, n_dst, n_src, 0};
-    const int grid = agg_grid(n_dst);
-    switch (pick_vec(dy, ldy, dx, ldx, dim)) {
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.src_deg = src_deg;
+    p.dst_deg = dst_deg;
+    p.x = dy;
+    p.out = dx;
+    p.ldx = ldy;
+    p.ldo = ldx;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.n_src = n_src;
+    const int grid = agg_grid_x(n_dst, 1);
+    switch (pick_vec(dim, dy, ldy, dx, ldx)) {
         case 4: launch_bwd_mode<4>(mode, p, grid, st); break;
         case 2: launch_bwd_mode<2>(mode, p, grid, st); break;
         default: launch_bwd_mode<1>(mode, p, grid, st); break;

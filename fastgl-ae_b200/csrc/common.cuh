@@ -21,6 +21,7 @@ struct Workspace {
     int sm_count = 0;
     unsigned long long* table = nullptr;  // hashtable slots (64 bit each)
     int64_t table_slots = 0;
+    bool table_dirty = true;              // slots may hold keys: clear the whole table before the next fused launch
     char* scratch = nullptr;              // scan partials, barrier words, per-call counters
     int64_t scratch_bytes = 0;
     int32_t* status = nullptr;            // device: [0] first error, [1] abort flag

@@ -70,6 +70,7 @@ struct KParams {
     int32_t table_shift;  // 32 - log2(table_slots)
     unsigned long long* barriers;  // one per team, 16 words apart
     int32_t* team_sums;            // [n_teams][team_size]
+    int32_t* node_pos;             // [n_teams][nodes_stride]: slot of every node, for the clean-up walk
     int32_t* status;               // [0] first error, [1] abort flag
 };
 
@@ -91,22 +92,24 @@ __device__ __forceinline__ unsigned long long ld_slot(const unsigned long long* 
 
 // Seed i gets local id i; of two equal seeds the later position wins, as a sequential run of
 // id_map.cu:259-287 leaves it.
-__device__ __forceinline__ void table_insert_seed(const Table& t, uint32_t key, uint32_t local, int32_t* status) {
+// Returns the slot position, or -1 when the table is full.
+__device__ __forceinline__ int table_insert_seed(const Table& t, uint32_t key, uint32_t local, int32_t* status) {
     const unsigned long long mine = ((unsigned long long)key << 32) | local;
     uint32_t pos = hash_pos(t, key);
     for (uint32_t probe = 0; probe <= t.mask; ++probe) {
         unsigned long long cur = ld_slot(t.slots + pos);
         if (cur == kEmpty) {
             cur = atomicCAS(t.slots + pos, kEmpty, mine);
-            if (cur == kEmpty) return;
+            if (cur == kEmpty) return (int)pos;
         }
         if ((uint32_t)(cur >> 32) == key) {
             atomicMax(t.slots + pos, mine);
-            return;
+            return (int)pos;
         }
         pos = (pos + 1) & t.mask;
     }
     set_status(status, FGL_ERR_PROBE);
+    return -1;
 }
 
 // Returns the local id (>= 0) if the key already has one, else ~pos of its slot (< 0).  created is set
@@ -161,6 +164,7 @@ struct Hop {
     int32_t* blk_indptr;   // may be NULL (MODE_SAMPLE without CSR output)
     int32_t* blk_src;      // edge array: global ids (MODE_SAMPLE) or local ids / ~pos
     int32_t* out_dst;      // MODE_SAMPLE only
+    int32_t* node_pos;     // slot position of every node of the list (fused mode), else NULL
     int hop, fanout, n_seeds;
     uint64_t ctr;
 };
@@ -220,6 +224,7 @@ __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const 
         const uint32_t pos = (uint32_t)~r;
         if ((int64_t)local < h.nodes_cap) {
             h.nodes[local] = g;
+            if (h.node_pos) h.node_pos[local] = (int)pos;
             atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32) | (uint32_t)local);
             r = local;
         } else {
@@ -419,8 +424,8 @@ __device__ __forceinline__ void phase_count_first(const Table& tab, const int32_
 
 // Phase D: local ids in first-occurrence order; returns the new node count.
 __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, const int32_t* edges, int e0, int e1,
-                                          int32_t* nodes, int64_t nodes_cap, int n_before, const Team& t, Smem& sm,
-                                          const int32_t* team_sums) {
+                                          int32_t* nodes, int32_t* node_pos, int64_t nodes_cap, int n_before,
+                                          const Team& t, Smem& sm, const int32_t* team_sums) {
     int before, total;
     team_prefix(team_sums, t, sm, before, total);
     int running = n_before + before;
@@ -441,6 +446,7 @@ __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, co
             const uint32_t key = (uint32_t)(cur >> 32);
             if ((int64_t)local < nodes_cap) {
                 nodes[local] = (int)key;
+                if (node_pos) node_pos[local] = (int)pos;
                 tab.slots[pos] = ((unsigned long long)key << 32) | (uint32_t)local;
             } else {
                 set_status(p.status, FGL_ERR_CAPACITY);
@@ -472,6 +478,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
     extern __shared__ uint32_t picks[];
     const int team_id = blockIdx.x / p.team_size;
     if (team_id >= p.n_teams) return;
+    if (*(volatile int32_t*)(p.status + 1) != 0) return;  // an earlier launch gave up: wait for fgl_ws_check
     Team t;
     t.rank = blockIdx.x % p.team_size;
     t.size = p.team_size;
@@ -495,24 +502,26 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
         const int32_t* seeds = p.seeds + (size_t)b * p.seed_stride;
 
         if (MODE == MODE_FUSED) {
-            // clear the team's table, then insert the seeds with local id = position
-            for (int64_t i = (int64_t)t.rank * kThreads + threadIdx.x; i < p.table_slots; i += (int64_t)t.size * kThreads)
-                tab.slots[i] = kEmpty;
+            // The team's table is empty here: the host cleared it once and every mini-batch removes its own
+            // entries at the end.  Insert the seeds with local id = position and remember their slots.
+            h.node_pos = p.node_pos + (size_t)team_id * p.nodes_stride;
             if (t.rank == 0 && threadIdx.x < FGL_COUNTS_STRIDE) h.counts[threadIdx.x] = threadIdx.x == 0 ? n0 : 0;
-            if (!team_barrier(t, &sm.flag)) return;
             int s0, s1;
             chunk_of(n0, t.rank, t.size, s0, s1);
             for (int s = s0 + (int)threadIdx.x; s < s1; s += kThreads) {
                 const int v = seeds[s];
                 h.nodes[s] = v;
+                int pos = -1;
                 if (v < 0 || (int64_t)v >= p.n_nodes)
                     set_status(p.status, FGL_ERR_BOUNDS);
                 else
-                    table_insert_seed(tab, (uint32_t)v, (uint32_t)s, p.status);
+                    pos = table_insert_seed(tab, (uint32_t)v, (uint32_t)s, p.status);
+                h.node_pos[s] = pos;
             }
             // the same CTA reads nodes[s0..s1) in phase A, so no barrier is needed before it; the
             // barrier after phase A orders the seed inserts before the first source insert
         } else {
+            h.node_pos = nullptr;
             h.nodes = const_cast<int32_t*>(seeds);  // MODE_SAMPLE reads the seeds in place
         }
 
@@ -537,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
             if (!ARRIVAL) {
                 phase_count_first(tab, h.blk_src, e0, e1, t, sm, team_sums);
                 if (!team_barrier(t, &sm.flag)) return;
-                n_cur = phase_rank(p, tab, h.blk_src, e0, e1, h.nodes, h.nodes_cap, n_cur, t, sm, team_sums);
+                n_cur = phase_rank(p, tab, h.blk_src, e0, e1, h.nodes, h.node_pos, h.nodes_cap, n_cur, t, sm, team_sums);
                 n_cur = (int)min((int64_t)n_cur, h.nodes_cap);
                 if (t.rank == 0 && threadIdx.x == 0) h.counts[hop + 1] = n_cur;
                 if (!team_barrier(t, &sm.flag)) return;
@@ -549,7 +558,17 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
             // keeps the next inserts behind every CTA's relabel reads
         }
         if (MODE == MODE_SAMPLE) break;
-        // the table is cleared at the top of the next mini-batch; everyone must be done reading it
+        // Clean-up walk: once every CTA has finished reading the table, empty exactly the slots this
+        // mini-batch filled (16 MB of table stay untouched and L2-resident instead of being rewritten).
+        if (!team_barrier(t, &sm.flag)) return;
+        {
+            int c0, c1;
+            chunk_of(n_cur, t.rank, t.size, c0, c1);
+            for (int i = c0 + (int)threadIdx.x; i < c1; i += kThreads) {
+                const int pos = __ldcg(h.node_pos + i);
+                if (pos >= 0) tab.slots[pos] = kEmpty;
+            }
+        }
         if (b + p.n_teams < p.n_batches) {
             if (!team_barrier(t, &sm.flag)) return;
         }
@@ -634,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant_
     if (!ARRIVAL) {
         phase_count_first(tab, p.map_src, e0, e1, t, sm, team_sums);
         if (!team_barrier(t, &sm.flag)) return;
-        const int n_total = phase_rank(p, tab, p.map_src, e0, e1, unique, h.nodes_cap, n_seeds, t, sm, team_sums);
+        const int n_total = phase_rank(p, tab, p.map_src, e0, e1, unique, nullptr, h.nodes_cap, n_seeds, t, sm, team_sums);
         if (t.rank == 0 && threadIdx.x == 0) p.counts[1] = (int)min((int64_t)n_total, h.nodes_cap);
         if (!team_barrier(t, &sm.flag)) return;
     }
@@ -676,13 +695,19 @@ static int launch_coop(Workspace* ws, K kernel, int grid, size_t dyn_smem, KPara
 }
 
 // scratch layout: [barriers: n_teams * 16 u64][team_sums: n_teams * team_size i32][counts: 16 i32]
-static int64_t scratch_need(int n_teams, int grid) { return (int64_t)n_teams * 128 + (int64_t)grid * 4 + 64 + 256; }
+//                 [node_pos: n_teams * nodes_stride i32]; only the part before node_pos is zeroed per call
+static int64_t scratch_head(int n_teams, int grid) { return (int64_t)n_teams * 128 + (((int64_t)grid * 4 + 127) / 128) * 128 + 128; }
+
+static int64_t scratch_need(int n_teams, int grid, int64_t nodes_stride = 0) {
+    return scratch_head(n_teams, grid) + (int64_t)n_teams * nodes_stride * 4;
+}
 
 static void place_scratch(Workspace* ws, KParams& kp, int n_teams, int grid, int32_t** call_counts) {
     char* base = ws->scratch;
     kp.barriers = (unsigned long long*)base;
     kp.team_sums = (int32_t*)(base + (size_t)n_teams * 128);
-    if (call_counts) *call_counts = (int32_t*)(base + (size_t)n_teams * 128 + (((size_t)grid * 4 + 127) / 128) * 128);
+    if (call_counts) *call_counts = (int32_t*)(base + scratch_head(n_teams, grid) - 128);
+    kp.node_pos = (int32_t*)(base + scratch_head(n_teams, grid));
     kp.status = ws->status;
 }
 
@@ -769,7 +794,7 @@ int fgl_sample(fgl_ws* ws, const void* indptr, int indptr_is_64, const int32_t* 
     kp.table = nullptr;
     kp.table_slots = 1024;
     kp.table_shift = 22;
-    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_need(1, grid), st));
+    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_head(1, grid), st));
     rc = launch_sample_map<MODE_SAMPLE>(ws, kp, indptr_is_64 != 0, false, grid, dyn, st);
     if (rc != FGL_OK) return rc;
     if (n_edges_host) {
@@ -826,8 +851,9 @@ int fgl_map(fgl_ws* ws, int32_t* src, int32_t* dst, const int32_t* seeds, int32_
     kp.table = ws->table;
     kp.table_slots = slots;
     kp.table_shift = 32 - log2_of(slots);
-    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_need(1, grid), st));
+    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_head(1, grid), st));
     FGL_CUDA_OK(ws, cudaMemsetAsync(ws->table, 0xFF, sizeof(unsigned long long) * (size_t)slots, st));
+    ws->table_dirty = true;  // this call leaves its keys in the table
     rc = arrival ? launch_coop(ws, map_kernel<true>, grid, 0, &kp, st) : launch_coop(ws, map_kernel<false>, grid, 0, &kp, st);
     if (rc != FGL_OK) return rc;
     if (n_unique_host) {
@@ -875,10 +901,17 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     n_teams = std::max(1, std::min(std::min(n_teams, (int)a->n_batches), max_grid));
     const int team_size = max_grid / n_teams;
     const int grid = team_size * n_teams;
-    const int64_t slots = pow2_at_least(cap[a->n_hops] + cap[a->n_hops] / 2 + 1);
+    // one table per team: sized for the worst case, or by the caller's hint (a smaller table stays in L2;
+    // if it fills up the launch reports FGL_ERR_PROBE and the caller retries without a hint)
+    int64_t slots = pow2_at_least(cap[a->n_hops] + cap[a->n_hops] / 2 + 1);
+    if (a->table_slots_hint > 0) slots = std::min(slots, pow2_at_least(a->table_slots_hint));
     if (slots > (1LL << 31)) return FGL_ERR_CAPACITY;
-    rc = ws_ensure(ws, slots * n_teams, scratch_need(n_teams, grid));
+    rc = ws_ensure(ws, slots * n_teams, scratch_need(n_teams, grid, a->nodes_stride));
     if (rc != FGL_OK) return rc;
+    if (ws->table_dirty) {
+        FGL_CUDA_OK(ws, cudaMemsetAsync(ws->table, 0xFF, sizeof(unsigned long long) * (size_t)ws->table_slots, st));
+        ws->table_dirty = false;
+    }
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
     place_scratch(ws, kp, n_teams, grid, nullptr);
@@ -908,7 +941,7 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     kp.table = ws->table;
     kp.table_slots = slots;
     kp.table_shift = 32 - log2_of(slots);
-    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_need(n_teams, grid), st));
+    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, (size_t)scratch_head(n_teams, grid), st));
     return launch_sample_map<MODE_FUSED>(ws, kp, is64, arrival, grid, dyn, st);
 }
 

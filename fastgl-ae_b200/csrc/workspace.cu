@@ -27,6 +27,7 @@ int ws_ensure(Workspace* ws, int64_t table_slots, int64_t scratch_bytes) {
             return FGL_ERR_NOMEM;
         }
         ws->table_slots = table_slots;
+        ws->table_dirty = true;
     }
     if (scratch_bytes > ws->scratch_bytes) {
         if (ws->scratch) FGL_CUDA_OK(ws, cudaFree(ws->scratch));
@@ -122,7 +123,10 @@ int fgl_ws_check(fgl_ws* ws, void* stream) {
     FGL_CUDA_OK(ws, cudaMemsetAsync(ws->status, 0, 2 * sizeof(int32_t), st));
     FGL_CUDA_OK(ws, cudaStreamSynchronize(st));
     const int code = ws->host_pinned[0];
-    if (code != FGL_OK) ws->last_error = std::string("device status: ") + fgl_status_str(code);
+    if (code != FGL_OK) {
+        ws->last_error = std::string("device status: ") + fgl_status_str(code);
+        ws->table_dirty = true;  // a failed launch may have left keys behind
+    }
     return code;
 }
 

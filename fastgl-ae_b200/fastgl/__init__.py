@@ -31,7 +31,7 @@ from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRI
 
 __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
-    "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward",
+    "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "set_sampling", "seed", "FusedBatch",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
@@ -290,6 +290,42 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     return out
 
 
+def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=True):
+    """One layer's forward aggregation for every mini-batch of a window in one launch.
+
+    ``fb`` is a ``FusedBatch``; ``hop`` the sampling hop whose block is aggregated (the input layer is hop
+    ``len(fanouts) - 1``).  Batch ``b``'s rows go to ``out[row_off[b] : row_off[b] + n_dst_b]`` where
+    ``row_off`` is the exclusive prefix sum of the batches' destination counts; returns ``row_off`` (a host
+    list with the total appended).  With ``use_row_map`` the rows of ``input_feat`` are addressed through the
+    window's global node ids (aggregation straight from the feature table); ``self_out`` also receives each
+    destination's own input row."""
+    _check_f32(input_feat, "input_feat")
+    _check_f32(out, "out")
+    if self_out is not None:
+        _check_f32(self_out, "self_out")
+    counts = fb.counts_host()
+    n_dst = counts[:, hop].tolist()
+    row_off = [0]
+    for n in n_dst:
+        row_off.append(row_off[-1] + int(n))
+    if out.size(0) < row_off[-1] or (self_out is not None and self_out.size(0) < row_off[-1]):
+        raise RuntimeError("out is too small for the window's destination rows")
+    dev = input_feat.device
+    off_dev = torch.tensor(row_off, dtype=torch.int64).to(dev, non_blocking=True)
+    dim = input_feat.size(1)
+    ptr, src = fb.block_indptr[hop], fb.block_src[hop]
+    with _on_device(dev):
+        rc = lib().fgl_agg_fwd_window(
+            ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
+            ctypes.c_int64(src.stride(0)), _ptr(fb.nodes if use_row_map else None), ctypes.c_int64(fb.nodes.stride(0)),
+            _ptr(off_dev), ctypes.c_int64(row_off[-1]), _ptr(input_feat),
+            ctypes.c_int64(input_feat.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
+            ctypes.c_int64(out.stride(0)), _ptr(self_out), ctypes.c_int64(self_out.stride(0) if self_out is not None else dim),
+            _stream(dev))
+    _raise(rc, "aggregate_window")
+    return row_off
+
+
 def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None):
     """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim]."""
     _check_i32(edge_ptr, "edge_ptr")
@@ -412,7 +448,7 @@ class FusedBatch:
 
 
 def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=None, arrival_order=None,
-                     rng_seed=None, rng_ctr=None, n_teams=0, out: FusedBatch | None = None) -> FusedBatch:
+                     rng_seed=None, rng_ctr=None, n_teams=0, table_slots=0, out: FusedBatch | None = None) -> FusedBatch:
     """All hops of ``seeds.size(0)`` mini-batches in one persistent kernel launch.
 
     ``seeds`` int32[n_batches, seed_stride], ``seed_counts`` int32[n_batches]; ``fanouts`` in sampling
@@ -461,6 +497,7 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
     use_arrival = _config["arrival_order"] if arrival_order is None else arrival_order
     a.flags = (FLAG_SAMPLE_REPLACE if use_replace else 0) | (FLAG_MAP_ARRIVAL_ORDER if use_arrival else 0)
     a.n_teams = int(n_teams)
+    a.table_slots_hint = int(table_slots)
     a.rng_seed = _config["rng_seed"] if rng_seed is None else rng_seed
     a.rng_ctr = _next_ctr() if rng_ctr is None else rng_ctr
     a.seeds = seeds.data_ptr()

@@ -16,13 +16,14 @@ FLAG_MAP_ARRIVAL_ORDER = 2
 FLAG_ZERO_DEG_PASSTHROUGH = 1
 ABI_VERSION = 1
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfastgl_b200.so")
+# FASTGL_B200_LIB points at another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("FASTGL_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfastgl_b200.so")
 
 # every symbol include/fastgl_b200.h declares
 EXPORTS = (
     "fgl_abi_version", "fgl_sizeof_fused_args", "fgl_status_str", "fgl_ws_create", "fgl_ws_destroy", "fgl_ws_reserve", "fgl_last_error",
     "fgl_ws_check", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
-    "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_agg_fwd", "fgl_agg_bwd",
+    "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_agg_fwd", "fgl_agg_fwd_window", "fgl_agg_bwd",
 )
 
 
@@ -38,6 +39,7 @@ class FusedArgs(ctypes.Structure):
         ("fanout", ctypes.c_int32 * MAX_HOPS),
         ("flags", ctypes.c_int32),
         ("n_teams", ctypes.c_int32),
+        ("table_slots_hint", ctypes.c_int64),
         ("rng_seed", ctypes.c_uint64),
         ("rng_ctr", ctypes.c_uint64),
         ("seeds", ctypes.c_void_p),

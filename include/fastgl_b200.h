@@ -106,6 +106,9 @@ typedef struct fgl_fused_args {
     int32_t fanout[FGL_MAX_HOPS];  /* in sampling order: fanout[0] is applied to the seeds */
     int32_t flags;                 /* FGL_SAMPLE_REPLACE | FGL_MAP_ARRIVAL_ORDER */
     int32_t n_teams;               /* mini-batches in flight at once (0 = library default) */
+    int64_t table_slots_hint;      /* 0 = size each team's table for the worst case; else an expected
+                                      number of slots (rounded up to a power of two).  A table that fills up
+                                      makes the launch report FGL_ERR_PROBE. */
     uint64_t rng_seed;
     uint64_t rng_ctr;              /* mini-batch b, hop h draws with counter rng_ctr + b * 8 + h */
     const int32_t* seeds;          /* [n_batches][seed_stride] */
@@ -156,6 +159,21 @@ int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* 
 int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                 const int32_t* dst_deg, const int32_t* row_map, const float* x, int64_t ldx, int32_t dim,
                 int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream);
+
+/* Forward aggregation (FGL_AGG_SUM or FGL_AGG_MEAN) of one layer for a whole window of mini-batches in one
+ * launch, laid out as fgl_sample_map_fused leaves them: batch b's block is indptr + b * indptr_stride,
+ * src + b * src_stride, its row map (may be NULL) row_map + b * row_map_stride.  out_row_off (device,
+ * n_batches + 1 entries) is the exclusive prefix sum of the batches' destination-row counts followed by the
+ * total (= total_rows); batch b's row d lands at out[(out_row_off[b] + d) * ldo].  If self_out is not
+ * NULL, the row's own input row x[row(d)] is copied to self_out[(out_row_off[b] + d) * ld_self] as well
+ * (the "self" operand of a GraphSAGE layer).  Rows are processed in batch-major order so that a batch's
+ * re-read source rows stay in L2.  Used for the first layer, which reads only the feature table and does
+ * not depend on the weights; the reference runs K10 once per mini-batch (GraphConv.py:109) after a CPU
+ * gather of the input rows (train_fastgl.py:161-184). */
+int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride,
+                       const int32_t* src, int64_t src_stride, const int32_t* row_map, int64_t row_map_stride,
+                       const int64_t* out_row_off, int64_t total_rows, const float* x, int64_t ldx, int32_t dim,
+                       int32_t flags, float* out, int64_t ldo, float* self_out, int64_t ld_self, void* stream);
 
 /* Aggregation backward; replaces the scatter kernels K9 / K11
  * (computation_aware_backward_gcn_cuda_kernel aggregate_acc_kernel.cu:468-517 and

@@ -317,6 +317,57 @@ def test_aggregate_forward_backward(fastgl, mode, dim):
     assert rel_err(dx.cpu().numpy(), refb) <= AGG_RTOL
 
 
+@pytest.mark.parametrize("dim", [100, 128, 256])
+def test_aggregate_sampled_block_shapes_with_row_map(fastgl, dim):
+    # in-degrees 0..15 (the sampled-block case) plus a few long rows, both zero-degree conventions
+    rng = np.random.default_rng(dim)
+    n_dst, n_src = 3000, 9000
+    deg = rng.integers(0, 16, size=n_dst)
+    deg[::97] = 40
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    src = rng.integers(0, n_src, size=int(indptr[-1])).astype(np.int32)
+    table = rng.standard_normal((20000, dim)).astype(np.float32)
+    row_map = rng.choice(20000, size=n_src, replace=False).astype(np.int32)
+    for mode in (0, 1):
+        for passthrough in (True, False):
+            out = fastgl.aggregate(mode, to_dev(indptr), to_dev(src), to_dev(table), n_dst, row_map=to_dev(row_map),
+                                   zero_deg_passthrough=passthrough)
+            ref = oc.aggregate_fwd(mode, indptr, src, table, n_dst, zero_deg_passthrough=passthrough, row_map=row_map)
+            assert rel_err(out.cpu().numpy(), ref) <= AGG_RTOL
+    fastgl.check_status()
+
+
+def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph):
+    indptr, indices = graph
+    rng = np.random.default_rng(23)
+    n = len(indptr) - 1
+    feat = rng.standard_normal((n, 100)).astype(np.float32)
+    seeds = rng.choice(n, size=(5, 200), replace=False).astype(np.int32)
+    counts = np.array([200, 200, 7, 0, 200], dtype=np.int32)
+    fan = [5, 10, 15]
+    fb = fastgl.sample_map_fused(to_dev(indptr), to_dev(indices), to_dev(seeds), to_dev(counts), fan, rng_seed=1, rng_ctr=0)
+    d_feat = to_dev(feat)
+    hop = 2
+    total = int(fb.counts_host()[:, hop].sum())
+    for _ in range(1):
+        out = torch.full((total, 100), 7.0, device=dev())
+        self_out = torch.full((total, 100), 7.0, device=dev())
+        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, d_feat, out, self_out=self_out)
+        assert row_off[-1] == total
+        for b in range(5):
+            (ptr, src, n_src, n_dst) = fb.blocks(b)[0]
+            nodes = fb.input_nodes(b).cpu().numpy()
+            ref = oc.aggregate_fwd(oc.MODE_MEAN, ptr.cpu().numpy(), src.cpu().numpy(), feat, n_dst, zero_deg_passthrough=False,
+                                   row_map=nodes)
+            got = out[row_off[b]: row_off[b + 1]].cpu().numpy()
+            assert got.shape == ref.shape
+            if n_dst:
+                assert rel_err(got, ref) <= AGG_RTOL
+                assert np.array_equal(self_out[row_off[b]: row_off[b + 1]].cpu().numpy(), feat[nodes[:n_dst]])
+    fastgl.check_status()
+
+
 def test_aggregate_high_degree_rows_and_row_map(fastgl):
     rng = np.random.default_rng(9)
     n_dst, n_src, dim = 64, 30000, 100
