@@ -274,6 +274,7 @@ def main():
     tr.sampled_edges = 0
     tr.time_layer0 = True
     tr.layer0_events.clear()
+    tr.sample_events.clear()
     counter_at_start = tr.sampler.batch_counter
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -287,21 +288,46 @@ def main():
     value = edges_all / (ms * 1e-3)
     fastgl.check_status(device)
 
-    # --- roofline of the dominant kernel: first-layer mean aggregation straight from the feature table ----
-    agg_ms = [s.elapsed_time(e) for s, e, _ in tr.layer0_events]
+    # --- roofline of the dominant kernel: the window-level first-layer aggregation (mean of neighbours + self
+    #     rows, straight from the feature table), one launch per window, timed by events on the launching stream
     D = cfg["feat_dim"]
-    alg_bytes = []
-    last_window = (args.steps % args.window) or args.window
-    for _, _, blk in tr.layer0_events[-last_window:]:  # the last window's blocks are still in the buffers
-        r_src = int(torch.unique(blk.src).numel())
-        alg_bytes.append(4 * D * (r_src + blk.n_dst) + 4 * blk.num_edges() + 4 * (blk.n_dst + 1) + 4 * r_src)
     peak, peak_kind = load_peaks()
-    mean_agg_ms = statistics.mean(agg_ms) if agg_ms else float("nan")
-    mean_bytes = statistics.mean(alg_bytes) if alg_bytes else 0.0
-    achieved = mean_bytes / (mean_agg_ms * 1e-3) / 1e9 if agg_ms else None
-    roofline = {"kernel": "agg_fwd_kernel<4, MEAN, row_map> (layer 0)", "bound": "hbm", "achieved": achieved, "peak": peak,
-                "peak_kind": peak_kind, "unit": "GB/s", "frac": (achieved / peak) if achieved else None, "traffic": None,
-                "algorithmic_bytes_per_launch": mean_bytes, "launch_ms": mean_agg_ms, "launches_timed": len(agg_ms)}
+    full = [(s.elapsed_time(e), fb) for s, e, fb in tr.layer0_events if fb.n_batches == args.window]
+    agg_ms = [t for t, _ in full]
+    roofline = {"kernel": "agg_fwd_kernel<4, MEAN, row_map> over a window (layer 0)", "bound": "hbm", "achieved": None,
+                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": None, "traffic": None}
+    sample_roofline = None
+    if agg_ms:
+        fb = full[-1][1]  # the last full window is still in the buffers
+        counts_h = fb.counts_host()
+        hop = len(cfg["fanouts"]) - 1
+        alg, sm_bytes = 0, 0
+        deg_all = indptr[1:] - indptr[:-1]
+        fan_s = list(reversed(cfg["fanouts"]))
+        for b in range(fb.n_batches):
+            n_dst, n_edges = int(counts_h[b, hop]), int(counts_h[b, 8 + hop])
+            touched = torch.cat([fb.block_src[hop][b, :n_edges], torch.arange(n_dst, dtype=torch.int32, device=device)])
+            r_all = int(torch.unique(touched).numel())
+            # reads: every distinct feature row once + its id; edge ids and offsets; writes: self and mean rows
+            alg += 4 * D * r_all + 4 * r_all + 4 * n_edges + 4 * (n_dst + 1) + 2 * 4 * D * n_dst
+            nodes = fb.nodes[b].long()
+            for h in range(len(fan_s)):  # sampler: S*40 + sum_seeds min(32*ceil(4*deg/32), 32*k) + 4E + 4U per hop
+                S, E, U = int(counts_h[b, h]), int(counts_h[b, 8 + h]), int(counts_h[b, h + 1]) - int(counts_h[b, h])
+                dg = deg_all[nodes[:S]]
+                k = torch.clamp(dg, max=fan_s[h])
+                sm_bytes += S * 40 + int(torch.minimum(32 * ((4 * dg + 31) // 32), 32 * k).sum()) + 4 * E + 4 * U
+        mean_ms = statistics.mean(agg_ms)
+        achieved = alg / (mean_ms * 1e-3) / 1e9
+        roofline.update({"achieved": achieved, "frac": achieved / peak, "algorithmic_bytes_per_launch": alg,
+                         "launch_ms": mean_ms, "launches_timed": len(agg_ms)})
+        smp = [s.elapsed_time(e) for s, e, nb in tr.sample_events if nb == args.window]
+        if smp:
+            smp_ms = statistics.mean(smp)
+            sample_roofline = {"kernel": "sample_map_kernel (3 hops x window)", "bound": "hbm",
+                               "achieved": sm_bytes / (smp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                               "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
+                               "launch_ms": smp_ms, "launches_timed": len(smp),
+                               "note": "event-timed on the launching stream; includes the host gap before the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
     host_rows, host_counts = [], []
@@ -333,8 +359,10 @@ def main():
 
     if rank == 0:
         steps_per_epoch = tr.steps_per_epoch()
-        # kernels of this library per step: 1/window fused sampling launches + 3 forward + 2 backward aggregations
-        launches = args.steps * (len(cfg["fanouts"]) * 2 - 1) + (args.steps + args.window - 1) // args.window
+        # kernels of this library: per window one fused sampling launch and one first-layer aggregation launch,
+        # per step 2 forward + 2 backward aggregations of the inner layers (the backward ones with a memset)
+        n_windows = (args.steps + args.window - 1) // args.window
+        launches = args.steps * 2 * (len(cfg["fanouts"]) - 1) + 2 * n_windows
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_json,
@@ -342,7 +370,8 @@ def main():
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
                 "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": cfg["batch"] * 4 + 4, "d2h_bytes_per_step": 4 + 64},
-                "gpu_launches": launches * world, "roofline": roofline, "clocks": clock_info}
+                "gpu_launches": launches * world, "roofline": roofline, "roofline_sample_map": sample_roofline,
+                "clocks": clock_info}
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))

@@ -66,6 +66,12 @@ def _check_f32(t: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be float32 (got {t.dtype})")
 
 
+def _check_rows_f32(t: torch.Tensor, name: str) -> None:
+    """A float32 CUDA matrix whose rows are contiguous (a column slice of a wider buffer is fine)."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise RuntimeError(f"{name} must be a float32 CUDA matrix with unit column stride")
+
+
 def _ws(device: torch.device) -> ctypes.c_void_p:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     with _state_lock:
@@ -300,9 +306,9 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     window's global node ids (aggregation straight from the feature table); ``self_out`` also receives each
     destination's own input row."""
     _check_f32(input_feat, "input_feat")
-    _check_f32(out, "out")
+    _check_rows_f32(out, "out")
     if self_out is not None:
-        _check_f32(self_out, "self_out")
+        _check_rows_f32(self_out, "self_out")
     counts = fb.counts_host()
     n_dst = counts[:, hop].tolist()
     row_off = [0]
@@ -314,6 +320,8 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     off_dev = torch.tensor(row_off, dtype=torch.int64).to(dev, non_blocking=True)
     dim = input_feat.size(1)
     ptr, src = fb.block_indptr[hop], fb.block_src[hop]
+    if row_off[-1] == 0:
+        return row_off
     with _on_device(dev):
         rc = lib().fgl_agg_fwd_window(
             ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),

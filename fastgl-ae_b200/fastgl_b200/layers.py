@@ -150,20 +150,24 @@ class MeanAggregate(torch.autograd.Function):
 
 
 class SAGEConv(nn.Module):
+    """h' = [h_dst | mean_{s in N(d)} h_s] W + b, with W = [W_self; W_neigh] stacked so that the layer is one GEMM."""
+
     def __init__(self, input_dim, output_dim):
         super().__init__()
-        self.w_self = nn.Parameter(torch.empty(input_dim, output_dim))
-        self.w_neigh = nn.Parameter(torch.empty(input_dim, output_dim))
+        self.input_dim = input_dim
+        self.weight = nn.Parameter(torch.empty(2 * input_dim, output_dim))
         self.bias = nn.Parameter(torch.zeros(output_dim))
-        gain = math.sqrt(2.0)
-        bound = gain * math.sqrt(6.0 / (input_dim + output_dim))
+        bound = math.sqrt(2.0) * math.sqrt(6.0 / (input_dim + output_dim))
         with torch.no_grad():
-            self.w_self.uniform_(-bound, bound)
-            self.w_neigh.uniform_(-bound, bound)
+            self.weight.uniform_(-bound, bound)
 
-    def forward(self, block, h, row_map=None, timer=None):
+    def forward(self, block, h, row_map=None, timer=None, self_neigh=None):
         """``h``: float32[n_src, in] -- or, with ``row_map`` (the block's global ids), the whole feature table.
+        ``self_neigh``: float32[n_dst, 2*in] already holding [h_dst | mean of neighbours] (the window-level
+        aggregation of the first layer); then ``block`` and ``h`` are not touched.
         ``timer`` (a list) receives (start_event, end_event, block) around the aggregation kernel."""
+        if self_neigh is not None:
+            return torch.addmm(self.bias, self_neigh, self.weight)
         n_dst = block.num_dst_nodes()
         edge_ptr, src_edges = block_csr(block)
         if timer is not None:
@@ -174,7 +178,7 @@ class SAGEConv(nn.Module):
             end.record()
             timer.append((start, end, block))
         h_self = h[:n_dst] if row_map is None else torch.index_select(h, 0, row_map[:n_dst].long())
-        return torch.addmm(self.bias, h_self, self.w_self) + torch.mm(h_neigh, self.w_neigh)
+        return torch.addmm(self.bias, torch.cat([h_self, h_neigh], 1), self.weight)
 
 
 class GraphSAGE(nn.Module):
@@ -187,13 +191,17 @@ class GraphSAGE(nn.Module):
         self.dropout = nn.Dropout(p=dropout)
         self.layer0_timer = None  # set to a list to time the first layer's aggregation kernel
 
-    def forward(self, blocks, features, input_nodes=None):
+    def forward(self, blocks, features, input_nodes=None, layer0=None):
         """``features``: the gathered input rows float32[n_src_0, in]; or, with ``input_nodes`` (int32 global
-        ids of block 0's sources), the full feature table, read in place by the first layer."""
+        ids of block 0's sources), the full feature table, read in place by the first layer; or ``None`` when
+        ``layer0`` = float32[n_dst_0, 2*in] already holds the first layer's [self | neighbour mean] rows."""
         h = features
         for i, layer in enumerate(self.layers):
             if i != 0:
                 h = self.dropout(torch.relu(h))
-            h = layer(blocks[i], h, row_map=input_nodes if i == 0 else None,
-                      timer=self.layer0_timer if i == 0 else None)
+            if i == 0 and layer0 is not None:
+                h = layer(None, None, self_neigh=layer0)
+            else:
+                h = layer(blocks[i], h, row_map=input_nodes if i == 0 else None,
+                          timer=self.layer0_timer if i == 0 else None)
         return h

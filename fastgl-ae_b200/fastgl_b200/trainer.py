@@ -15,6 +15,8 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+import fastgl
+
 from .sampler import FusedMapSampler
 from .scheduler import MatchReorder
 
@@ -54,7 +56,8 @@ class FlatGrads:
 
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
-                 lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0):
+                 lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
+                 window_layer0=True):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -73,8 +76,13 @@ class Trainer:
         self._set_epoch_seeds()
         self.sampled_edges = 0
         self.last_loss = None
-        self.layer0_events = []   # (start, end, n_dst, n_src, E) of the first-layer aggregation, when timed
+        self.layer0_events = []   # (start, end, block | window) of the first-layer aggregation, when timed
+        self.sample_events = []   # (start, end, n_batches) of the fused sampling launches, when timed
         self.time_layer0 = False
+        # The first layer's [self | neighbour-mean] rows do not depend on the weights, so they are produced for
+        # the whole window by one launch straight from the feature table.
+        self.window_layer0 = bool(window_layer0) and hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
+        self._layer0_buf = None
 
     def _set_epoch_seeds(self):
         self.my_seeds = shard_seeds(self.train_nids, self.rank, self.world, 12345 + self.epoch)
@@ -98,12 +106,33 @@ class Trainer:
             rows.append(chunk)
         return torch.stack(rows).contiguous(), torch.tensor(counts, dtype=torch.int32)
 
-    def train_batch(self, fb, b: int, labels_of=None):
+    def aggregate_window_layer0(self, fb):
+        """[self | mean of neighbours] rows of the input layer for every batch of the window: (buffer, row_off)."""
+        hop = len(self.fanouts) - 1
+        D = self.feat.size(1)
+        total = int(fb.counts_host()[:, hop].sum())
+        if self._layer0_buf is None or self._layer0_buf.size(0) < total:
+            self._layer0_buf = torch.empty((int(total * 1.25) + 1, 2 * D), dtype=torch.float32, device=self.dev)
+        buf = self._layer0_buf
+        if self.time_layer0:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, self.feat, buf[:, D:], self_out=buf[:, :D])
+        if self.time_layer0:
+            end.record()
+            self.layer0_events.append((start, end, fb))
+        return buf, row_off
+
+    def train_batch(self, fb, b: int, labels_of=None, layer0=None):
         input_nodes, blocks = self.sampler.window_blocks(fb, b)
         seeds = input_nodes[: blocks[-1].n_dst]
         y = self.labels[seeds.long()] if labels_of is None else labels_of
-        self.model.layer0_timer = self.layer0_events if self.time_layer0 else None
-        logits = self.model(blocks, self.feat, input_nodes=input_nodes)
+        if layer0 is not None:
+            buf, row_off = layer0
+            logits = self.model(blocks, None, layer0=buf[row_off[b]: row_off[b + 1]])
+        else:
+            self.model.layer0_timer = self.layer0_events if self.time_layer0 else None
+            logits = self.model(blocks, self.feat, input_nodes=input_nodes)
         loss = F.cross_entropy(logits, y)
         self.grads.zero()
         loss.backward()
@@ -127,12 +156,19 @@ class Trainer:
             else:
                 seeds, counts = self._next_window_seeds(nb)
                 counts = counts.to(self.dev, non_blocking=True)
+            if self.time_layer0:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
             fb = self.sampler.sample_window(seeds, counts, n_teams=self.n_teams)
+            if self.time_layer0:
+                end.record()
+                self.sample_events.append((start, end, nb))
+            layer0 = self.aggregate_window_layer0(fb) if self.window_layer0 else None
             order = list(range(nb))
             if self.matcher is not None:
                 order = self.matcher.reorder([fb.input_nodes(b) for b in range(nb)])
             for b in order:
-                loss = self.train_batch(fb, b)
+                loss = self.train_batch(fb, b, layer0=layer0)
                 if read_loss_each_step:
                     losses.append(float(loss.item()))
             done += nb
