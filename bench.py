@@ -192,6 +192,10 @@ def main():
     ap.add_argument("--window", type=int, default=8, help="mini-batches sampled per kernel launch")
     ap.add_argument("--teams", type=int, default=0)
     ap.add_argument("--reorder", action="store_true", help="Match-Reorder each window")
+    ap.add_argument("--matmul", default="fp32", choices=["fp32", "tf32"],
+                    help="arithmetic of the dense-layer GEMMs that stay in PyTorch (tf32 is what the reference's "
+                         "pinned PyTorch 1.10.1 used by default on Ampere)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the per-batch step op by op instead of a CUDA graph")
     ap.add_argument("--cpu-steps", type=int, default=3, help="mini-batches of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -239,11 +243,12 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     torch.manual_seed(12345)
+    torch.backends.cuda.matmul.allow_tf32 = args.matmul == "tf32"
     indptr, indices, feat, labels, train = build_inputs(cfg, device)
     model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
-                 reorder=args.reorder, rank=rank, world=world, n_teams=args.teams)
+                 reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph)
 
     def barrier():
         if world > 1:
@@ -368,6 +373,7 @@ def main():
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_json,
                 "per_gpu_value": value / world, "epoch_time_s": steps_per_epoch * ms / args.steps * 1e-3,
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
+                "dense_matmul": args.matmul, "cuda_graph": not args.no_graph, "graph_fallback_steps": tr.graph_fallbacks,
                 "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": cfg["batch"] * 4 + 4, "d2h_bytes_per_step": 4 + 64},
                 "gpu_launches": launches * world, "roofline": roofline, "roofline_sample_map": sample_roofline,

@@ -78,6 +78,9 @@ struct AggParams {
     int64_t indptr_stride, src_stride, row_map_stride;
     int32_t n_batches;
     const int64_t* out_row_off;  // [n_batches + 1]: first output row of batch b, then the total
+    // optional: the real number of destination rows, read on the device (n_dst is then the padded row count
+    // the launch is sized for; forward rows beyond the real count are zero-filled)
+    const int32_t* n_dst_dev;
 };
 
 // Forward: out[d,:] = scale_d * sum_e w_e * x[row(src[e]),:]
@@ -94,7 +97,13 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
     const int n_warps = gridDim.x * kAggWarps;
     const int chunks = p.dim / VEC;  // dim % VEC == 0 by dispatch
     const bool window = p.out_row_off != nullptr;
-    const int64_t total = window ? __ldg(p.out_row_off + p.n_batches) : (int64_t)p.n_dst;
+    const int64_t padded = window ? __ldg(p.out_row_off + p.n_batches) : (int64_t)p.n_dst;
+    const int64_t total = p.n_dst_dev ? min((int64_t)max(__ldg(p.n_dst_dev), 0), padded) : padded;
+    // padding rows of a launch sized for more rows than the block has: zero them
+    for (int64_t g = total + warp_global; g < padded; g += n_warps) {
+        T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
+        for (int c = lane; c < chunks; c += 32) orow[c] = V::zero();
+    }
 
     // State of the row after the current one.  Its ids are fetched one row ahead so that the dependent chain
     // indptr -> src -> row_map is off the critical path.
@@ -214,7 +223,8 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
     const int n_warps = gridDim.x * kAggWarps;
     const int chunks = p.dim / VEC;
 
-    for (int d = warp_global; d < p.n_dst; d += n_warps) {
+    const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
+    for (int d = warp_global; d < n_dst; d += n_warps) {
         const int a = __ldg(p.indptr + d), b = __ldg(p.indptr + d + 1);
         if (a >= b) continue;  // aggregate_acc_kernel.cu:498-500, :580-582
         float scale = 1.0f;
@@ -334,7 +344,7 @@ extern "C" {
 
 int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
                 const int32_t* row_map, const float* x, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags,
-                float* out, int64_t ldo, void* stream) {
+                float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream) {
     if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || dim < 1 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
     if (n_dst == 0) return FGL_OK;
     if (!indptr || !x || !out) return FGL_ERR_INVALID;
@@ -351,6 +361,7 @@ int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
     p.ldo = ldo;
     p.dim = dim;
     p.n_dst = n_dst;
+    p.n_dst_dev = n_dst_dev;
     p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
     return launch_fwd_any(mode, p, dim3(agg_grid_x(n_dst, 1), 1), pick_vec(dim, x, ldx, out, ldo), (cudaStream_t)stream);
 }
@@ -387,7 +398,7 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
 
 int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
                 const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
-                void* stream) {
+                const int32_t* n_dst_dev, void* stream) {
     if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || n_src < 0 || dim < 1 || ldy < dim || ldx < dim)
         return FGL_ERR_INVALID;
     if (n_src == 0) return FGL_OK;
@@ -410,6 +421,7 @@ int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
     p.dim = dim;
     p.n_dst = n_dst;
     p.n_src = n_src;
+    p.n_dst_dev = n_dst_dev;
     const int grid = agg_grid_x(n_dst, 1);
     switch (pick_vec(dim, dy, ldy, dx, ldx)) {
         case 4: launch_bwd_mode<4>(mode, p, grid, st); break;

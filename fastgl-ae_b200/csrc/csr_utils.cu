@@ -78,6 +78,41 @@ __global__ void __launch_bounds__(kScanThreads) exclusive_sum_kernel(const int32
     }
 }
 
+// Up to FGL_MAX_SEGMENTS device-to-device copies and a few int32 words in one launch: stages one mini-batch's
+// blocks into the fixed buffers a captured CUDA graph reads, without one cudaMemcpyAsync per piece.
+struct StageParams {
+    fgl_segment seg[FGL_MAX_SEGMENTS];
+    int64_t first_block[FGL_MAX_SEGMENTS + 1];  // CTA range of every segment
+    int32_t n_segs;
+    int32_t* words_dst;
+    int32_t words[FGL_MAX_SEGMENTS];
+    int32_t n_words;
+};
+
+constexpr int kStageThreads = 256;
+constexpr int64_t kStageBytesPerBlock = kStageThreads * 16 * 8;  // 32 KB per CTA
+
+__global__ void __launch_bounds__(kStageThreads) stage_segments_kernel(const __grid_constant__ StageParams p) {
+    if (blockIdx.x == 0 && threadIdx.x < p.n_words) p.words_dst[threadIdx.x] = p.words[threadIdx.x];
+    int s = 0;
+    while (s + 1 < p.n_segs && (int64_t)blockIdx.x >= p.first_block[s + 1]) ++s;
+    if (s >= p.n_segs) return;
+    const int64_t lo = ((int64_t)blockIdx.x - p.first_block[s]) * kStageBytesPerBlock;
+    const int64_t hi = lo + kStageBytesPerBlock < p.seg[s].bytes ? lo + kStageBytesPerBlock : p.seg[s].bytes;
+    char* dst = static_cast<char*>(p.seg[s].dst);
+    const char* src = static_cast<const char*>(p.seg[s].src);
+    if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+        const int64_t v_hi = lo + ((hi - lo) / 16) * 16;
+        for (int64_t o = lo + (int64_t)threadIdx.x * 16; o < v_hi; o += kStageThreads * 16)
+            *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
+        for (int64_t o = v_hi + (int64_t)threadIdx.x * 4; o < hi; o += kStageThreads * 4)
+            *reinterpret_cast<uint32_t*>(dst + o) = *reinterpret_cast<const uint32_t*>(src + o);
+    } else {
+        for (int64_t o = lo + (int64_t)threadIdx.x * 4; o < hi; o += kStageThreads * 4)
+            *reinterpret_cast<uint32_t*>(dst + o) = *reinterpret_cast<const uint32_t*>(src + o);
+    }
+}
+
 }  // namespace fgl
 
 using namespace fgl;
@@ -91,6 +126,33 @@ int fgl_cal_deg(const int32_t* ids, int64_t n_ids, int32_t* deg, int32_t n_nodes
     if (n_ids == 0 || n_nodes == 0) return FGL_OK;
     const int grid = (int)std::min<int64_t>((n_ids + 255) / 256, 148 * 16);
     cal_deg_kernel<<<grid, 256, 0, st>>>(ids, n_ids, deg, n_nodes);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_stage_segments(const fgl_segment* segs, int32_t n_segs, int32_t* words_dst, const int32_t* words, int32_t n_words,
+                       void* stream) {
+    if (n_segs < 0 || n_segs > FGL_MAX_SEGMENTS || n_words < 0 || n_words > FGL_MAX_SEGMENTS || (n_segs > 0 && !segs) ||
+        (n_words > 0 && (!words || !words_dst)))
+        return FGL_ERR_INVALID;
+    StageParams p;
+    std::memset(&p, 0, sizeof(p));
+    int64_t blocks = 0;
+    for (int i = 0; i < n_segs; ++i) {
+        if (segs[i].bytes < 0 || segs[i].bytes % 4 != 0 || (segs[i].bytes > 0 && (!segs[i].dst || !segs[i].src)) ||
+            ((uintptr_t)segs[i].dst & 3) || ((uintptr_t)segs[i].src & 3))
+            return FGL_ERR_INVALID;
+        p.seg[i] = segs[i];
+        p.first_block[i] = blocks;
+        blocks += (segs[i].bytes + kStageBytesPerBlock - 1) / kStageBytesPerBlock;
+    }
+    for (int i = n_segs; i <= FGL_MAX_SEGMENTS; ++i) p.first_block[i] = blocks;
+    p.n_segs = n_segs;
+    p.words_dst = words_dst;
+    for (int i = 0; i < n_words; ++i) p.words[i] = words[i];
+    p.n_words = n_words;
+    if (blocks == 0) blocks = 1;
+    if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
+    stage_segments_kernel<<<(unsigned)blocks, kStageThreads, 0, (cudaStream_t)stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

@@ -32,7 +32,7 @@ from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRI
 __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
-    "sample_map_fused", "fused_capacity", "set_sampling", "seed", "FusedBatch",
+    "sample_map_fused", "fused_capacity", "stage_segments", "set_sampling", "seed", "FusedBatch",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -266,9 +266,11 @@ def exclusive_sum_noalloc(in_degs, out):
 # a4-a7  aggregation
 # ------------------------------------------------------------------------------------------------
 def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=None, dst_norm_degs=None,
-              zero_deg_passthrough=True, row_map=None, out=None):
+              zero_deg_passthrough=True, row_map=None, out=None, n_dst_dev=None):
     """out[d] = sum over the row's edges of w * input_feat[row(src)], w by ``mode`` (AGG_SUM | AGG_MEAN |
-    AGG_SYMNORM); ``row_map`` (int32) turns block-local ids into rows of ``input_feat``."""
+    AGG_SYMNORM); ``row_map`` (int32) turns block-local ids into rows of ``input_feat``.  ``n_dst_dev`` (int32
+    CUDA tensor, optional) holds the real row count on the device; ``dst_nodes`` is then the padded count the
+    output is sized for (used to replay a captured CUDA graph on blocks of different sizes)."""
     _check_i32(edge_ptr, "edge_ptr")
     _check_i32(src_edges, "src_edges")
     _check_f32(input_feat, "input_feat")
@@ -291,7 +293,7 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
                                _ptr(dst_norm_degs), _ptr(row_map), _ptr(input_feat), ctypes.c_int64(input_feat.stride(0)),
                                ctypes.c_int32(dim), ctypes.c_int32(n_dst),
                                ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH if zero_deg_passthrough else 0), _ptr(out),
-                               ctypes.c_int64(out.stride(0)), _stream(dev))
+                               ctypes.c_int64(out.stride(0)), _ptr(n_dst_dev), _stream(dev))
     _raise(rc, "aggregate")
     return out
 
@@ -334,8 +336,10 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     return row_off
 
 
-def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None):
-    """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim]."""
+def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None,
+                       n_dst_dev=None):
+    """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim].  ``n_dst_dev`` as in
+    ``aggregate``."""
     _check_i32(edge_ptr, "edge_ptr")
     _check_i32(src_edges, "src_edges")
     _check_f32(d_out, "d_input")
@@ -349,7 +353,7 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
         rc = lib().fgl_agg_bwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
                                _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), ctypes.c_int32(dim),
                                ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
-                               ctypes.c_int64(d_x.stride(0)), _stream(dev))
+                               ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
     _raise(rc, "aggregate_backward")
     return d_x
 
@@ -518,6 +522,31 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
     rc = lib().fgl_sample_map_fused(ws, ctypes.byref(a), _stream(dev))
     _raise(rc, "sample_map_fused", ws)
     return out
+
+
+def stage_segments(copies, words_dst=None, words=()):
+    """``copies``: up to 8 ``(dst, src)`` pairs of CUDA tensors (``src.numel()`` elements of a 4-byte dtype are
+    copied to the front of ``dst``); ``words`` (up to 8 ints) are written to the int32 tensor ``words_dst``.
+    One kernel launch on the current stream."""
+    n = len(copies)
+    if n > _capi.MAX_SEGMENTS or len(words) > _capi.MAX_SEGMENTS:
+        raise RuntimeError("at most 8 copies and 8 words per call")
+    segs = (_capi.Segment * max(1, n))()
+    dev = None
+    for i, (dst, src) in enumerate(copies):
+        if dst.element_size() != 4 or src.element_size() != 4 or not dst.is_cuda or not src.is_cuda:
+            raise RuntimeError("stage_segments copies 4-byte CUDA tensors")
+        if dst.numel() < src.numel() or not src.is_contiguous() or not dst.is_contiguous():
+            raise RuntimeError("stage_segments needs contiguous tensors and a destination at least as large as the source")
+        segs[i].dst, segs[i].src, segs[i].bytes = dst.data_ptr(), src.data_ptr(), src.numel() * 4
+        dev = dst.device
+    if words_dst is not None:
+        _check_i32(words_dst, "words_dst")
+        dev = words_dst.device
+    vals = (ctypes.c_int32 * max(1, len(words)))(*[int(w) for w in words])
+    with _on_device(dev):
+        rc = lib().fgl_stage_segments(segs, ctypes.c_int32(n), _ptr(words_dst), vals, ctypes.c_int32(len(words)), _stream(dev))
+    _raise(rc, "stage_segments")
 
 
 def check_status(device=None) -> None:

@@ -14,7 +14,7 @@ AGG_SUM, AGG_MEAN, AGG_SYMNORM = 0, 1, 2
 FLAG_SAMPLE_REPLACE = 1
 FLAG_MAP_ARRIVAL_ORDER = 2
 FLAG_ZERO_DEG_PASSTHROUGH = 1
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # FASTGL_B200_LIB points at another build of the same library (kernel experiments)
 LIB_PATH = os.environ.get("FASTGL_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libfastgl_b200.so")
@@ -23,7 +23,7 @@ LIB_PATH = os.environ.get("FASTGL_B200_LIB") or os.path.join(os.path.dirname(os.
 EXPORTS = (
     "fgl_abi_version", "fgl_sizeof_fused_args", "fgl_status_str", "fgl_ws_create", "fgl_ws_destroy", "fgl_ws_reserve", "fgl_last_error",
     "fgl_ws_check", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
-    "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_agg_fwd", "fgl_agg_fwd_window", "fgl_agg_bwd",
+    "fgl_stage_segments", "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_agg_fwd", "fgl_agg_fwd_window", "fgl_agg_bwd",
 )
 
 
@@ -54,6 +54,13 @@ class FusedArgs(ctypes.Structure):
         ("block_src_stride", ctypes.c_int64 * MAX_HOPS),
     ]
 
+
+class Segment(ctypes.Structure):
+    """struct fgl_segment"""
+    _fields_ = [("dst", ctypes.c_void_p), ("src", ctypes.c_void_p), ("bytes", ctypes.c_int64)]
+
+
+MAX_SEGMENTS = 8
 
 _lib = None
 

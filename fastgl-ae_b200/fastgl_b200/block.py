@@ -12,14 +12,18 @@ import torch
 
 
 class Block:
-    __slots__ = ("indptr", "src", "n_src", "n_dst", "_dst")
+    __slots__ = ("indptr", "src", "n_src", "n_dst", "_dst", "n_dst_dev")
 
-    def __init__(self, indptr: torch.Tensor, src: torch.Tensor, n_src: int, n_dst: int, dst: torch.Tensor | None = None):
+    def __init__(self, indptr: torch.Tensor, src: torch.Tensor, n_src: int, n_dst: int, dst: torch.Tensor | None = None,
+                 n_dst_dev: torch.Tensor | None = None):
         self.indptr = indptr
         self.src = src
         self.n_src = int(n_src)
         self.n_dst = int(n_dst)
         self._dst = dst
+        # Optional int32[1] CUDA tensor with the real destination count; n_dst / n_src are then padded sizes
+        # (a block of fixed shape that a captured CUDA graph re-reads for every mini-batch).
+        self.n_dst_dev = n_dst_dev
 
     def num_src_nodes(self) -> int:
         return self.n_src

@@ -132,11 +132,13 @@ class MeanAggregate(torch.autograd.Function):
     """mean over in-neighbours (rows without in-edges give zeros); optional row map into a feature table."""
 
     @staticmethod
-    def forward(ctx, x, edge_ptr, src_edges, n_dst, row_map):
+    def forward(ctx, x, edge_ptr, src_edges, n_dst, row_map, n_dst_dev=None):
         ctx.save_for_backward(edge_ptr, src_edges)
         ctx.n_src = x.size(0)
         ctx.mapped = row_map is not None
-        return fastgl.aggregate(fastgl.AGG_MEAN, edge_ptr, src_edges, x, n_dst, zero_deg_passthrough=False, row_map=row_map)
+        ctx.n_dst_dev = n_dst_dev
+        return fastgl.aggregate(fastgl.AGG_MEAN, edge_ptr, src_edges, x, n_dst, zero_deg_passthrough=False, row_map=row_map,
+                                n_dst_dev=n_dst_dev)
 
     @staticmethod
     def backward(ctx, d_out):
@@ -145,8 +147,39 @@ class MeanAggregate(torch.autograd.Function):
             if ctx.mapped:
                 raise RuntimeError("no gradient flows into a feature table that is aggregated through a row map")
             edge_ptr, src_edges = ctx.saved_tensors
-            d_x = fastgl.aggregate_backward(fastgl.AGG_MEAN, edge_ptr, src_edges, d_out.contiguous(), ctx.n_src)
-        return d_x, None, None, None, None
+            d_x = fastgl.aggregate_backward(fastgl.AGG_MEAN, edge_ptr, src_edges, d_out.contiguous(), ctx.n_src,
+                                            n_dst_dev=ctx.n_dst_dev)
+        return d_x, None, None, None, None, None
+
+
+class _TallLinear(torch.autograd.Function):
+    """x W + b for a tall x (tens of thousands of rows, a few hundred columns).
+
+    The weight gradient x^T dy has a tiny output and a very long reduction; as one GEMM it runs on a handful
+    of CTAs.  Here the rows are split into S slabs, a batched GEMM produces S partial products on S times as
+    many CTAs, and the partials are summed; the bias gradient is reduced in the same two stages."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        return torch.addmm(bias, x, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.mm(dy, weight.t()) if ctx.needs_input_grad[0] else None
+        n = x.size(0)
+        slabs = next((s for s in (32, 16, 8) if n % s == 0 and n // s >= 512), 0)
+        if slabs and x.is_contiguous():
+            xs = x.view(slabs, n // slabs, x.size(1))
+            dys = dy.view(slabs, n // slabs, dy.size(1))
+            dw = torch.bmm(xs.transpose(1, 2), dys).sum(0)
+            db = dys.sum(1).sum(0)
+        else:
+            dw = torch.mm(x.t(), dy)
+            db = dy.sum(0)
+        return dx, dw, db
 
 
 class SAGEConv(nn.Module):
@@ -167,18 +200,18 @@ class SAGEConv(nn.Module):
         aggregation of the first layer); then ``block`` and ``h`` are not touched.
         ``timer`` (a list) receives (start_event, end_event, block) around the aggregation kernel."""
         if self_neigh is not None:
-            return torch.addmm(self.bias, self_neigh, self.weight)
+            return _TallLinear.apply(self_neigh, self.weight, self.bias)
         n_dst = block.num_dst_nodes()
         edge_ptr, src_edges = block_csr(block)
         if timer is not None:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-        h_neigh = MeanAggregate.apply(h, edge_ptr, src_edges, n_dst, row_map)
+        h_neigh = MeanAggregate.apply(h, edge_ptr, src_edges, n_dst, row_map, getattr(block, "n_dst_dev", None))
         if timer is not None:
             end.record()
             timer.append((start, end, block))
         h_self = h[:n_dst] if row_map is None else torch.index_select(h, 0, row_map[:n_dst].long())
-        return torch.addmm(self.bias, torch.cat([h_self, h_neigh], 1), self.weight)
+        return _TallLinear.apply(torch.cat([h_self, h_neigh], 1), self.weight, self.bias)
 
 
 class GraphSAGE(nn.Module):

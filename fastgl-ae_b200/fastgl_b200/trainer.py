@@ -17,6 +17,7 @@ import torch.nn.functional as F
 
 import fastgl
 
+from .block import Block
 from .sampler import FusedMapSampler
 from .scheduler import MatchReorder
 
@@ -54,10 +55,93 @@ class FlatGrads:
             self.buffer.div_(world)
 
 
+class GraphedStep:
+    """The per-mini-batch part of a training step -- inner layers forward, loss, backward and (single GPU) the
+    optimizer step -- captured once as a CUDA graph over buffers of fixed, padded shape and replayed for every
+    mini-batch.  A staging kernel copies the batch's first-layer rows and inner blocks into those buffers and
+    writes the real row counts, which the aggregation kernels read on the device.  This removes the ~60 host
+    launches per step that otherwise bound the step time (the reference even blocks on an event three times
+    per step, train_fastgl.py:348,362,373)."""
+
+    def __init__(self, trainer, pad_dst):
+        self.tr = trainer
+        tr = trainer
+        dev, D = tr.dev, tr.feat.size(1)
+        L = len(tr.fanouts)
+        self.L = L
+        self.pad_dst = list(pad_dst)            # padded destination count of block i (input layer first)
+        assert len(self.pad_dst) == L and self.pad_dst[-1] == tr.batch_size
+        self.x0 = torch.zeros((self.pad_dst[0], 2 * D), dtype=torch.float32, device=dev)
+        self.sizes = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.seeds = torch.zeros(tr.batch_size, dtype=torch.int32, device=dev)
+        self.blocks = [None]
+        for i in range(1, L):
+            ptr = torch.zeros(self.pad_dst[i] + 1, dtype=torch.int32, device=dev)
+            src = torch.zeros(self.pad_dst[i] * tr.fanouts[i], dtype=torch.int32, device=dev)
+            self.blocks.append(Block(ptr, src, self.pad_dst[i - 1], self.pad_dst[i], n_dst_dev=self.sizes[i: i + 1]))
+        self.graph = None
+        self.loss = None
+        self.step_in_graph = tr.world == 1
+
+    def fits(self, counts_row) -> bool:
+        L = self.L
+        if int(counts_row[0]) != self.tr.batch_size:
+            return False
+        return all(int(counts_row[L - 1 - i]) <= self.pad_dst[i] for i in range(L))
+
+    def stage(self, fb, b, counts_row, layer0):
+        """Copy mini-batch ``b`` of the window into the static buffers (one kernel launch)."""
+        L = self.L
+        buf, row_off = layer0
+        n_dst = [int(counts_row[L - 1 - i]) for i in range(L)]
+        copies = [(self.x0, buf[row_off[b]: row_off[b] + n_dst[0]]), (self.seeds, fb.nodes[b, : self.tr.batch_size])]
+        for i in range(1, L):
+            h = L - 1 - i
+            copies.append((self.blocks[i].indptr, fb.block_indptr[h][b, : n_dst[i] + 1]))
+            copies.append((self.blocks[i].src, fb.block_src[h][b, : int(counts_row[8 + h])]))
+        fastgl.stage_segments(copies, self.sizes, n_dst)
+
+    def _body(self):
+        tr = self.tr
+        y = tr.labels[self.seeds.long()]
+        logits = tr.model(self.blocks, None, layer0=self.x0)
+        loss = F.cross_entropy(logits, y)
+        tr.grads.zero()
+        loss.backward()
+        if self.step_in_graph:
+            tr.opt.step()
+        return loss
+
+    def capture(self):
+        """Warm up on a side stream (restoring model and optimizer afterwards) and capture the step."""
+        tr = self.tr
+        model_state = {k: v.clone() for k, v in tr.model.state_dict().items()}
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        # undo the warm-up steps in place: the graph must capture the very tensors the optimizer will keep using
+        tr.model.load_state_dict(model_state)
+        tr.zero_optimizer_state()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._body()
+
+    def replay(self):
+        self.graph.replay()
+        if not self.step_in_graph:
+            self.tr.grads.all_reduce(self.tr.world)
+            self.tr.opt.step()
+        return self.loss
+
+
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
                  lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
-                 window_layer0=True):
+                 window_layer0=True, cuda_graph=False):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -70,7 +154,11 @@ class Trainer:
         self.sampler.edge_src, self.sampler.edge_ptr, self.sampler.nodes_num = indices, indptr, self.n_nodes
         self.matcher = MatchReorder(self.n_nodes) if reorder else None
         self.grads = FlatGrads(model.parameters())
-        self.opt = torch.optim.Adam(model.parameters(), lr=lr, weight_decay=weight_decay, fused=True)
+        self.lr, self.weight_decay = lr, weight_decay
+        self.use_graph = bool(cuda_graph)
+        self.graphed = None
+        self.graph_fallbacks = 0
+        self.reset_optimizer()
         self.train_nids = train_nids
         self.epoch = 0
         self._set_epoch_seeds()
@@ -83,6 +171,36 @@ class Trainer:
         # the whole window by one launch straight from the feature table.
         self.window_layer0 = bool(window_layer0) and hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
         self._layer0_buf = None
+
+    def reset_optimizer(self):
+        self.opt = torch.optim.Adam(self.model.parameters(), lr=self.lr, weight_decay=self.weight_decay, fused=True,
+                                    capturable=self.use_graph)
+
+    def zero_optimizer_state(self):
+        for state in self.opt.state.values():
+            for v in state.values():
+                if torch.is_tensor(v):
+                    v.zero_()
+
+    def _graph_step(self, fb, b, layer0):
+        """Replay the captured step for batch ``b``; returns None when the batch does not fit the padded shapes."""
+        counts_row = fb.counts_host()[b]
+        L = len(self.fanouts)
+        if self.graphed is None:
+            if int(counts_row[0]) != self.batch_size:
+                return None
+            pad = []
+            for i in range(L):
+                n = int(fb.counts_host()[:, L - 1 - i].max())
+                pad.append(self.batch_size if i == L - 1 else ((int(n * 1.12) + 255) // 256) * 256)
+            self.graphed = GraphedStep(self, pad)
+            self.graphed.stage(fb, b, counts_row, layer0)
+            self.graphed.capture()
+        if not self.graphed.fits(counts_row):
+            self.graph_fallbacks += 1
+            return None
+        self.graphed.stage(fb, b, counts_row, layer0)
+        return self.graphed.replay()
 
     def _set_epoch_seeds(self):
         self.my_seeds = shard_seeds(self.train_nids, self.rank, self.world, 12345 + self.epoch)
@@ -124,6 +242,13 @@ class Trainer:
         return buf, row_off
 
     def train_batch(self, fb, b: int, labels_of=None, layer0=None):
+        if self.use_graph and layer0 is not None and labels_of is None:
+            loss = self._graph_step(fb, b, layer0)
+            if loss is not None:
+                c = fb.counts_host()[b]
+                self.sampled_edges += int(c[8: 8 + len(self.fanouts)].sum())
+                self.last_loss = loss
+                return loss
         input_nodes, blocks = self.sampler.window_blocks(fb, b)
         seeds = input_nodes[: blocks[-1].n_dst]
         y = self.labels[seeds.long()] if labels_of is None else labels_of

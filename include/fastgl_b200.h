@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define FGL_ABI_VERSION 1
+#define FGL_ABI_VERSION 2
 
 /* status codes */
 #define FGL_OK 0
@@ -134,6 +134,19 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* args, void* stream);
  * deg[0 .. n_nodes) is zeroed and then counts the occurrences of each id. */
 int fgl_cal_deg(const int32_t* ids, int64_t n_ids, int32_t* deg, int32_t n_nodes, void* stream);
 
+/* Stages one mini-batch into fixed buffers: up to FGL_MAX_SEGMENTS device-to-device copies (sizes and
+ * addresses multiples of 4 bytes) and up to FGL_MAX_SEGMENTS int32 words written to words_dst, in one kernel
+ * launch.  No counterpart in the reference; it feeds the static inputs of a captured CUDA graph (block CSR
+ * arrays, first-layer rows, row counts) without one cudaMemcpyAsync per piece. */
+#define FGL_MAX_SEGMENTS 8
+typedef struct fgl_segment {
+    void* dst;
+    const void* src;
+    int64_t bytes;
+} fgl_segment;
+int fgl_stage_segments(const fgl_segment* segs, int32_t n_segs, int32_t* words_dst, const int32_t* words,
+                       int32_t n_words, void* stream);
+
 /* Exclusive scan with the total appended; replaces exclusive_sum_cuda (utilis.cu:17-41; binding
  * aggregate_acc.cpp:514-520).  out has n + 1 entries. */
 int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream);
@@ -155,10 +168,13 @@ int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* 
  * computation_aware_forward_gin_cuda_kernel :376-427).  out[d, 0..dim) = sum over e in
  * [indptr[d], indptr[d+1]) of w * x[row(src[e]), 0..dim), with w by mode and row(i) = row_map[i] if
  * row_map is not NULL (aggregation straight from a feature table by global id) else i.  src_deg /
- * dst_deg are only read in FGL_AGG_SYMNORM. */
+ * dst_deg are only read in FGL_AGG_SYMNORM.
+ * n_dst_dev (may be NULL) points at the real row count in device memory; n_dst is then the padded count the
+ * launch is sized for (rows beyond the real count are zero-filled), which lets a captured CUDA graph be
+ * replayed on blocks of different sizes. */
 int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                 const int32_t* dst_deg, const int32_t* row_map, const float* x, int64_t ldx, int32_t dim,
-                int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream);
+                int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream);
 
 /* Forward aggregation (FGL_AGG_SUM or FGL_AGG_MEAN) of one layer for a whole window of mini-batches in one
  * launch, laid out as fgl_sample_map_fused leaves them: batch b's block is indptr + b * indptr_stride,
@@ -179,10 +195,11 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
  * (computation_aware_backward_gcn_cuda_kernel aggregate_acc_kernel.cu:468-517 and
  * computation_aware_backward_gin_cuda_kernel :555-596).  dx[0 .. n_src) is zeroed, then
  * dx[src[e], :] += w * dy[d, :] for every edge e of row d.  Rows without in-edges contribute nothing
- * (as the reference, :498-500, :580-582). */
+ * (as the reference, :498-500, :580-582).  n_dst_dev as in fgl_agg_fwd (n_src is never read from the
+ * device: dx is zero-filled over all n_src rows). */
 int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                 const int32_t* dst_deg, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst,
-                int32_t n_src, float* dx, int64_t ldx, void* stream);
+                int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,103 @@
+"""GPU tests of the training loop around the kernels: the windowed sampler path equals the per-op path, the
+loss of the CUDA path tracks a float64 CPU restatement of the same GraphSAGE-mean model built on the oracle,
+and the CUDA-graph step reproduces the op-by-op step."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import make_graph
+from oracle import oracle_c as oc
+
+pytestmark = pytest.mark.gpu
+
+
+def setup_problem(n=6000, feat_dim=100, classes=7, seed=5):
+    indptr, indices = make_graph(n, 14, seed=seed, hub=400)
+    rng = np.random.default_rng(seed)
+    feat = rng.standard_normal((n, feat_dim)).astype(np.float32)
+    labels = rng.integers(0, classes, n)
+    train = np.sort(rng.choice(n, size=n // 2, replace=False)).astype(np.int32)
+    return indptr, indices, feat, labels, train
+
+
+def make_trainer(problem, cuda_graph, window=4, window_layer0=True, hidden=32, batch=256):
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+    indptr, indices, feat, labels, train = problem
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    model = GraphSAGE(feat.shape[1], hidden, 7, 3, dropout=0.0).to(dev)
+    tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), torch.from_numpy(feat).to(dev),
+                 torch.from_numpy(labels).to(dev), torch.from_numpy(train).to(dev), model, [15, 10, 5], batch_size=batch,
+                 window=window, cuda_graph=cuda_graph, window_layer0=window_layer0)
+    return tr
+
+
+def test_sample_blocks_and_sample_window_give_identical_blocks():
+    from fastgl_b200.sampler import FusedMapSampler
+    indptr, indices, _, _, train = setup_problem()
+    dev = torch.device("cuda", 0)
+    a, b = FusedMapSampler([15, 10, 5], rng_seed=11), FusedMapSampler([15, 10, 5], rng_seed=11)
+    for s in (a, b):
+        s.edge_src, s.edge_ptr, s.nodes_num = torch.from_numpy(indices).to(dev), torch.from_numpy(indptr).to(dev), len(indptr) - 1
+    seeds = torch.from_numpy(train[:768].reshape(3, 256)).to(dev)
+    fb = a.sample_window(seeds, torch.full((3,), 256, dtype=torch.int32, device=dev))
+    for i in range(3):
+        inputs_w, blocks_w = a.window_blocks(fb, i)
+        inputs_o, outputs_o, blocks_o = b.sample_blocks(None, seeds[i])
+        assert torch.equal(inputs_w, inputs_o) and torch.equal(outputs_o, seeds[i])
+        for bw, bo in zip(blocks_w, blocks_o):
+            assert torch.equal(bw.indptr, bo.indptr) and torch.equal(bw.src, bo.src)
+            assert (bw.n_src, bw.n_dst) == (bo.n_src, bo.n_dst)
+            assert torch.equal(bw.edges()[1], bo.edges()[1])     # dst-local ids of transfer_edge_id == CSR rows
+
+
+def test_loss_curve_tracks_the_cpu_restatement():
+    problem = setup_problem()
+    indptr, indices, feat, labels, train = problem
+    tr = make_trainer(problem, cuda_graph=False)
+    # float64 CPU model with the same initial weights, same seeds, same sampled blocks (via the oracle)
+    params = [p.detach().double().cpu().clone().requires_grad_(True) for p in tr.model.parameters()]
+    opt = torch.optim.Adam(params, lr=0.01, weight_decay=5e-4)
+    gpu_losses = tr.run_steps(6, read_loss_each_step=True)
+    from fastgl_b200.trainer import shard_seeds
+    seeds_all = shard_seeds(torch.from_numpy(train), 0, 1, 12345).numpy()
+    f64 = torch.from_numpy(feat).double()
+    cpu_losses = []
+    for step in range(6):
+        seeds = seeds_all[step * 256:(step + 1) * 256]
+        inputs, _, blocks = oc.sample_blocks(indptr, indices, seeds, [15, 10, 5], False, rng_seed=12345, rng_ctr=8 * step)
+        h = f64[torch.from_numpy(inputs.astype(np.int64))]
+        for i, blk in enumerate(blocks):
+            w, bias = params[2 * i], params[2 * i + 1]
+            deg = np.diff(blk["indptr"])
+            dst = np.repeat(np.arange(blk["n_dst"]), deg)
+            agg = torch.zeros((blk["n_dst"], h.shape[1]), dtype=torch.float64)
+            agg.index_add_(0, torch.from_numpy(dst), h[torch.from_numpy(blk["src_local"].astype(np.int64))])
+            agg = agg / torch.from_numpy(np.maximum(deg, 1)).double().unsqueeze(1)
+            if i:
+                pass
+            h = torch.cat([h[: blk["n_dst"]], agg], 1) @ w + bias
+            if i != len(blocks) - 1:
+                h = torch.relu(h)
+        loss = torch.nn.functional.cross_entropy(h, torch.from_numpy(labels[seeds.astype(np.int64)]))
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        cpu_losses.append(float(loss.detach()))
+    assert np.allclose(gpu_losses, cpu_losses, rtol=2e-3, atol=2e-3), (gpu_losses, cpu_losses)
+    assert gpu_losses[-1] < gpu_losses[0]
+
+
+@pytest.mark.parametrize("window_layer0", [True])
+def test_cuda_graph_step_matches_the_op_by_op_step(window_layer0):
+    problem = setup_problem(seed=9)
+    eager = make_trainer(problem, cuda_graph=False, window_layer0=window_layer0)
+    graphed = make_trainer(problem, cuda_graph=True, window_layer0=window_layer0)
+    le = eager.run_steps(10, read_loss_each_step=True)
+    lg = graphed.run_steps(10, read_loss_each_step=True)
+    assert graphed.graphed is not None and graphed.graph_fallbacks <= 2
+    assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
+    for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+    assert eager.sampled_edges == graphed.sampled_edges
