@@ -63,12 +63,11 @@ __device__ __forceinline__ void set_status(int32_t* status, int code) {
     atomicCAS(status, FGL_OK, code);
 }
 
-// Philox4x32-10 (Salmon et al., SC'11); the reference draws from cuRAND's generator of the same
-// family (sample.cu:68-70,91).  Returns the first output word of the block
-// counter = (pick_slot, seed_slot, lo32(ctr), hi32(ctr)), key = (lo32(seed), hi32(seed)).
-__device__ __forceinline__ uint32_t philox_draw(uint64_t rng_seed, uint64_t rng_ctr, uint32_t seed_slot,
-                                                uint32_t pick_slot) {
-    uint32_t c0 = pick_slot, c1 = seed_slot, c2 = (uint32_t)rng_ctr, c3 = (uint32_t)(rng_ctr >> 32);
+// Philox4x32-10 (Salmon et al., SC'11); the reference draws from cuRAND's generator of the same family
+// (sample.cu:68-70,91).  One block = counter (block_idx, seed_slot, lo32(ctr), hi32(ctr)) under key
+// (lo32(seed), hi32(seed)) gives four words; pick slot i of a seed uses word i % 4 of block i / 4.
+__device__ __forceinline__ uint4 philox_block(uint64_t rng_seed, uint64_t rng_ctr, uint32_t seed_slot, uint32_t block_idx) {
+    uint32_t c0 = block_idx, c1 = seed_slot, c2 = (uint32_t)rng_ctr, c3 = (uint32_t)(rng_ctr >> 32);
     uint32_t k0 = (uint32_t)rng_seed, k1 = (uint32_t)(rng_seed >> 32);
 #pragma unroll
     for (int r = 0; r < 10; ++r) {
@@ -81,7 +80,16 @@ __device__ __forceinline__ uint32_t philox_draw(uint64_t rng_seed, uint64_t rng_
         k0 += 0x9E3779B9u;
         k1 += 0xBB67AE85u;
     }
-    return c0;
+    return make_uint4(c0, c1, c2, c3);
+}
+
+__device__ __forceinline__ uint32_t philox_word(const uint4& b, int i) {
+    return i == 0 ? b.x : (i == 1 ? b.y : (i == 2 ? b.z : b.w));
+}
+
+__device__ __forceinline__ uint32_t philox_draw(uint64_t rng_seed, uint64_t rng_ctr, uint32_t seed_slot,
+                                                uint32_t pick_slot) {
+    return philox_word(philox_block(rng_seed, rng_ctr, seed_slot, pick_slot >> 2), (int)(pick_slot & 3));
 }
 
 __device__ __forceinline__ int warp_incl_scan(int v, int lane) {

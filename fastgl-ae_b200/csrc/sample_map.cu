@@ -72,6 +72,9 @@ struct KParams {
     int32_t* team_sums;            // [n_teams][team_size]
     int32_t* node_pos;             // [n_teams][nodes_stride]: slot of every node, for the clean-up walk
     int32_t* status;               // [0] first error, [1] abort flag
+#ifdef FGL_PHASE_TIMING
+    unsigned long long* dbg;       // phase timestamps of team 0 / rank 0 (instrumented builds only)
+#endif
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -115,11 +118,10 @@ __device__ __forceinline__ int table_insert_seed(const Table& t, uint32_t key, u
 // Returns the local id (>= 0) if the key already has one, else ~pos of its slot (< 0).  created is set
 // for the thread whose atomicCAS claimed the slot.
 template <bool ARRIVAL>
-__device__ __forceinline__ int table_insert(const Table& t, uint32_t key, uint32_t edge, int32_t* status,
-                                            bool& created) {
+__device__ __forceinline__ int table_insert_from(const Table& t, uint32_t key, uint32_t edge, uint32_t pos,
+                                                 int32_t* status, bool& created) {
     created = false;
     const unsigned long long mine = ((unsigned long long)key << 32) | (ARRIVAL ? kPending : (kPending | edge));
-    uint32_t pos = hash_pos(t, key);
     for (uint32_t probe = 0; probe <= t.mask; ++probe) {
         unsigned long long cur = ld_slot(t.slots + pos);
         if (cur == kEmpty) {
@@ -139,6 +141,12 @@ __device__ __forceinline__ int table_insert(const Table& t, uint32_t key, uint32
     }
     set_status(status, FGL_ERR_PROBE);
     return 0;
+}
+
+template <bool ARRIVAL>
+__device__ __forceinline__ int table_insert(const Table& t, uint32_t key, uint32_t edge, int32_t* status,
+                                            bool& created) {
+    return table_insert_from<ARRIVAL>(t, key, edge, hash_pos(t, key), status, created);
 }
 
 // Value of a key that must be present (a seed); missing keys report FGL_ERR_BOUNDS and map to 0.
@@ -199,6 +207,10 @@ __device__ __forceinline__ void load_adj(const KParams& p, int v, long long& sta
     deg = d < 0 ? 0 : (d > 0x7fffffffLL ? 0x7fffffff : (int)d);
 }
 
+template <bool ARRIVAL>
+__device__ __forceinline__ void finish_edge(const KParams& p, const Hop& h, const Table& tab, int g, int e, int r,
+                                            bool created);
+
 // One sampled edge: picked source `g` of seed `v`, edge number e within the hop.
 template <int MODE, bool ARRIVAL>
 __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const Table& tab, int v, int g, int e) {
@@ -214,8 +226,16 @@ __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const 
     }
     bool created;
     int r = table_insert<ARRIVAL>(tab, (uint32_t)g, (uint32_t)e, p.status, created);
+    finish_edge<ARRIVAL>(p, h, tab, g, e, r, created);
+}
+
+// Second half of an insert: in arrival-order mode the claiming thread takes the next local id and publishes
+// it; then the edge's entry (local id, or ~slot while the id is pending) is stored.
+template <bool ARRIVAL>
+__device__ __forceinline__ void finish_edge(const KParams& p, const Hop& h, const Table& tab, int g, int e, int r,
+                                            bool created) {
     if (ARRIVAL && created) {
-        // the claiming thread takes the next local id: one atomicAdd per group of claiming lanes
+        // one atomicAdd per group of claiming lanes
         cg::coalesced_group grp = cg::coalesced_threads();
         int base = 0;
         if (grp.thread_rank() == 0) base = atomicAdd(h.counts + h.hop + 1, (int)grp.size());
@@ -236,53 +256,133 @@ __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const 
     h.blk_src[e] = r;
 }
 
-// Groups of G lanes (G >= fanout, G in {8,16,32}) serve one seed each; picks live in registers.
+// Fanouts up to 32, in two steps per tile of kThreads seeds.
+// Step 1, one thread per seed: the thread chooses its seed's picks alone (Floyd's algorithm needs only the
+// earlier picks of the same seed, kept in the thread's row of shared memory; one Philox block yields four
+// picks) -- a small fraction of the instructions a lane-per-pick scheme spends on shuffles and ballots.
+// Step 2, a group of G lanes per seed, one lane per pick: a group works on kSeedsPerIter seeds at a time and
+// issues their dependent loads stage by stage -- picked sources, first table probes, claims -- so that four
+// independent round trips are in flight per lane instead of one chain after the other.
+constexpr int kSeedsPerIter = 4;
+constexpr int kGroupPathMaxFanout = 32;
+
+__device__ __forceinline__ int picks_stride(int fanout) { return fanout | 1; }  // odd: conflict-free rows
+
 template <int MODE, bool ARRIVAL, int G>
-__device__ __forceinline__ void sample_tile_narrow(const KParams& p, const Hop& h, const Table& tab, Smem& sm,
-                                                   int tile0, int tile_n) {
-    constexpr int kGroups = kThreads / G;
-    const int gid = threadIdx.x / G, gl = threadIdx.x % G;
-    const int lane = threadIdx.x & 31;
-    const int gbase = lane - gl;  // first lane of my group inside the warp
-    const uint32_t gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << gbase);
+__device__ __forceinline__ void sample_tile_groups(const KParams& p, const Hop& h, const Table& tab, Smem& sm,
+                                                   uint32_t* picks, int tile0, int tile_n) {
     const bool replace = (p.flags & FGL_SAMPLE_REPLACE) != 0;
     const int fanout = h.fanout;
-    for (int it = 0; it * kGroups < tile_n; ++it) {
-        const int j = it * kGroups + gid;
-        const bool active = j < tile_n;
-        int v = 0, deg = 0, off = 0;
-        long long start = 0;
-        if (active) {
-            v = sm.v[j];
-            deg = sm.deg[j];
-            off = sm.off[j];
-            start = sm.start[j];
-        }
-        const int k = min(deg, fanout);
-        uint32_t pick = (uint32_t)gl;
-        const bool random = active && deg > fanout;
-        if (__any_sync(0xffffffffu, random)) {
-            uint32_t r = 0;
-            if (random && gl < fanout) r = philox_draw(p.rng_seed, h.ctr, (uint32_t)(tile0 + j), (uint32_t)gl);
-            if (replace) {
-                if (random) pick = __umulhi(r, (uint32_t)deg);
-            } else {
-                // Floyd: slot i draws t in [0, deg-k+i]; a repeat is replaced by deg-k+i itself
-                for (int i = 0; i < fanout; ++i) {
-                    const uint32_t ri = __shfl_sync(0xffffffffu, r, gbase + (i & (G - 1)));
+    const int stride = picks_stride(fanout);
+    {
+        const int t = threadIdx.x;
+        const int deg = t < tile_n ? sm.deg[t] : 0;
+        if (deg > fanout) {
+            uint32_t* mine = picks + (size_t)t * stride;
+            uint4 blk = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < fanout; ++i) {
+                if ((i & 3) == 0) blk = philox_block(p.rng_seed, h.ctr, (uint32_t)(tile0 + t), (uint32_t)(i >> 2));
+                const uint32_t r = philox_word(blk, i & 3);
+                uint32_t pk;
+                if (replace) {
+                    pk = __umulhi(r, (uint32_t)deg);
+                } else {
+                    // Floyd: slot i draws tt in [0, deg-k+i]; a repeat is replaced by deg-k+i itself
                     const uint32_t jj = (uint32_t)(deg - fanout + i);
-                    const uint32_t t = __umulhi(ri, jj + 1u);
-                    const bool hit = random && gl < i && pick == t;
-                    const uint32_t ball = __ballot_sync(0xffffffffu, hit) & gmask;
-                    if (random && gl == i) pick = ball ? jj : t;
+                    const uint32_t tt = __umulhi(r, jj + 1u);
+                    bool hit = false;
+                    for (int q = 0; q < i; ++q) hit |= (mine[q] == tt);
+                    pk = hit ? jj : tt;
+                }
+                mine[i] = pk;
+            }
+        }
+    }
+    __syncthreads();
+
+    constexpr int kGroups = kThreads / G;
+    constexpr int KS = kSeedsPerIter;
+    const int gid = threadIdx.x / G, gl = threadIdx.x % G;
+    for (int it = 0; it * kGroups * KS < tile_n; ++it) {
+        int v[KS], off[KS], g[KS];
+        bool has[KS];
+        // stage 1: the picked sources
+#pragma unroll
+        for (int q = 0; q < KS; ++q) {
+            const int j = (it * KS + q) * kGroups + gid;
+            v[q] = 0;
+            off[q] = 0;
+            g[q] = 0;
+            has[q] = false;
+            if (j < tile_n) {
+                const int deg = sm.deg[j];
+                has[q] = gl < min(deg, fanout);
+                if (has[q]) {
+                    v[q] = sm.v[j];
+                    off[q] = sm.off[j];
+                    const uint32_t pk = deg > fanout ? picks[(size_t)j * stride + gl] : (uint32_t)gl;
+                    g[q] = __ldg(p.indices + sm.start[j] + (long long)pk);
                 }
             }
         }
-        if (active && gl < k) {
-            const int g = p.indices[start + (long long)pick];
-            emit_edge<MODE, ARRIVAL>(p, h, tab, v, g, off + gl);
+        if (MODE == MODE_SAMPLE) {
+#pragma unroll
+            for (int q = 0; q < KS; ++q) {
+                if (has[q]) {
+                    h.blk_src[off[q] + gl] = g[q];
+                    if (h.out_dst) h.out_dst[off[q] + gl] = v[q];
+                }
+            }
+        } else {
+            // stage 2: first probe of every source
+            uint32_t pos[KS];
+            unsigned long long cur[KS], seen[KS];
+#pragma unroll
+            for (int q = 0; q < KS; ++q) {
+                if (has[q] && (g[q] < 0 || (int64_t)g[q] >= p.n_nodes)) {
+                    set_status(p.status, FGL_ERR_BOUNDS);
+                    h.blk_src[off[q] + gl] = 0;
+                    has[q] = false;
+                }
+                pos[q] = hash_pos(tab, (uint32_t)g[q]);
+                cur[q] = has[q] ? ld_slot(tab.slots + pos[q]) : 0ULL;
+            }
+            // stage 3: claim the slots that looked empty
+#pragma unroll
+            for (int q = 0; q < KS; ++q) {
+                seen[q] = cur[q];
+                if (has[q] && cur[q] == kEmpty) {
+                    const uint32_t e = (uint32_t)(off[q] + gl);
+                    seen[q] = atomicCAS(tab.slots + pos[q], kEmpty,
+                                        ((unsigned long long)(uint32_t)g[q] << 32) | (ARRIVAL ? kPending : (kPending | e)));
+                }
+            }
+            // stage 4: settle every edge; collisions continue probing one by one
+#pragma unroll
+            for (int q = 0; q < KS; ++q) {
+                if (!has[q]) continue;
+                const uint32_t key = (uint32_t)g[q];
+                const int e = off[q] + gl;
+                bool created = false;
+                int r;
+                if (cur[q] == kEmpty && seen[q] == kEmpty) {
+                    created = true;
+                    r = ~(int)pos[q];
+                } else if ((uint32_t)(seen[q] >> 32) == key) {
+                    const uint32_t lo = (uint32_t)seen[q];
+                    if (!(lo & kPending)) {
+                        r = (int)lo;
+                    } else {
+                        if (!ARRIVAL && lo > (kPending | (uint32_t)e))
+                            atomicMin(tab.slots + pos[q], ((unsigned long long)key << 32) | (kPending | (uint32_t)e));
+                        r = ~(int)pos[q];
+                    }
+                } else {
+                    r = table_insert_from<ARRIVAL>(tab, key, (uint32_t)e, (pos[q] + 1) & tab.mask, p.status, created);
+                }
+                finish_edge<ARRIVAL>(p, h, tab, g[q], e, r, created);
+            }
         }
-        __syncwarp();
     }
 }
 
@@ -334,11 +434,19 @@ __device__ __forceinline__ void phase_count_seeds(const KParams& p, const Hop& h
     int s0, s1;
     chunk_of(h.n_seeds, t.rank, t.size, s0, s1);
     int acc = 0;
-    for (int s = s0 + (int)threadIdx.x; s < s1; s += kThreads) {
-        long long start;
-        int deg;
-        load_adj<PtrT>(p, __ldcg(h.nodes + s), start, deg);
-        acc += min(deg, h.fanout);
+    for (int s = s0 + (int)threadIdx.x; s < s1; s += 4 * kThreads) {
+        int v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = (s + q * kThreads < s1) ? __ldcg(h.nodes + s + q * kThreads) : -1;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (s + q * kThreads < s1) {
+                long long start;
+                int deg;
+                load_adj<PtrT>(p, v[q], start, deg);
+                acc += min(deg, h.fanout);
+            }
+        }
     }
     const int total = block_sum(acc, sm.scan);
     if (threadIdx.x == 0) __stcg(team_sums + t.rank, total);
@@ -394,11 +502,11 @@ __device__ __forceinline__ void phase_sample(const KParams& p, const Hop& h, con
         __syncthreads();
         const int tile_n = min(kThreads, s1 - tile0);
         if (h.fanout <= 8)
-            sample_tile_narrow<MODE, ARRIVAL, 8>(p, h, tab, sm, tile0, tile_n);
+            sample_tile_groups<MODE, ARRIVAL, 8>(p, h, tab, sm, picks, tile0, tile_n);
         else if (h.fanout <= 16)
-            sample_tile_narrow<MODE, ARRIVAL, 16>(p, h, tab, sm, tile0, tile_n);
-        else if (h.fanout <= 32)
-            sample_tile_narrow<MODE, ARRIVAL, 32>(p, h, tab, sm, tile0, tile_n);
+            sample_tile_groups<MODE, ARRIVAL, 16>(p, h, tab, sm, picks, tile0, tile_n);
+        else if (h.fanout <= kGroupPathMaxFanout)
+            sample_tile_groups<MODE, ARRIVAL, 32>(p, h, tab, sm, picks, tile0, tile_n);
         else
             sample_tile_wide<MODE, ARRIVAL>(p, h, tab, sm, picks, tile0, tile_n);
         running += tile_total;
@@ -417,7 +525,17 @@ __device__ __forceinline__ bool is_first(const Table& tab, int marker, int e) {
 __device__ __forceinline__ void phase_count_first(const Table& tab, const int32_t* edges, int e0, int e1, const Team& t,
                                                   Smem& sm, int32_t* team_sums) {
     int acc = 0;
-    for (int e = e0 + (int)threadIdx.x; e < e1; e += kThreads) acc += is_first(tab, __ldcg(edges + e), e) ? 1 : 0;
+    for (int e = e0 + (int)threadIdx.x; e < e1; e += 4 * kThreads) {
+        int m[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) m[q] = (e + q * kThreads < e1) ? __ldcg(edges + e + q * kThreads) : 0;
+        unsigned long long cur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = (m[q] < 0) ? ld_slot(tab.slots + (uint32_t)~m[q]) : 0ULL;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            acc += (m[q] < 0 && (uint32_t)cur[q] == (kPending | (uint32_t)(e + q * kThreads))) ? 1 : 0;
+    }
     const int total = block_sum(acc, sm.scan);
     if (threadIdx.x == 0) __stcg(team_sums + t.rank, total);
 }
@@ -429,28 +547,37 @@ __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, co
     int before, total;
     team_prefix(team_sums, t, sm, before, total);
     int running = n_before + before;
-    for (int tile0 = e0; tile0 < e1; tile0 += kThreads) {
-        const int e = tile0 + (int)threadIdx.x;
-        int marker = 0;
-        bool first = false;
-        if (e < e1) {
-            marker = __ldcg(edges + e);
-            first = is_first(tab, marker, e);
+    // every thread ranks four consecutive edges: their entries and slots are loaded together
+    for (int tile0 = e0; tile0 < e1; tile0 += 4 * kThreads) {
+        const int eb = tile0 + 4 * (int)threadIdx.x;
+        int m[4];
+        unsigned long long cur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) m[q] = (eb + q < e1) ? __ldcg(edges + eb + q) : 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = (m[q] < 0) ? ld_slot(tab.slots + (uint32_t)~m[q]) : 0ULL;
+        int mine = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (!(m[q] < 0 && (uint32_t)cur[q] == (kPending | (uint32_t)(eb + q)))) m[q] = 0;  // keep first occurrences
+            mine += m[q] < 0 ? 1 : 0;
         }
         int tile_total;
-        const int excl = block_excl_scan(first ? 1 : 0, sm.scan, tile_total);
-        if (first) {
-            const int local = running + excl;
-            const uint32_t pos = (uint32_t)~marker;
-            const unsigned long long cur = ld_slot(tab.slots + pos);
-            const uint32_t key = (uint32_t)(cur >> 32);
-            if ((int64_t)local < nodes_cap) {
-                nodes[local] = (int)key;
-                if (node_pos) node_pos[local] = (int)pos;
-                tab.slots[pos] = ((unsigned long long)key << 32) | (uint32_t)local;
-            } else {
-                set_status(p.status, FGL_ERR_CAPACITY);
-                tab.slots[pos] = ((unsigned long long)key << 32);
+        int local = running + block_excl_scan(mine, sm.scan, tile_total);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (m[q] < 0) {
+                const uint32_t pos = (uint32_t)~m[q];
+                const uint32_t key = (uint32_t)(cur[q] >> 32);
+                if ((int64_t)local < nodes_cap) {
+                    nodes[local] = (int)key;
+                    if (node_pos) node_pos[local] = (int)pos;
+                    tab.slots[pos] = ((unsigned long long)key << 32) | (uint32_t)local;
+                } else {
+                    set_status(p.status, FGL_ERR_CAPACITY);
+                    tab.slots[pos] = ((unsigned long long)key << 32);
+                }
+                ++local;
             }
         }
         running += tile_total;
@@ -460,14 +587,32 @@ __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, co
 
 // Phase E: slot positions -> local ids.
 __device__ __forceinline__ void phase_relabel(const Table& tab, int32_t* edges, int e0, int e1) {
-    for (int e = e0 + (int)threadIdx.x; e < e1; e += kThreads) {
-        const int marker = __ldcg(edges + e);
-        if (marker < 0) {
-            const unsigned long long cur = ld_slot(tab.slots + (uint32_t)~marker);
-            edges[e] = (int)((uint32_t)cur & ~kPending);
-        }
+    for (int e = e0 + (int)threadIdx.x; e < e1; e += 4 * kThreads) {
+        int m[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) m[q] = (e + q * kThreads < e1) ? __ldcg(edges + e + q * kThreads) : 0;
+        unsigned long long cur[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cur[q] = (m[q] < 0) ? ld_slot(tab.slots + (uint32_t)~m[q]) : 0ULL;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (m[q] < 0) edges[e + q * kThreads] = (int)((uint32_t)cur[q] & ~kPending);
     }
 }
+
+#ifdef FGL_PHASE_TIMING
+__device__ __forceinline__ void phase_stamp(const KParams& p, int team_id, const Team& t, int& slot) {
+    if (team_id == 0 && t.rank == 0 && threadIdx.x == 0 && slot < 500) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        p.dbg[slot] = now;
+    }
+    ++slot;
+}
+#define FGL_STAMP() phase_stamp(p, team_id, t, dbg_slot)
+#else
+#define FGL_STAMP()
+#endif
 
 // ----------------------------------------------------------------------------------------------
 // kernels
@@ -491,7 +636,11 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
     tab.mask = (uint32_t)(p.table_slots - 1);
     tab.shift = p.table_shift;
 
+#ifdef FGL_PHASE_TIMING
+    int dbg_slot = 0;
+#endif
     for (int b = team_id; b < p.n_batches; b += p.n_teams) {
+        FGL_STAMP();  // batch start
         Hop h;
         h.nodes = p.nodes + (size_t)b * p.nodes_stride;
         h.nodes_cap = p.nodes_stride;
@@ -534,26 +683,36 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
             h.blk_indptr = p.blk_indptr[hop] ? p.blk_indptr[hop] + (size_t)b * p.blk_indptr_stride[hop] : nullptr;
             h.blk_src = p.blk_src[hop] + (size_t)b * p.blk_src_stride[hop];
 
+            FGL_STAMP();  // A start
             phase_count_seeds<PtrT>(p, h, t, sm, team_sums);
             if (MODE == MODE_FUSED && ARRIVAL && t.rank == 0 && threadIdx.x == 0) h.counts[hop + 1] = n_cur;
+            FGL_STAMP();  // A done
             if (!team_barrier(t, &sm.flag)) return;
+            FGL_STAMP();  // barrier 1 done
 
             int e0, e1, e_total;
             phase_sample<PtrT, MODE, ARRIVAL>(p, h, tab, t, sm, picks, team_sums, e0, e1, e_total);
             if (MODE == MODE_SAMPLE) break;
+            FGL_STAMP();  // B done
             if (!team_barrier(t, &sm.flag)) return;
+            FGL_STAMP();  // barrier 2 done
 
             if (!ARRIVAL) {
                 phase_count_first(tab, h.blk_src, e0, e1, t, sm, team_sums);
+                FGL_STAMP();  // C done
                 if (!team_barrier(t, &sm.flag)) return;
+                FGL_STAMP();  // barrier 3 done
                 n_cur = phase_rank(p, tab, h.blk_src, e0, e1, h.nodes, h.node_pos, h.nodes_cap, n_cur, t, sm, team_sums);
                 n_cur = (int)min((int64_t)n_cur, h.nodes_cap);
                 if (t.rank == 0 && threadIdx.x == 0) h.counts[hop + 1] = n_cur;
+                FGL_STAMP();  // D done
                 if (!team_barrier(t, &sm.flag)) return;
+                FGL_STAMP();  // barrier 4 done
             } else {
                 n_cur = (int)min((int64_t)__ldcg(h.counts + hop + 1), h.nodes_cap);
             }
             phase_relabel(tab, h.blk_src, e0, e1);
+            FGL_STAMP();  // E done
             // the next hop's phase A only reads nodes[] (complete since the last barrier); its barrier
             // keeps the next inserts behind every CTA's relabel reads
         }
@@ -677,6 +836,8 @@ static int log2_of(int64_t pow2) {
 
 template <typename K>
 static int max_coresident(Workspace* ws, K kernel, size_t dyn_smem, int* out) {
+    if (dyn_smem > 48 * 1024)
+        FGL_CUDA_OK(ws, cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem));
     int per_sm = 0;
     FGL_CUDA_OK(ws, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, dyn_smem));
     if (per_sm < 1) {
@@ -689,6 +850,8 @@ static int max_coresident(Workspace* ws, K kernel, size_t dyn_smem, int* out) {
 
 template <typename K>
 static int launch_coop(Workspace* ws, K kernel, int grid, size_t dyn_smem, KParams* kp, cudaStream_t st) {
+    if (dyn_smem > 48 * 1024)
+        FGL_CUDA_OK(ws, cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem));
     void* args[] = {(void*)kp};
     FGL_CUDA_OK(ws, cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), args, dyn_smem, st));
     return FGL_OK;
@@ -709,6 +872,9 @@ static void place_scratch(Workspace* ws, KParams& kp, int n_teams, int grid, int
     if (call_counts) *call_counts = (int32_t*)(base + scratch_head(n_teams, grid) - 128);
     kp.node_pos = (int32_t*)(base + scratch_head(n_teams, grid));
     kp.status = ws->status;
+#ifdef FGL_PHASE_TIMING
+    kp.dbg = (unsigned long long*)(ws->status + 16);
+#endif
 }
 
 template <int MODE>
@@ -727,7 +893,12 @@ static int occupancy_sample_map(Workspace* ws, bool is64, bool arrival, size_t d
 #undef FGL_OCC
 }
 
-static size_t picks_smem(int max_fanout) { return max_fanout > 32 ? (size_t)kWarps * max_fanout * sizeof(uint32_t) : 0; }
+// dynamic shared memory: a row of picks per seed of a tile (fanout <= 32) or per warp (wider fanouts)
+static size_t picks_smem(int max_fanout) {
+    const size_t per_seed = (size_t)kThreads * (std::min(max_fanout, kGroupPathMaxFanout) | 1) * sizeof(uint32_t);
+    const size_t per_warp = max_fanout > kGroupPathMaxFanout ? (size_t)kWarps * max_fanout * sizeof(uint32_t) : 0;
+    return std::max(per_seed, per_warp);
+}
 
 }  // namespace fgl
 
@@ -870,6 +1041,13 @@ int fgl_map(fgl_ws* ws, int32_t* src, int32_t* dst, const int32_t* seeds, int32_
     }
     return FGL_OK;
 }
+
+#ifdef FGL_PHASE_TIMING
+// Instrumented builds only: copies the phase timestamps (ns) of team 0 / CTA 0 of the last fused launch.
+int fgl_debug_phase_times(fgl_ws* ws, unsigned long long* out, int n) {
+    return cudaMemcpy(out, ws->status + 16, sizeof(unsigned long long) * (size_t)n, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     if (!ws || !a || !a->indptr || !a->indices || a->n_nodes <= 0 || a->n_batches < 0 || a->n_hops < 1 ||

@@ -79,8 +79,8 @@ int fgl_ws_create(int device, fgl_ws** out) {
     ws->device = device;
     fgl::DeviceGuard guard(device);
     cudaError_t e = cudaDeviceGetAttribute(&ws->sm_count, cudaDevAttrMultiProcessorCount, device);
-    if (e == cudaSuccess) e = cudaMalloc(&ws->status, 16 * sizeof(int32_t));
-    if (e == cudaSuccess) e = cudaMemset(ws->status, 0, 16 * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ws->status, 16 * sizeof(int32_t) + 512 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(ws->status, 0, 16 * sizeof(int32_t) + 512 * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMallocHost(&ws->host_pinned, 64 * sizeof(int32_t));
     if (e != cudaSuccess) {
         cudaGetLastError();

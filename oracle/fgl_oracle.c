@@ -69,11 +69,12 @@ void fglo_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t o
 }
 
 static inline uint32_t fglo_draw(uint64_t rng_seed, uint64_t rng_ctr, uint32_t seed_slot, uint32_t pick_slot) {
-    uint32_t ctr[4] = {pick_slot, seed_slot, (uint32_t)rng_ctr, (uint32_t)(rng_ctr >> 32)};
+    /* one block serves four picks: counter word 0 = pick_slot / 4, output word pick_slot % 4 */
+    uint32_t ctr[4] = {pick_slot >> 2, seed_slot, (uint32_t)rng_ctr, (uint32_t)(rng_ctr >> 32)};
     uint32_t key[2] = {(uint32_t)rng_seed, (uint32_t)(rng_seed >> 32)};
     uint32_t out[4];
     fglo_philox4x32_10(ctr, key, out);
-    return out[0];
+    return out[pick_slot & 3];
 }
 
 static inline uint32_t fglo_bounded(uint32_t r, uint32_t n) {

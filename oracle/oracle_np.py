@@ -67,12 +67,13 @@ def philox4x32_10(ctr, key):
 def draw(rng_seed: int, rng_ctr: int, seed_slot: int, pick_slot: int) -> int:
     """The 32-bit random word for pick ``pick_slot`` of seed position ``seed_slot``.
 
-    key = (lo32(rng_seed), hi32(rng_seed)); counter = (pick_slot, seed_slot,
-    lo32(rng_ctr), hi32(rng_ctr)); the first output word is used.
+    key = (lo32(rng_seed), hi32(rng_seed)); counter = (pick_slot // 4, seed_slot,
+    lo32(rng_ctr), hi32(rng_ctr)); output word ``pick_slot % 4`` of the block is used,
+    so one block serves four picks.
     """
     key = (rng_seed & MASK32, (rng_seed >> 32) & MASK32)
-    ctr = (pick_slot, seed_slot, rng_ctr & MASK32, (rng_ctr >> 32) & MASK32)
-    return philox4x32_10(ctr, key)[0]
+    ctr = (pick_slot >> 2, seed_slot, rng_ctr & MASK32, (rng_ctr >> 32) & MASK32)
+    return philox4x32_10(ctr, key)[pick_slot & 3]
 
 
 def bounded(r: int, n: int) -> int:
