@@ -81,7 +81,19 @@ struct AggParams {
     // optional: the real number of destination rows, read on the device (n_dst is then the padded row count
     // the launch is sized for; forward rows beyond the real count are zero-filled)
     const int32_t* n_dst_dev;
+    // optional: x is row-sharded over several tables (one per GPU, peer-mapped); global row r lives in
+    // shards[r / rows_per_shard] at local row r % rows_per_shard
+    const float* const* shards;
+    int64_t rows_per_shard;
 };
+
+// Start of input row r: in the single table, or in the shard (possibly another GPU's HBM, read with plain
+// peer loads over NVLink) that owns it.
+__device__ __forceinline__ const float* x_row(const AggParams& p, int64_t r) {
+    if (p.shards == nullptr) return p.x + r * p.ldx;
+    const int64_t s = r / p.rows_per_shard;
+    return p.shards[s] + (r - s * p.rows_per_shard) * p.ldx;
+}
 
 // Forward: out[d,:] = scale_d * sum_e w_e * x[row(src[e]),:]
 // NACC vector accumulators per lane cover 32 * NACC * VEC floats per pass; UNR neighbours' loads are in
@@ -146,12 +158,12 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
         const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b * p.row_map_stride : nullptr;
         T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
         if (p.self_out) {
-            const T* xr = reinterpret_cast<const T*>(p.x + self_row * p.ldx);
+            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row));
             T* srow = reinterpret_cast<T*>(p.self_out + g * p.ld_self);
             for (int c = lane; c < chunks; c += 32) srow[c] = __ldg(xr + c);
         }
         if (a >= e_end) {  // aggregate_acc_kernel.cu:307-308, :405-406
-            const T* xr = reinterpret_cast<const T*>(p.x + self_row * p.ldx);
+            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row));
             for (int c = lane; c < chunks; c += 32) orow[c] = p.passthrough ? __ldg(xr + c) : V::zero();
             continue;
         }
@@ -184,7 +196,7 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                         const int j = min(j0 + u, cnt - 1);  // past the end: reload the last row, skip its FMA
                         const int64_t r = __shfl_sync(0xffffffffu, my_row, j);
                         w[u] = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, j) : 1.0f;
-                        const T* xr = reinterpret_cast<const T*>(p.x + r * p.ldx);
+                        const T* xr = reinterpret_cast<const T*>(x_row(p, r));
 #pragma unroll
                         for (int k = 0; k < NACC; ++k) {
                             const int c = c0 + k * 32 + lane;
@@ -205,6 +217,34 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                 const int c = c0 + k * 32 + lane;
                 if (c < chunks) orow[c] = (MODE == FGL_AGG_SUM) ? acc[k] : V::scale(acc[k], scale);
             }
+        }
+    }
+}
+
+// Row gather: out[i,:] = x[ids[i],:] (single or sharded table).  A warp per row, UNR rows in flight per warp.
+// Replaces the CPU index_select + host-to-device copy of load_subtensors (train_fastgl.py:161-184).
+template <int VEC>
+__global__ void __launch_bounds__(kAggThreads) gather_rows_kernel(const AggParams p, const int32_t* __restrict__ ids, int64_t n_ids) {
+    using T = typename Vec<VEC>::T;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_global = (int64_t)blockIdx.x * kAggWarps + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * kAggWarps;
+    const int chunks = p.dim / VEC;
+    constexpr int UNR = 4;
+    for (int64_t i0 = warp_global * UNR; i0 < n_ids; i0 += n_warps * UNR) {
+        const T* src[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int64_t i = i0 + u < n_ids ? i0 + u : n_ids - 1;
+            src[u] = reinterpret_cast<const T*>(x_row(p, (int64_t)__ldg(ids + i)));
+        }
+        for (int c = lane; c < chunks; c += 32) {
+            T v[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) v[u] = __ldg(src[u] + c);
+#pragma unroll
+            for (int u = 0; u < UNR; ++u)
+                if (i0 + u < n_ids) reinterpret_cast<T*>(p.out + (i0 + u) * p.ldo)[c] = v[u];
         }
     }
 }
@@ -345,9 +385,17 @@ extern "C" {
 int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
                 const int32_t* row_map, const float* x, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags,
                 float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream) {
+    return fgl_agg_fwd_sharded(mode, indptr, src, src_deg, dst_deg, row_map, x, nullptr, 0, ldx, dim, n_dst, flags, out, ldo,
+                               n_dst_dev, stream);
+}
+
+int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                        const int32_t* dst_deg, const int32_t* row_map, const float* x, const float* const* shards,
+                        int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
+                        int64_t ldo, const int32_t* n_dst_dev, void* stream) {
     if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || dim < 1 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
     if (n_dst == 0) return FGL_OK;
-    if (!indptr || !x || !out) return FGL_ERR_INVALID;
+    if (!indptr || (!x && !shards) || (shards && rows_per_shard < 1) || !out) return FGL_ERR_INVALID;
     if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
     AggParams p{};
     p.indptr = indptr;
@@ -362,24 +410,29 @@ int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
     p.dim = dim;
     p.n_dst = n_dst;
     p.n_dst_dev = n_dst_dev;
+    p.shards = shards;
+    p.rows_per_shard = rows_per_shard;
     p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
-    return launch_fwd_any(mode, p, dim3(agg_grid_x(n_dst, 1), 1), pick_vec(dim, x, ldx, out, ldo), (cudaStream_t)stream);
+    return launch_fwd_any(mode, p, dim3(agg_grid_x(n_dst, 1), 1), pick_vec(dim, shards ? nullptr : x, ldx, out, ldo),
+                          (cudaStream_t)stream);
 }
 
 int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride, const int32_t* src,
                        int64_t src_stride, const int32_t* row_map, int64_t row_map_stride, const int64_t* out_row_off,
-                       int64_t total_rows, const float* x, int64_t ldx, int32_t dim, int32_t flags, float* out, int64_t ldo,
-                       float* self_out, int64_t ld_self, void* stream) {
+                       int64_t total_rows, const float* x, const float* const* shards, int64_t rows_per_shard, int64_t ldx,
+                       int32_t dim, int32_t flags, float* out, int64_t ldo, float* self_out, int64_t ld_self, void* stream) {
     if ((mode != FGL_AGG_SUM && mode != FGL_AGG_MEAN) || n_batches < 0 || total_rows < 0 || total_rows > 0x7fffffffLL ||
         dim < 1 || ldx < dim || ldo < dim || (self_out && ld_self < dim))
         return FGL_ERR_INVALID;
     if (n_batches == 0 || total_rows == 0) return FGL_OK;
-    if (!indptr || !src || !out_row_off || !x || !out) return FGL_ERR_INVALID;
+    if (!indptr || !src || !out_row_off || (!x && !shards) || (shards && rows_per_shard < 1) || !out) return FGL_ERR_INVALID;
     AggParams p{};
     p.indptr = indptr;
     p.src = src;
     p.row_map = row_map;
     p.x = x;
+    p.shards = shards;
+    p.rows_per_shard = rows_per_shard;
     p.out = out;
     p.self_out = self_out;
     p.ldx = ldx;
@@ -392,8 +445,33 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
     p.row_map_stride = row_map_stride;
     p.n_batches = n_batches;
     p.out_row_off = out_row_off;
-    const int vec = pick_vec(dim, x, ldx, out, ldo, self_out, self_out ? ld_self : 4);
+    const int vec = pick_vec(dim, shards ? nullptr : x, ldx, out, ldo, self_out, self_out ? ld_self : 4);
     return launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
+}
+
+int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows_per_shard, int64_t ld, int32_t dim,
+                    const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream) {
+    if ((!table && !shards) || (shards && rows_per_shard < 1) || dim < 1 || ld < dim || ldo < dim || n_ids < 0) return FGL_ERR_INVALID;
+    if (n_ids == 0) return FGL_OK;
+    if (!ids || !out) return FGL_ERR_INVALID;
+    AggParams p{};
+    p.x = table;
+    p.shards = shards;
+    p.rows_per_shard = rows_per_shard;
+    p.out = out;
+    p.ldx = ld;
+    p.ldo = ldo;
+    p.dim = dim;
+    // the shard bases cannot be inspected on the host: rely on the leading dimension and cudaMalloc alignment
+    const int vec = pick_vec(dim, shards ? (const void*)nullptr : (const void*)table, ld, out, ldo);
+    const int grid = agg_grid_x((int)std::min<int64_t>((n_ids + 3) / 4, 0x7fffffff), 1);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (vec) {
+        case 4: gather_rows_kernel<4><<<grid, kAggThreads, 0, st>>>(p, ids, n_ids); break;
+        case 2: gather_rows_kernel<2><<<grid, kAggThreads, 0, st>>>(p, ids, n_ids); break;
+        default: gather_rows_kernel<1><<<grid, kAggThreads, 0, st>>>(p, ids, n_ids); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
 int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,

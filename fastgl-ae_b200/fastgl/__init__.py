@@ -32,7 +32,7 @@ from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRI
 __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
-    "sample_map_fused", "fused_capacity", "stage_segments", "set_sampling", "seed", "FusedBatch",
+    "sample_map_fused", "fused_capacity", "stage_segments", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -263,6 +263,57 @@ def exclusive_sum_noalloc(in_degs, out):
 
 
 # ------------------------------------------------------------------------------------------------
+# feature tables
+# ------------------------------------------------------------------------------------------------
+class ShardedTable:
+    """A float32 feature table whose rows are block-partitioned over several device buffers -- typically one
+    per GPU of the box, every peer's buffer mapped into this process (symmetric memory or CUDA IPC).  Global
+    row ``r`` is row ``r % rows_per_shard`` of shard ``r // rows_per_shard``.  The kernels read peers' rows
+    with plain 128-bit loads over NVLink.
+
+    ``shards``: a list of CUDA tensors [rows_per_shard, dim] (kept alive here) or of raw device pointers."""
+
+    def __init__(self, shards, rows_per_shard: int, dim: int, n_rows: int, device, ld: int | None = None):
+        self.keep = [s for s in shards if isinstance(s, torch.Tensor)]
+        ptrs = [int(s.data_ptr()) if isinstance(s, torch.Tensor) else int(s) for s in shards]
+        for t in self.keep:
+            if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.size(1) != dim:
+                raise RuntimeError("shards must be float32 [rows, dim] with unit column stride")
+        self.device = torch.device(device)
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64).to(self.device)
+        self.rows_per_shard = int(rows_per_shard)
+        self.dim = int(dim)
+        self.ld = int(ld if ld is not None else (self.keep[0].stride(0) if self.keep else dim))
+        self.n_rows = int(n_rows)
+
+    def size(self, i):
+        return (self.n_rows, self.dim)[i]
+
+
+def _table_args(input_feat):
+    """(x pointer, shards pointer, rows_per_shard, ld, dim, device) of a dense or sharded table."""
+    if isinstance(input_feat, ShardedTable):
+        return ctypes.c_void_p(0), _ptr(input_feat.ptrs), input_feat.rows_per_shard, input_feat.ld, input_feat.dim, input_feat.device
+    _check_rows_f32(input_feat, "input_feat")
+    return _ptr(input_feat), ctypes.c_void_p(0), 0, input_feat.stride(0), input_feat.size(1), input_feat.device
+
+
+def gather_rows(table, ids, out=None):
+    """``out[i] = table[ids[i]]`` for a dense CUDA matrix or a ``ShardedTable``; ``ids`` int32."""
+    _check_i32(ids, "ids")
+    x, shards, rps, ld, dim, dev = _table_args(table)
+    if out is None:
+        out = torch.empty((ids.numel(), dim), dtype=torch.float32, device=dev)
+    else:
+        _check_rows_f32(out, "out")
+    with _on_device(dev):
+        rc = lib().fgl_gather_rows(x, shards, ctypes.c_int64(rps), ctypes.c_int64(ld), ctypes.c_int32(dim), _ptr(ids),
+                                   ctypes.c_int64(ids.numel()), _ptr(out), ctypes.c_int64(out.stride(0)), _stream(dev))
+    _raise(rc, "gather_rows")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
 # a4-a7  aggregation
 # ------------------------------------------------------------------------------------------------
 def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=None, dst_norm_degs=None,
@@ -273,27 +324,27 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     output is sized for (used to replay a captured CUDA graph on blocks of different sizes)."""
     _check_i32(edge_ptr, "edge_ptr")
     _check_i32(src_edges, "src_edges")
-    _check_f32(input_feat, "input_feat")
-    if input_feat.dim() != 2:
-        raise RuntimeError("input_feat must be 2-D")
+    if not isinstance(input_feat, ShardedTable):
+        _check_f32(input_feat, "input_feat")
+        if input_feat.dim() != 2:
+            raise RuntimeError("input_feat must be 2-D")
     for t, n in ((src_norm_degs, "src_norm_degs"), (dst_norm_degs, "dst_norm_degs"), (row_map, "row_map")):
         if t is not None:
             _check_i32(t, n)
     n_dst = int(dst_nodes)
     if edge_ptr.numel() < n_dst + 1:
         raise RuntimeError("edge_ptr is shorter than dst_nodes + 1")
-    dev = input_feat.device
-    dim = input_feat.size(1)
+    x, shards, rps, ld, dim, dev = _table_args(input_feat)
     if out is None:
         out = torch.empty((n_dst, dim), dtype=torch.float32, device=dev)
     else:
-        _check_f32(out, "out")
+        _check_rows_f32(out, "out")
     with _on_device(dev):
-        rc = lib().fgl_agg_fwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
-                               _ptr(dst_norm_degs), _ptr(row_map), _ptr(input_feat), ctypes.c_int64(input_feat.stride(0)),
-                               ctypes.c_int32(dim), ctypes.c_int32(n_dst),
-                               ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH if zero_deg_passthrough else 0), _ptr(out),
-                               ctypes.c_int64(out.stride(0)), _ptr(n_dst_dev), _stream(dev))
+        rc = lib().fgl_agg_fwd_sharded(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                                       _ptr(dst_norm_degs), _ptr(row_map), x, shards, ctypes.c_int64(rps), ctypes.c_int64(ld),
+                                       ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+                                       ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH if zero_deg_passthrough else 0), _ptr(out),
+                                       ctypes.c_int64(out.stride(0)), _ptr(n_dst_dev), _stream(dev))
     _raise(rc, "aggregate")
     return out
 
@@ -307,7 +358,7 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     list with the total appended).  With ``use_row_map`` the rows of ``input_feat`` are addressed through the
     window's global node ids (aggregation straight from the feature table); ``self_out`` also receives each
     destination's own input row."""
-    _check_f32(input_feat, "input_feat")
+    x, shards, rps, ld, dim, dev = _table_args(input_feat)
     _check_rows_f32(out, "out")
     if self_out is not None:
         _check_rows_f32(self_out, "self_out")
@@ -318,9 +369,7 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
         row_off.append(row_off[-1] + int(n))
     if out.size(0) < row_off[-1] or (self_out is not None and self_out.size(0) < row_off[-1]):
         raise RuntimeError("out is too small for the window's destination rows")
-    dev = input_feat.device
     off_dev = torch.tensor(row_off, dtype=torch.int64).to(dev, non_blocking=True)
-    dim = input_feat.size(1)
     ptr, src = fb.block_indptr[hop], fb.block_src[hop]
     if row_off[-1] == 0:
         return row_off
@@ -328,8 +377,8 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
         rc = lib().fgl_agg_fwd_window(
             ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
             ctypes.c_int64(src.stride(0)), _ptr(fb.nodes if use_row_map else None), ctypes.c_int64(fb.nodes.stride(0)),
-            _ptr(off_dev), ctypes.c_int64(row_off[-1]), _ptr(input_feat),
-            ctypes.c_int64(input_feat.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
+            _ptr(off_dev), ctypes.c_int64(row_off[-1]), x, shards, ctypes.c_int64(rps),
+            ctypes.c_int64(ld), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
             ctypes.c_int64(out.stride(0)), _ptr(self_out), ctypes.c_int64(self_out.stride(0) if self_out is not None else dim),
             _stream(dev))
     _raise(rc, "aggregate_window")

@@ -176,6 +176,22 @@ int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
                 const int32_t* dst_deg, const int32_t* row_map, const float* x, int64_t ldx, int32_t dim,
                 int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream);
 
+/* fgl_agg_fwd over a feature table that is row-sharded across GPUs: shards (device array of n pointers, each a
+ * table of the same leading dimension, mapped into this GPU's address space -- its own HBM or a peer's over
+ * NVLink) replaces x (x may then be NULL); global row r is shards[r / rows_per_shard][r % rows_per_shard].
+ * Rows are fetched with plain 128-bit peer loads, each warp its own rows: no collective, no TMA multicast.
+ * No counterpart in the reference, which keeps features on the host (train_fastgl.py:233). */
+int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                        const int32_t* dst_deg, const int32_t* row_map, const float* x, const float* const* shards,
+                        int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
+                        int64_t ldo, const int32_t* n_dst_dev, void* stream);
+
+/* Row gather out[i, :] = table[ids[i], :] from a single table (shards = NULL) or a row-sharded one (table may
+ * be NULL), as above.  Replaces the CPU index_select + host-to-device copy of load_subtensors
+ * (train_fastgl.py:161-184) and the MatchServer cache look-ups (MatchReorderServer.py:79-110). */
+int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows_per_shard, int64_t ld, int32_t dim,
+                    const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream);
+
 /* Forward aggregation (FGL_AGG_SUM or FGL_AGG_MEAN) of one layer for a whole window of mini-batches in one
  * launch, laid out as fgl_sample_map_fused leaves them: batch b's block is indptr + b * indptr_stride,
  * src + b * src_stride, its row map (may be NULL) row_map + b * row_map_stride.  out_row_off (device,
@@ -185,11 +201,13 @@ int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
  * (the "self" operand of a GraphSAGE layer).  Rows are processed in batch-major order so that a batch's
  * re-read source rows stay in L2.  Used for the first layer, which reads only the feature table and does
  * not depend on the weights; the reference runs K10 once per mini-batch (GraphConv.py:109) after a CPU
- * gather of the input rows (train_fastgl.py:161-184). */
+ * gather of the input rows (train_fastgl.py:161-184).  x / shards / rows_per_shard as in
+ * fgl_agg_fwd_sharded. */
 int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride,
                        const int32_t* src, int64_t src_stride, const int32_t* row_map, int64_t row_map_stride,
-                       const int64_t* out_row_off, int64_t total_rows, const float* x, int64_t ldx, int32_t dim,
-                       int32_t flags, float* out, int64_t ldo, float* self_out, int64_t ld_self, void* stream);
+                       const int64_t* out_row_off, int64_t total_rows, const float* x, const float* const* shards,
+                       int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t flags, float* out, int64_t ldo,
+                       float* self_out, int64_t ld_self, void* stream);
 
 /* Aggregation backward; replaces the scatter kernels K9 / K11
  * (computation_aware_backward_gcn_cuda_kernel aggregate_acc_kernel.cu:468-517 and

@@ -368,6 +368,48 @@ def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph):
     fastgl.check_status()
 
 
+@pytest.mark.parametrize("dim", [100, 602, 1024])
+def test_gather_rows_dense_and_sharded(fastgl, dim):
+    rng = np.random.default_rng(dim)
+    n = 10_000
+    table = rng.standard_normal((n, dim)).astype(np.float32)
+    ids = rng.integers(0, n, size=7777).astype(np.int32)
+    d_table = to_dev(table)
+    got = fastgl.gather_rows(d_table, to_dev(ids))
+    assert np.array_equal(got.cpu().numpy(), table[ids])               # a copy: bit-exact
+    assert fastgl.gather_rows(d_table, torch.zeros(0, dtype=torch.int32, device=dev())).shape == (0, dim)
+    # the same table cut into three row blocks (all on this GPU; on a multi-GPU box they would be peers' buffers)
+    rps = 3400
+    shards = [to_dev(np.ascontiguousarray(table[i * rps:(i + 1) * rps])) for i in range(3)]
+    st = fastgl.ShardedTable(shards, rps, dim, n, dev())
+    assert np.array_equal(fastgl.gather_rows(st, to_dev(ids)).cpu().numpy(), table[ids])
+
+
+def test_aggregate_from_a_sharded_table_matches_the_dense_table(fastgl, graph):
+    indptr, indices = graph
+    rng = np.random.default_rng(31)
+    n = len(indptr) - 1
+    feat = rng.standard_normal((n, 128)).astype(np.float32)
+    seeds = rng.choice(n, size=(2, 300), replace=False).astype(np.int32)
+    fb = fastgl.sample_map_fused(to_dev(indptr), to_dev(indices), to_dev(seeds), to_dev(np.array([300, 300], dtype=np.int32)),
+                                 [5, 10], rng_seed=2, rng_ctr=0)
+    rps = (n + 3) // 4
+    shards = [to_dev(np.ascontiguousarray(feat[i * rps:(i + 1) * rps])) for i in range(4)]
+    st = fastgl.ShardedTable(shards, rps, 128, n, dev())
+    d_feat = to_dev(feat)
+    ptr, src, n_src, n_dst = fb.blocks(1)[0]
+    nodes = fb.input_nodes(1)
+    a = fastgl.aggregate(fastgl.AGG_MEAN, ptr, src, d_feat, n_dst, row_map=nodes, zero_deg_passthrough=False)
+    b = fastgl.aggregate(fastgl.AGG_MEAN, ptr, src, st, n_dst, row_map=nodes, zero_deg_passthrough=False)
+    assert torch.equal(a, b)
+    total = int(fb.counts_host()[:, 1].sum())
+    oa, ob = torch.empty((total, 128), device=dev()), torch.empty((total, 128), device=dev())
+    sa, sb = torch.empty_like(oa), torch.empty_like(ob)
+    fastgl.aggregate_window(fastgl.AGG_MEAN, fb, 1, d_feat, oa, self_out=sa)
+    fastgl.aggregate_window(fastgl.AGG_MEAN, fb, 1, st, ob, self_out=sb)
+    assert torch.equal(oa, ob) and torch.equal(sa, sb)
+
+
 def test_aggregate_high_degree_rows_and_row_map(fastgl):
     rng = np.random.default_rng(9)
     n_dst, n_src, dim = 64, 30000, 100
