@@ -36,6 +36,9 @@ CONFIGS = {
                           fanouts=[15, 10, 5], hidden=256, batch=1024),
     "small": dict(n_nodes=100_000, avg_degree=20.0, feat_dim=128, n_classes=10, train_frac=0.10,
                   fanouts=[15, 10, 5], hidden=256, batch=1024),
+    # high-degree aggregation stress (Reddit-shaped): dense graph, 602-d rows (2408 B: 8-byte aligned only), GCN
+    "reddit-like": dict(n_nodes=233_000, avg_degree=492.0, feat_dim=602, n_classes=41, train_frac=0.66,
+                        fanouts=[25, 10], hidden=256, batch=1024, model="gcn", rmat=(0.45, 0.22, 0.22)),
 }
 
 
@@ -100,7 +103,8 @@ class ClockSampler:
 
 def build_inputs(cfg, device):
     from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
-    indptr, indices = rmat_graph(cfg["n_nodes"], cfg["avg_degree"], seed=12345, device=device)
+    a, b, c = cfg.get("rmat", (0.57, 0.19, 0.19))
+    indptr, indices = rmat_graph(cfg["n_nodes"], cfg["avg_degree"], seed=12345, device=device, a=a, b=b, c=c)
     feat, labels, train = synthetic_node_data(cfg["n_nodes"], cfg["feat_dim"], cfg["n_classes"], cfg["train_frac"],
                                               seed=12345, device=device)
     return indptr, indices, feat, labels, train
@@ -205,11 +209,16 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    model_name = "GCN" if cfg.get("model") == "gcn" else "GraphSAGE-mean"
+    table_mb = cfg["n_nodes"] * cfg["feat_dim"] * 4 / 1e6
+    adj_mb = cfg["n_nodes"] * cfg["avg_degree"] * 4 / 1e6
     config_json = {"workload": f"{args.config}: seeded R-MAT {cfg['n_nodes']} nodes x avg degree {cfg['avg_degree']} "
                                f"(symmetrised), {cfg['feat_dim']}-d fp32 features resident in HBM, {cfg['n_classes']} classes, "
-                               f"3-layer GraphSAGE-mean hidden {cfg['hidden']}, fanout {cfg['fanouts']}, batch {cfg['batch']} per GPU",
+                               f"{len(cfg['fanouts'])}-layer {model_name} hidden {cfg['hidden']}, fanout {cfg['fanouts']}, "
+                               f"batch {cfg['batch']} per GPU",
                    "window": args.window, "parallelism": f"dp{world}", "global_batch": cfg["batch"] * world,
-                   "l2": "inputs larger than L2: 392 MB feature table + 0.5 GB adjacency are gathered at random each step"}
+                   "l2": f"inputs larger than L2: {table_mb:.0f} MB feature table + {adj_mb:.0f} MB adjacency are gathered at "
+                         "random each step"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -235,7 +244,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the fastgl ops have no CPU path")
     import fastgl
-    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.layers import GCN, GraphSAGE
     from fastgl_b200.trainer import Trainer
 
     torch.cuda.set_device(local_rank)
@@ -245,7 +254,10 @@ def main():
     torch.manual_seed(12345)
     torch.backends.cuda.matmul.allow_tf32 = args.matmul == "tf32"
     indptr, indices, feat, labels, train = build_inputs(cfg, device)
-    model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
+    if cfg.get("model") == "gcn":
+        model = GCN(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
+    else:
+        model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
                  reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph)
@@ -354,7 +366,7 @@ def main():
     fastgl.check_status(device)
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and cfg.get("model") != "gcn":
         step, cores = make_cpu_stepper(cfg, indptr, indices, feat, labels, train)
         step()
         edges, dt = time_cpu_steps(step, args.cpu_steps)

@@ -155,7 +155,7 @@ class Trainer:
         self.matcher = MatchReorder(self.n_nodes) if reorder else None
         self.grads = FlatGrads(model.parameters())
         self.lr, self.weight_decay = lr, weight_decay
-        self.use_graph = bool(cuda_graph)
+        self.use_graph = bool(cuda_graph) and hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
         self.graphed = None
         self.graph_fallbacks = 0
         self.reset_optimizer()
@@ -169,7 +169,8 @@ class Trainer:
         self.time_layer0 = False
         # The first layer's [self | neighbour-mean] rows do not depend on the weights, so they are produced for
         # the whole window by one launch straight from the feature table.
-        self.window_layer0 = bool(window_layer0) and hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
+        self.sage = hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
+        self.window_layer0 = bool(window_layer0) and self.sage
         self._layer0_buf = None
 
     def reset_optimizer(self):
@@ -255,9 +256,13 @@ class Trainer:
         if layer0 is not None:
             buf, row_off = layer0
             logits = self.model(blocks, None, layer0=buf[row_off[b]: row_off[b + 1]])
-        else:
+        elif self.sage:
             self.model.layer0_timer = self.layer0_events if self.time_layer0 else None
             logits = self.model(blocks, self.feat, input_nodes=input_nodes)
+        else:
+            # the reference's models (GCN / GIN) take the gathered input rows (train_fastgl.py:357,365)
+            batch_inputs = fastgl.gather_rows(self.feat, input_nodes)
+            logits = self.model(blocks, batch_inputs, neighbor_list=self.fanouts)
         loss = F.cross_entropy(logits, y)
         self.grads.zero()
         loss.backward()
