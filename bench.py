@@ -36,6 +36,14 @@ CONFIGS = {
                           fanouts=[15, 10, 5], hidden=256, batch=1024),
     "small": dict(n_nodes=100_000, avg_degree=20.0, feat_dim=128, n_classes=10, train_frac=0.10,
                   fanouts=[15, 10, 5], hidden=256, batch=1024),
+    # large-scale data-parallel run (papers100M-shaped): ~57 GB of features + ~14 GB of graph replicated per GPU
+    "papers-like": dict(n_nodes=111_000_000, avg_degree=28.8, feat_dim=128, n_classes=172, train_frac=0.011,
+                        fanouts=[15, 10, 5], hidden=256, batch=1024),
+    # feature-sharded run (IGB-shaped): 1024-d rows block-partitioned over the ranks' HBM, read with peer loads
+    "igb-like": dict(n_nodes=100_000_000, avg_degree=12.0, feat_dim=1024, n_classes=19, train_frac=0.01,
+                     fanouts=[15, 10, 5], hidden=256, batch=1024, sharded=True),
+    "igb-like-small": dict(n_nodes=8_000_000, avg_degree=12.0, feat_dim=1024, n_classes=19, train_frac=0.01,
+                           fanouts=[15, 10, 5], hidden=256, batch=1024, sharded=True),
     # high-degree aggregation stress (Reddit-shaped): dense graph, 602-d rows (2408 B: 8-byte aligned only), GCN
     "reddit-like": dict(n_nodes=233_000, avg_degree=492.0, feat_dim=602, n_classes=41, train_frac=0.66,
                         fanouts=[25, 10], hidden=256, batch=1024, model="gcn", rmat=(0.45, 0.22, 0.22)),
@@ -101,12 +109,22 @@ class ClockSampler:
         return out
 
 
-def build_inputs(cfg, device):
+def build_inputs(cfg, device, rank=0, world=1):
     from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
     a, b, c = cfg.get("rmat", (0.57, 0.19, 0.19))
     indptr, indices = rmat_graph(cfg["n_nodes"], cfg["avg_degree"], seed=12345, device=device, a=a, b=b, c=c)
-    feat, labels, train = synthetic_node_data(cfg["n_nodes"], cfg["feat_dim"], cfg["n_classes"], cfg["train_frac"],
-                                              seed=12345, device=device)
+    if cfg.get("sharded") and world > 1:
+        # every rank fills only its own row block; the blocks are then opened by all ranks over CUDA IPC
+        from fastgl_b200.sharding import rows_per_shard, share_feature_shards
+        _, labels, train = synthetic_node_data(cfg["n_nodes"], 1, cfg["n_classes"], cfg["train_frac"], seed=12345, device=device)
+        rps = rows_per_shard(cfg["n_nodes"], world)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(12345 + 31 * rank)
+        shard = torch.randn((rps, cfg["feat_dim"]), generator=gen, device=device, dtype=torch.float32)
+        feat = share_feature_shards(shard, cfg["n_nodes"])
+    else:
+        feat, labels, train = synthetic_node_data(cfg["n_nodes"], cfg["feat_dim"], cfg["n_classes"], cfg["train_frac"],
+                                                  seed=12345, device=device)
     return indptr, indices, feat, labels, train
 
 
@@ -253,7 +271,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     torch.manual_seed(12345)
     torch.backends.cuda.matmul.allow_tf32 = args.matmul == "tf32"
-    indptr, indices, feat, labels, train = build_inputs(cfg, device)
+    indptr, indices, feat, labels, train = build_inputs(cfg, device, rank, world)
     if cfg.get("model") == "gcn":
         model = GCN(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
     else:
@@ -366,7 +384,7 @@ def main():
     fastgl.check_status(device)
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and cfg.get("model") != "gcn":
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and cfg.get("model") != "gcn" and cfg["n_nodes"] <= 10_000_000:
         step, cores = make_cpu_stepper(cfg, indptr, indices, feat, labels, train)
         step()
         edges, dt = time_cpu_steps(step, args.cpu_steps)
@@ -394,6 +412,10 @@ def main():
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
     if world > 1:
+        # drop peers' mappings before any rank tears its allocations down
+        del tr, feat
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
 
 
