@@ -157,7 +157,7 @@ class _TallLinear(torch.autograd.Function):
 
     The weight gradient x^T dy has a tiny output and a very long reduction; as one GEMM it runs on a handful
     of CTAs.  Here the rows are split into S slabs, a batched GEMM produces S partial products on S times as
-    many CTAs, and the partials are summed; the bias gradient is reduced in the same two stages."""
+    many CTAs, and the partials (and the per-slab column sums for the bias) are folded by a 1 x S GEMM."""
 
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -169,16 +169,17 @@ class _TallLinear(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         dy = dy.contiguous()
         dx = torch.mm(dy, weight.t()) if ctx.needs_input_grad[0] else None
-        n = x.size(0)
-        slabs = next((s for s in (32, 16, 8) if n % s == 0 and n // s >= 512), 0)
+        n, k, m = x.size(0), x.size(1), dy.size(1)
+        slabs = next((s for s in (16, 8) if n % s == 0 and n // s >= 512), 0)
         if slabs and x.is_contiguous():
-            xs = x.view(slabs, n // slabs, x.size(1))
-            dys = dy.view(slabs, n // slabs, dy.size(1))
-            dw = torch.bmm(xs.transpose(1, 2), dys).sum(0)
-            db = dys.sum(1).sum(0)
+            ones = dy.new_ones((1, slabs))
+            part = torch.bmm(x.view(slabs, n // slabs, k).transpose(1, 2), dy.view(slabs, n // slabs, m))
+            dw = torch.mm(ones, part.view(slabs, k * m)).view(k, m)
+            col = torch.bmm(dy.new_ones((slabs, 1, n // slabs)), dy.view(slabs, n // slabs, m))
+            db = torch.mm(ones, col.view(slabs, m)).view(m)
         else:
             dw = torch.mm(x.t(), dy)
-            db = dy.sum(0)
+            db = torch.mv(dy.t(), dy.new_ones(n))
         return dx, dw, db
 
 
