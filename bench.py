@@ -355,6 +355,10 @@ def main():
         achieved = alg / (mean_ms * 1e-3) / 1e9
         roofline.update({"achieved": achieved, "frac": achieved / peak, "algorithmic_bytes_per_launch": alg,
                          "launch_ms": mean_ms, "launches_timed": len(agg_ms)})
+        if args.config == "products-like" and args.window == 8:
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
+            # ncu capture summarised in profiles/agg_fwd_kernel_window_products-like.md
+            roofline["traffic"] = 744.6e6
         smp = [s.elapsed_time(e) for s, e, nb in tr.sample_events if nb == args.window]
         if smp:
             smp_ms = statistics.mean(smp)
@@ -362,6 +366,7 @@ def main():
                                "achieved": sm_bytes / (smp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
                                "launch_ms": smp_ms, "launches_timed": len(smp),
+                               "traffic": 428.1e6 if (args.config == "products-like" and args.window == 8) else None,
                                "note": "event-timed on the launching stream; includes the host gap before the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
