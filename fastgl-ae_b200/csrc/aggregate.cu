@@ -85,6 +85,9 @@ struct AggParams {
     // shards[r / rows_per_shard] at local row r % rows_per_shard
     const float* const* shards;
     int64_t rows_per_shard;
+    // FGL_AGG_EDGE: one weight per (edge, head), edge_w[e * n_heads + h]; head h covers dim / n_heads columns
+    const float* edge_w;
+    int32_t n_heads;
 };
 
 // Start of input row r: in the single table, or in the shard (possibly another GPU's HBM, read with plain
@@ -173,8 +176,12 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
 
         for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
             T acc[NACC];
+            int head[NACC];
 #pragma unroll
-            for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
+            for (int k = 0; k < NACC; ++k) {
+                acc[k] = V::zero();
+                head[k] = (MODE == FGL_AGG_EDGE) ? min(((c0 + k * 32 + lane) * VEC) / (p.dim / p.n_heads), p.n_heads - 1) : 0;
+            }
             for (int e0 = a; e0 < e_end; e0 += 32) {
                 const int cnt = min(32, e_end - e0);
                 int64_t my_row = first_row;
@@ -207,7 +214,12 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                     for (int u = 0; u < UNR; ++u) {
                         if (j0 + u < cnt) {  // warp-uniform
 #pragma unroll
-                            for (int k = 0; k < NACC; ++k) V::fma(acc[k], w[u], v[u][k]);
+                            for (int k = 0; k < NACC; ++k) {
+                                const float wk = (MODE == FGL_AGG_EDGE)
+                                                     ? __ldg(p.edge_w + (int64_t)(e0 + j0 + u) * p.n_heads + head[k])
+                                                     : w[u];
+                                V::fma(acc[k], wk, v[u][k]);
+                            }
                         }
                     }
                 }
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
 #pragma unroll
             for (int k = 0; k < NACC; ++k) {
                 const int c = c0 + k * 32 + lane;
-                if (c < chunks) orow[c] = (MODE == FGL_AGG_SUM) ? acc[k] : V::scale(acc[k], scale);
+                if (c < chunks) orow[c] = (MODE == FGL_AGG_SUM || MODE == FGL_AGG_EDGE) ? acc[k] : V::scale(acc[k], scale);
             }
         }
     }
@@ -274,10 +286,12 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
 
         for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
             T g[NACC];
+            int head[NACC];
 #pragma unroll
             for (int k = 0; k < NACC; ++k) {
                 const int c = c0 + k * 32 + lane;
                 g[k] = (c < chunks) ? V::scale(__ldg(grow + c), scale) : V::zero();
+                head[k] = (MODE == FGL_AGG_EDGE) ? min((c * VEC) / (p.dim / p.n_heads), p.n_heads - 1) : 0;
             }
             for (int e0 = a; e0 < b; e0 += 32) {
                 const int cnt = min(32, b - e0);
@@ -295,9 +309,58 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
 #pragma unroll
                     for (int k = 0; k < NACC; ++k) {
                         const int c = c0 + k * 32 + lane;
-                        if (c < chunks) red_add(xr + c, (MODE == FGL_AGG_SYMNORM) ? V::scale(g[k], w) : g[k]);
+                        if (c < chunks) {
+                            if (MODE == FGL_AGG_EDGE)
+                                red_add(xr + c, V::scale(g[k], __ldg(p.edge_w + (int64_t)(e0 + j) * p.n_heads + head[k])));
+                            else
+                                red_add(xr + c, (MODE == FGL_AGG_SYMNORM) ? V::scale(g[k], w) : g[k]);
+                        }
                     }
                 }
+            }
+        }
+    }
+}
+
+// Gradient of the edge weights: dw[e, h] = sum over head h's columns f of dy[d, f] * x[src[e], f] for every edge e of
+// row d (the term the reference drops, GraphConv.py:227).  A warp per destination row; per neighbour the lanes
+// multiply their vectors, reduce within runs of lanes that share a head, and the first lane of each run adds.
+template <int VEC>
+__global__ void __launch_bounds__(kAggThreads) agg_edge_wgrad_kernel(const AggParams p, float* __restrict__ dw) {
+    using T = typename Vec<VEC>::T;
+    const int lane = threadIdx.x & 31;
+    const int warp_global = blockIdx.x * kAggWarps + (threadIdx.x >> 5);
+    const int n_warps = gridDim.x * kAggWarps;
+    const int chunks = p.dim / VEC;
+    const int unit = p.dim / p.n_heads;
+    for (int d = warp_global; d < p.n_dst; d += n_warps) {
+        const int a = __ldg(p.indptr + d), b = __ldg(p.indptr + d + 1);
+        const T* grow = reinterpret_cast<const T*>(p.out + (int64_t)d * p.ldo);  // dy
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+            const int c = c0 + lane;
+            const bool live = c < chunks;
+            const int head = live ? (c * VEC) / unit : -1;
+            T g = Vec<VEC>::zero();
+            if (live) g = __ldg(grow + c);
+            const int prev_head = __shfl_up_sync(0xffffffffu, head, 1);
+            const bool leader = live && (lane == 0 || prev_head != head);
+            for (int e = a; e < b; ++e) {
+                const int s = __ldg(p.src + e);
+                float v = 0.0f;
+                if (live) {
+                    const T xv = __ldg(reinterpret_cast<const T*>(p.x + (int64_t)s * p.ldx) + c);
+                    const float* gp = reinterpret_cast<const float*>(&g);
+                    const float* xp = reinterpret_cast<const float*>(&xv);
+#pragma unroll
+                    for (int q = 0; q < VEC; ++q) v = fmaf(gp[q], xp[q], v);
+                }
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {  // segmented suffix sum over lanes of the same head
+                    const float ov = __shfl_down_sync(0xffffffffu, v, off);
+                    const int oh = __shfl_down_sync(0xffffffffu, head, off);
+                    if (lane + off < 32 && oh == head) v += ov;
+                }
+                if (leader) atomicAdd(dw + (int64_t)e * p.n_heads + head, v);
             }
         }
     }
@@ -346,6 +409,7 @@ static void launch_fwd_mode(int mode, const AggParams& p, dim3 grid, cudaStream_
     if (mode == FGL_AGG_SUM) launch_fwd_nacc<VEC, FGL_AGG_SUM>(p, grid, st);
     if (mode == FGL_AGG_MEAN) launch_fwd_nacc<VEC, FGL_AGG_MEAN>(p, grid, st);
     if (mode == FGL_AGG_SYMNORM) launch_fwd_nacc<VEC, FGL_AGG_SYMNORM>(p, grid, st);
+    if (mode == FGL_AGG_EDGE) launch_fwd_nacc<VEC, FGL_AGG_EDGE>(p, grid, st);
 }
 
 static int launch_fwd_any(int mode, const AggParams& p, dim3 grid, int vec, cudaStream_t st) {
@@ -374,6 +438,7 @@ static void launch_bwd_mode(int mode, const AggParams& p, int grid, cudaStream_t
     if (mode == FGL_AGG_SUM) launch_bwd_nacc<VEC, FGL_AGG_SUM>(p, grid, st);
     if (mode == FGL_AGG_MEAN) launch_bwd_nacc<VEC, FGL_AGG_MEAN>(p, grid, st);
     if (mode == FGL_AGG_SYMNORM) launch_bwd_nacc<VEC, FGL_AGG_SYMNORM>(p, grid, st);
+    if (mode == FGL_AGG_EDGE) launch_bwd_nacc<VEC, FGL_AGG_EDGE>(p, grid, st);
 }
 
 }  // namespace fgl
@@ -447,6 +512,91 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
     p.out_row_off = out_row_off;
     const int vec = pick_vec(dim, shards ? nullptr : x, ldx, out, ldo, self_out, self_out ? ld_self : 4);
     return launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
+}
+
+int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* x, int64_t ldx,
+                     int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream) {
+    if (n_dst < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
+    if (n_dst == 0) return FGL_OK;
+    if (!indptr || !x || !out || !edge_w) return FGL_ERR_INVALID;
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.x = x;
+    p.out = out;
+    p.ldx = ldx;
+    p.ldo = ldo;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.edge_w = edge_w;
+    p.n_heads = n_heads;
+    p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
+    int vec = pick_vec(dim, x, ldx, out, ldo);
+    while (vec > 1 && (dim / n_heads) % vec != 0) vec /= 2;  // a vector never straddles two heads
+    return launch_fwd_any(FGL_AGG_EDGE, p, dim3(agg_grid_x(n_dst, 1), 1), vec, (cudaStream_t)stream);
+}
+
+int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* dy, int64_t ldy,
+                     int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, void* stream) {
+    if (n_dst < 0 || n_src < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldy < dim || ldx < dim) return FGL_ERR_INVALID;
+    if (n_src == 0) return FGL_OK;
+    if (!dx) return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemset2DAsync(dx, sizeof(float) * (size_t)ldx, 0, sizeof(float) * (size_t)dim, (size_t)n_src, st) != cudaSuccess)
+        return FGL_ERR_CUDA;
+    if (n_dst == 0) return FGL_OK;
+    if (!indptr || !dy || !edge_w) return FGL_ERR_INVALID;
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.x = dy;
+    p.out = dx;
+    p.ldx = ldy;
+    p.ldo = ldx;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.n_src = n_src;
+    p.edge_w = edge_w;
+    p.n_heads = n_heads;
+    int vec = pick_vec(dim, dy, ldy, dx, ldx);
+    while (vec > 1 && (dim / n_heads) % vec != 0) vec /= 2;
+    const int grid = agg_grid_x(n_dst, 1);
+    switch (vec) {
+        case 4: launch_bwd_mode<4>(FGL_AGG_EDGE, p, grid, st); break;
+        case 2: launch_bwd_mode<2>(FGL_AGG_EDGE, p, grid, st); break;
+        default: launch_bwd_mode<1>(FGL_AGG_EDGE, p, grid, st); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x, int64_t ldx, const float* dy,
+                       int64_t ldy, int32_t dim, int32_t n_dst, int64_t n_edges, float* dw, void* stream) {
+    if (n_dst < 0 || n_edges < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldy < dim) return FGL_ERR_INVALID;
+    if (n_edges == 0) return FGL_OK;
+    if (!dw) return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)n_edges * (size_t)n_heads, st) != cudaSuccess) return FGL_ERR_CUDA;
+    if (n_dst == 0) return FGL_OK;
+    if (!indptr || !src || !x || !dy) return FGL_ERR_INVALID;
+    AggParams p{};
+    p.indptr = indptr;
+    p.src = src;
+    p.x = x;
+    p.out = const_cast<float*>(dy);
+    p.ldx = ldx;
+    p.ldo = ldy;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.n_heads = n_heads;
+    int vec = pick_vec(dim, x, ldx, dy, ldy);
+    while (vec > 1 && (dim / n_heads) % vec != 0) vec /= 2;
+    const int grid = agg_grid_x(n_dst, 1);
+    switch (vec) {
+        case 4: agg_edge_wgrad_kernel<4><<<grid, kAggThreads, 0, st>>>(p, dw); break;
+        case 2: agg_edge_wgrad_kernel<2><<<grid, kAggThreads, 0, st>>>(p, dw); break;
+        default: agg_edge_wgrad_kernel<1><<<grid, kAggThreads, 0, st>>>(p, dw); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
 int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows_per_shard, int64_t ld, int32_t dim,

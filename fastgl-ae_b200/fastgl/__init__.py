@@ -1,11 +1,11 @@
 """``fastgl`` -- drop-in replacement of the reference's PyTorch extension of the same name.
 
 The reference binds 19 ops with pybind11 (cuda_operators/aggregate_acc.cpp:601-621); the ones its
-Python callers use (FusedMapSampler.py:76,98; GraphConv.py:26,37,93-96,109,132) are re-exposed here
+Python callers use (FusedMapSampler.py:76,98; GraphConv.py:26,37,93-96,109,132,204,224) are re-exposed here
 with the same names, positional arguments, dtypes, return lists and error behaviour:
 
     sample_node, transfer_edge_id, cal_deg, exclusive_sum,
-    forward_gcn, backward_gcn, forwaed_gin (sic), backward_gin
+    forward_gcn, backward_gcn, forwaed_gin (sic), backward_gin, forward_gat, backward_gat
 
 Each op allocates its outputs with torch and calls the C ABI of ``libfastgl_b200.so``
 (include/fastgl_b200.h) with raw device pointers and torch's current CUDA stream.  The dense weight
@@ -31,7 +31,7 @@ from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRI
 
 __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
-    "forwaed_gin", "backward_gin", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
+    "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
@@ -405,6 +405,70 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
                                ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
     _raise(rc, "aggregate_backward")
     return d_x
+
+
+def forward_gat(edge_ptr, edge_data, src_edges, input_feat, neighbor_num, dst_nodes, num_heads):
+    """aggregate_acc.cpp:211-246 -> computation_aware_forward_gat_cuda (aggregate_acc_kernel.cu:789-885).
+
+    ``edge_data`` float32[E, num_heads] holds one attention coefficient per edge and head; head ``h`` owns the
+    columns ``[h * dim / num_heads, (h + 1) * dim / num_heads)`` of ``input_feat``.  Returns ``[out]`` with
+    ``out[d] = sum_e edge_data[e, head] * input_feat[src[e]]``; a row without in-edges copies its own input row."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    _check_f32(edge_data, "edge_data")
+    _check_f32(input_feat, "input_feat")
+    H, dim, n_dst = int(num_heads), input_feat.size(1), int(dst_nodes)
+    if edge_data.dim() != 2 or edge_data.size(1) != H or dim % H != 0 or edge_data.size(0) < src_edges.numel():
+        raise RuntimeError("edge_data must be [n_edges, num_heads] and num_heads must divide the feature width")
+    dev = input_feat.device
+    out = torch.empty((n_dst, dim), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_agg_edge_fwd(_ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(input_feat),
+                                    ctypes.c_int64(input_feat.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+                                    ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH), _ptr(out), ctypes.c_int64(dim), _stream(dev))
+    _raise(rc, "forward_gat")
+    return [out]
+
+
+def backward_gat(edge_ptr, edge_data, src_edges, d_input, src_nodes, num_heads):
+    """aggregate_acc.cpp:248-281 -> computation_aware_backward_gat_cuda (aggregate_acc_kernel.cu:887-979).
+
+    Returns ``[d_x]`` with ``d_x[src[e]] += edge_data[e, head] * d_input[d]``; like the reference, no gradient
+    is produced for ``edge_data`` (GraphConv.py:227)."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    _check_f32(edge_data, "edge_data")
+    _check_f32(d_input, "d_input")
+    H, dim, n_dst = int(num_heads), d_input.size(1), d_input.size(0)
+    if edge_data.dim() != 2 or edge_data.size(1) != H or dim % H != 0:
+        raise RuntimeError("edge_data must be [n_edges, num_heads] and num_heads must divide the feature width")
+    dev = d_input.device
+    d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_agg_edge_bwd(_ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(d_input),
+                                    ctypes.c_int64(d_input.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+                                    ctypes.c_int32(int(src_nodes)), _ptr(d_x), ctypes.c_int64(dim), _stream(dev))
+    _raise(rc, "backward_gat")
+    return [d_x]
+
+
+def edge_weight_grad(edge_ptr, src_edges, input_feat, d_out, num_heads):
+    """Gradient of ``forward_gat`` with respect to ``edge_data`` (not computed by the reference):
+    ``d_w[e, h] = <d_out[d, head h], input_feat[src[e], head h]>`` for every edge ``e`` of row ``d``."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    _check_f32(input_feat, "input_feat")
+    _check_f32(d_out, "d_out")
+    H, dim, E = int(num_heads), d_out.size(1), src_edges.numel()
+    dev = d_out.device
+    d_w = torch.empty((E, H), dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_agg_edge_wgrad(_ptr(edge_ptr), _ptr(src_edges), ctypes.c_int32(H), _ptr(input_feat),
+                                      ctypes.c_int64(input_feat.stride(0)), _ptr(d_out), ctypes.c_int64(d_out.stride(0)),
+                                      ctypes.c_int32(dim), ctypes.c_int32(d_out.size(0)), ctypes.c_int64(E), _ptr(d_w),
+                                      _stream(dev))
+    _raise(rc, "edge_weight_grad")
+    return d_w
 
 
 def forward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, input_feat, weight, neighbor_num, dst_nodes):

@@ -1,7 +1,8 @@
 """GNN layers over the ``fastgl`` aggregation ops.
 
-``MA_Function`` / ``MA_Function_GIN``, ``GCNConv`` / ``GINConv`` and ``GCN`` / ``GIN`` keep the interface and
-the arithmetic of the reference's GraphConv.py (:19-40, :102-135, :42-99, :138-195): update-then-aggregate for
+``MA_Function`` / ``MA_Function_GIN`` / ``MA_Function_GAT``, ``GCNConv`` / ``GINConv`` / ``GATConv`` and ``GCN`` /
+``GIN`` / ``GAT`` keep the interface and the arithmetic of the reference's GraphConv.py (:19-40, :102-135, :196-228,
+:42-99, :138-195, :231-312): update-then-aggregate for
 GCN, aggregate-then-update for GIN, dropout between layers, no bias and no activation.  ``SAGEConv`` /
 ``GraphSAGE`` add the mean aggregator that the benchmark configurations name (the reference has none): 
 ``h' = h_dst W_self + mean_{s in N(d)} h_s W_neigh + b``, with the first layer aggregating straight from the
@@ -125,6 +126,89 @@ class GIN(_Stack):
             block = blocks[i]
             edge_ptr, src_edges = block_csr(block)
             h = layer(edge_ptr, src_edges, block.num_dst_nodes(), h, neighbor_list[i])
+        return h
+
+
+class MA_Function_GAT(torch.autograd.Function):
+    """GraphConv.py:196-228.  ``attention_grad=False`` is the reference: no gradient reaches ``edge_data``
+    (backward returns None for it, GraphConv.py:227); ``True`` adds the missing term."""
+
+    @staticmethod
+    def forward(ctx, edge_ptr, edge_data, src_edges, dst_edges, dst_nodes, input_feat, num_heads, neighbor_num,
+                attention_grad=False):
+        edge_data = edge_data.contiguous()
+        out = fastgl.forward_gat(edge_ptr, edge_data, src_edges, input_feat, neighbor_num, dst_nodes, num_heads)[0]
+        ctx.src_nodes, ctx.num_heads, ctx.attention_grad = input_feat.size(0), num_heads, attention_grad
+        ctx.save_for_backward(edge_ptr, edge_data, src_edges, input_feat)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_input):
+        edge_ptr, edge_data, src_edges, input_feat = ctx.saved_tensors
+        d_input = d_input.contiguous()
+        d_x = fastgl.backward_gat(edge_ptr, edge_data, src_edges, d_input, ctx.src_nodes, ctx.num_heads)[0]
+        d_w = None
+        if ctx.attention_grad and ctx.needs_input_grad[1]:
+            d_w = fastgl.edge_weight_grad(edge_ptr, src_edges, input_feat, d_input, ctx.num_heads)
+        return None, d_w, None, None, None, d_x, None, None, None
+
+
+def edge_softmax(e: torch.Tensor, dst: torch.Tensor, n_dst: int) -> torch.Tensor:
+    """Softmax of the edge scores ``e`` [E, H] over the in-edges of every destination (what the reference
+    takes from ``dgl.nn.functional.edge_softmax``, GraphConv.py:268)."""
+    idx = dst.long()
+    top = torch.full((n_dst, e.size(1)), float("-inf"), dtype=e.dtype, device=e.device)
+    top = top.scatter_reduce(0, idx[:, None].expand_as(e), e, "amax", include_self=True)
+    ex = torch.exp(e - top[idx])
+    denom = torch.zeros((n_dst, e.size(1)), dtype=e.dtype, device=e.device).index_add_(0, idx, ex)
+    return ex / denom[idx]
+
+
+class GATConv(nn.Module):
+    """GraphConv.py:231-283: shared linear map, additive attention, edge softmax, weighted multi-head sum."""
+
+    def __init__(self, input_dim, output_dim, num_heads, feat_drop=0.0, attn_drop=0.0, negative_slope=0.2,
+                 attention_grad=False):
+        super().__init__()
+        self.out_feats, self.num_heads, self.attention_grad = output_dim, num_heads, attention_grad
+        self.fc = nn.Linear(input_dim, output_dim * num_heads, bias=False)
+        self.attn_l = nn.Parameter(torch.empty(1, num_heads, output_dim))
+        self.attn_r = nn.Parameter(torch.empty(1, num_heads, output_dim))
+        self.feat_drop, self.attn_drop = nn.Dropout(feat_drop), nn.Dropout(attn_drop)
+        self.leaky_relu = nn.LeakyReLU(negative_slope)
+        gain = nn.init.calculate_gain("relu")
+        nn.init.xavier_normal_(self.fc.weight, gain=gain)
+        nn.init.xavier_normal_(self.attn_l, gain=gain)
+        nn.init.xavier_normal_(self.attn_r, gain=gain)
+
+    def forward(self, block, input_feat, neighbor_num):
+        n_dst = block.num_dst_nodes()
+        feat_src = self.fc(input_feat).view(-1, self.num_heads, self.out_feats)
+        el = (feat_src * self.attn_l).sum(dim=-1)
+        er = (feat_src[:n_dst] * self.attn_r).sum(dim=-1)
+        edge_ptr, src_edges = block_csr(block)
+        dst_edges = block.edges()[1]
+        e = self.leaky_relu(el[src_edges.long()] + er[dst_edges.long()])
+        edge_data = self.attn_drop(edge_softmax(e, dst_edges, n_dst))
+        flat = feat_src.reshape(-1, self.num_heads * self.out_feats)
+        return MA_Function_GAT.apply(edge_ptr, edge_data, src_edges, dst_edges, n_dst, flat, self.num_heads, neighbor_num,
+                                     self.attention_grad)
+
+
+class GAT(nn.Module):
+    """GraphConv.py:285-312: ``heads`` heads of ``n_hidden`` in the inner layers, one head of ``n_classes`` last."""
+
+    def __init__(self, in_feats, n_hidden, n_classes, n_layers, activation=None, dropout=0.5, heads=8, attention_grad=False):
+        super().__init__()
+        self.layers = nn.ModuleList([GATConv(in_feats, n_hidden, heads, attention_grad=attention_grad)])
+        for _ in range(1, n_layers - 1):
+            self.layers.append(GATConv(n_hidden * heads, n_hidden, heads, feat_drop=dropout, attention_grad=attention_grad))
+        self.layers.append(GATConv(n_hidden * heads, n_classes, 1, feat_drop=dropout, attention_grad=attention_grad))
+
+    def forward(self, blocks, features, neighbor_list=(5, 10, 15)):
+        h = features
+        for i, layer in enumerate(self.layers):
+            h = layer(blocks[i], h, neighbor_list[i])
         return h
 
 

@@ -45,6 +45,8 @@ extern "C" {
 #define FGL_AGG_SUM 0     /* out[d] = sum_s x[s]                                  (GIN,  K10/K11) */
 #define FGL_AGG_MEAN 1    /* out[d] = sum_s x[s] / deg_in(d)                      (GraphSAGE-mean) */
 #define FGL_AGG_SYMNORM 2 /* out[d] = sum_s x[s] * rsqrt(dst_deg[d]) * rsqrt(src_deg[s]) (GCN, K8/K9) */
+#define FGL_AGG_EDGE 3    /* out[d, h] = sum_e w[e, h] * x[src[e], h]: per-edge, per-head weights (GAT, K12);
+                             only through fgl_agg_edge_fwd / fgl_agg_edge_bwd */
 
 #define FGL_MAX_HOPS 7
 #define FGL_COUNTS_STRIDE 16 /* per mini-batch: [0..7] node counts n_0..n_L, [8..15] edge counts per hop */
@@ -185,6 +187,25 @@ int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src,
                         const int32_t* dst_deg, const int32_t* row_map, const float* x, const float* const* shards,
                         int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
                         int64_t ldo, const int32_t* n_dst_dev, void* stream);
+
+/* Edge-weighted multi-head aggregation; replaces computation_aware_forward_gat_cuda /
+ * computation_aware_backward_gat_cuda (aggregate_acc_kernel.cu:789-979; bindings aggregate_acc.cpp
+ * forward_gat / backward_gat).  edge_w is float32 [n_edges][n_heads] (the attention coefficients after the
+ * edge softmax), head h owns columns [h * dim / n_heads, (h + 1) * dim / n_heads).
+ * Forward: out[d, f] = sum over row d's edges e of edge_w[e, head(f)] * x[src[e], f]; a row without in-edges
+ * copies x[d] when FGL_AGG_ZERO_DEG_PASSTHROUGH is set (:870-872).  Backward: dx is zero-filled, then
+ * dx[src[e], f] += edge_w[e, head(f)] * dy[d, f]; like the reference, no gradient flows to edge_w. */
+int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* x,
+                     int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream);
+int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* dy,
+                     int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, void* stream);
+
+/* Gradient of the attention coefficients, which the reference does not compute (MA_Function_GAT.backward returns
+ * None for edge_data, GraphConv.py:227): dw[e, h] = sum over head h's columns f of dy[d, f] * x[src[e], f] for
+ * every edge e of row d.  dw is float32 [n_edges][n_heads] and is zero-filled first. */
+int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x, int64_t ldx,
+                       const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int64_t n_edges, float* dw,
+                       void* stream);
 
 /* Row gather out[i, :] = table[ids[i], :] from a single table (shards = NULL) or a row-sharded one (table may
  * be NULL), as above.  Replaces the CPU index_select + host-to-device copy of load_subtensors

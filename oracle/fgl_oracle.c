@@ -17,6 +17,7 @@
  *   fglo_exclusive_sum   cuda_operators/utilis.cu:17-41
  *   fglo_agg_fwd         cuda_operators/aggregate_acc_kernel.cu:271-331, 376-427
  *   fglo_agg_bwd         cuda_operators/aggregate_acc_kernel.cu:468-517, 555-596
+ *   fglo_agg_edge_fwd/bwd cuda_operators/aggregate_acc_kernel.cu:836-885, 925-979
  *
  * Loops over independent seeds / rows carry an OpenMP pragma so that the
  * CPU baseline can use all host cores; results do not depend on the thread
@@ -235,6 +236,49 @@ void fglo_agg_bwd(int mode, const int32_t* indptr, const int32_t* src, const int
         }
     }
 #pragma omp parallel for
+    for (int32_t s = 0; s < n_src; ++s)
+        for (int32_t f = 0; f < dim; ++f) dx[(int64_t)s * ldx + f] = (float)acc[(size_t)s * (size_t)dim + f];
+    free(acc);
+}
+
+/* ---- edge-weighted multi-head aggregation (GAT; aggregate_acc_kernel.cu:836-885, 925-979) --------------- */
+void fglo_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* x,
+                       int64_t ldx, int32_t dim, int32_t n_dst, int zero_deg_passthrough, float* out, int64_t ldo) {
+    const int32_t unit = dim / n_heads;
+#pragma omp parallel
+    {
+        double* acc = (double*)malloc(sizeof(double) * (size_t)dim);
+#pragma omp for schedule(dynamic, 64)
+        for (int32_t d = 0; d < n_dst; ++d) {
+            float* o = out + (int64_t)d * ldo;
+            if (indptr[d] == indptr[d + 1]) { /* aggregate_acc_kernel.cu:870-872 */
+                for (int32_t f = 0; f < dim; ++f) o[f] = zero_deg_passthrough ? x[(int64_t)d * ldx + f] : 0.0f;
+                continue;
+            }
+            for (int32_t f = 0; f < dim; ++f) acc[f] = 0.0;
+            for (int32_t e = indptr[d]; e < indptr[d + 1]; ++e) {
+                const float* r = x + (int64_t)src[e] * ldx;
+                const float* w = edge_w + (int64_t)e * n_heads;
+                for (int32_t f = 0; f < dim; ++f) acc[f] += (double)w[f / unit] * (double)r[f];
+            }
+            for (int32_t f = 0; f < dim; ++f) o[f] = (float)acc[f];
+        }
+        free(acc);
+    }
+}
+
+void fglo_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* dy,
+                       int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx) {
+    const int32_t unit = dim / n_heads;
+    double* acc = (double*)calloc((size_t)n_src * (size_t)dim, sizeof(double));
+    for (int32_t d = 0; d < n_dst; ++d) {
+        const float* g = dy + (int64_t)d * ldy;
+        for (int32_t e = indptr[d]; e < indptr[d + 1]; ++e) {
+            const float* w = edge_w + (int64_t)e * n_heads;
+            double* a = acc + (size_t)src[e] * (size_t)dim;
+            for (int32_t f = 0; f < dim; ++f) a[f] += (double)w[f / unit] * (double)g[f];
+        }
+    }
     for (int32_t s = 0; s < n_src; ++s)
         for (int32_t f = 0; f < dim; ++f) dx[(int64_t)s * ldx + f] = (float)acc[(size_t)s * (size_t)dim + f];
     free(acc);

@@ -135,3 +135,25 @@ def aggregate_bwd(mode, indptr, src, dy, n_src, src_deg=None, dst_deg=None):
                        ctypes.c_int64(D), ctypes.c_int32(D), ctypes.c_int32(n_dst), ctypes.c_int32(n_src),
                        _p(dx), ctypes.c_int64(D))
     return dx
+
+
+def aggregate_edge_fwd(indptr, src, edge_w, x, n_dst, zero_deg_passthrough=True):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    edge_w = np.ascontiguousarray(edge_w, dtype=np.float32)
+    indptr, src = _i32(indptr), _i32(src)
+    D, H = x.shape[1], edge_w.shape[1]
+    out = np.zeros((n_dst, D), dtype=np.float32)
+    lib().fglo_agg_edge_fwd(_p(indptr), _p(src), _p(edge_w), ctypes.c_int32(H), _p(x), ctypes.c_int64(D), ctypes.c_int32(D),
+                            ctypes.c_int32(n_dst), ctypes.c_int(int(zero_deg_passthrough)), _p(out), ctypes.c_int64(D))
+    return out
+
+
+def aggregate_edge_bwd(indptr, src, edge_w, dy, n_src):
+    dy = np.ascontiguousarray(dy, dtype=np.float32)
+    edge_w = np.ascontiguousarray(edge_w, dtype=np.float32)
+    indptr, src = _i32(indptr), _i32(src)
+    n_dst, D = dy.shape
+    dx = np.zeros((n_src, D), dtype=np.float32)
+    lib().fglo_agg_edge_bwd(_p(indptr), _p(src), _p(edge_w), ctypes.c_int32(edge_w.shape[1]), _p(dy), ctypes.c_int64(D),
+                            ctypes.c_int32(D), ctypes.c_int32(n_dst), ctypes.c_int32(n_src), _p(dx), ctypes.c_int64(D))
+    return dx

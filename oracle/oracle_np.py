@@ -19,6 +19,7 @@ compute when their threads are executed one after another in index order:
 * ``backward_gcn``      cuda_operators/aggregate_acc_kernel.cu:430-517
 * ``forward_gin``       cuda_operators/aggregate_acc_kernel.cu:333-427
 * ``backward_gin``      cuda_operators/aggregate_acc_kernel.cu:519-596
+* ``aggregate_edge_fwd / _bwd``  cuda_operators/aggregate_acc_kernel.cu:789-979 (GAT)
 
 Where the reference leaves a result to thread arrival order (the order of
 the non-seed unique nodes, id_map.cu:317-320) the oracle takes the order a
@@ -245,6 +246,38 @@ def aggregate_bwd(mode, indptr, src, dy, n_src, src_deg=None, dst_deg=None):
         for e in range(int(indptr[d]), int(indptr[d + 1])):
             s = int(src[e])
             dx[s] += _edge_weight(mode, d, s, src_deg, dst_deg, indptr) * dy[d].astype(np.float64)
+    return dx
+
+
+def aggregate_edge_fwd(indptr, src, edge_w, x, n_dst, zero_deg_passthrough=True):
+    """out[d, f] = sum_e edge_w[e, head(f)] * x[src[e], f], head(f) = f // (dim / heads)
+    (aggregate_acc_kernel.cu:836-885; a row without in-edges copies its own input row, :870-872)."""
+    x = np.asarray(x)
+    edge_w = np.asarray(edge_w)
+    D, H = x.shape[1], edge_w.shape[1]
+    head = np.arange(D) // (D // H)
+    out = np.zeros((n_dst, D), dtype=np.float64)
+    for d in range(n_dst):
+        a, b = int(indptr[d]), int(indptr[d + 1])
+        if a == b:
+            if zero_deg_passthrough:
+                out[d] = x[d]
+            continue
+        for e in range(a, b):
+            out[d] += edge_w[e, head].astype(np.float64) * x[int(src[e])].astype(np.float64)
+    return out
+
+
+def aggregate_edge_bwd(indptr, src, edge_w, dy, n_src):
+    """dx[src[e], f] += edge_w[e, head(f)] * dy[d, f] (aggregate_acc_kernel.cu:925-979); no gradient to edge_w."""
+    dy = np.asarray(dy)
+    edge_w = np.asarray(edge_w)
+    n_dst, D = dy.shape
+    head = np.arange(D) // (D // edge_w.shape[1])
+    dx = np.zeros((n_src, D), dtype=np.float64)
+    for d in range(n_dst):
+        for e in range(int(indptr[d]), int(indptr[d + 1])):
+            dx[int(src[e])] += edge_w[e, head].astype(np.float64) * dy[d].astype(np.float64)
     return dx
 
 

@@ -74,5 +74,5 @@ def test_ops_reject_cpu_and_non_contiguous_tensors():
 def test_reference_op_names_are_exposed():
     import fastgl
     for name in ("sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
-                 "forwaed_gin", "backward_gin"):
+                 "forwaed_gin", "backward_gin", "forward_gat", "backward_gat"):
         assert callable(getattr(fastgl, name))

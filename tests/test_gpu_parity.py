@@ -461,6 +461,28 @@ def test_gin_ops_match_oracle(fastgl):
     assert rel_err(d_x.cpu().numpy(), rx) <= 5e-5 and rel_err(d_w.cpu().numpy(), rw) <= 5e-5
 
 
+@pytest.mark.parametrize("dim,heads", [(64, 8), (256, 8), (47, 1), (24, 8), (602, 7)])
+def test_gat_ops_match_oracle(fastgl, dim, heads):
+    rng = np.random.default_rng(dim + heads)
+    n_dst, n_src = 400, 1500
+    indptr, src = random_block(rng, n_dst, n_src, 20)
+    E = int(indptr[-1])
+    x = rng.standard_normal((n_src, dim)).astype(np.float32)
+    w = rng.random((E, heads)).astype(np.float32)
+    g = rng.standard_normal((n_dst, dim)).astype(np.float32)
+    t = [to_dev(a) for a in (indptr, w, src, x, g)]
+    out = fastgl.forward_gat(t[0], t[1], t[2], t[3], 20, n_dst, heads)[0]
+    assert rel_err(out.cpu().numpy(), oc.aggregate_edge_fwd(indptr, src, w, x, n_dst)) <= AGG_RTOL
+    d_x = fastgl.backward_gat(t[0], t[1], t[2], t[4], n_src, heads)[0]
+    assert rel_err(d_x.cpu().numpy(), oc.aggregate_edge_bwd(indptr, src, w, g, n_src)) <= AGG_RTOL
+    # gradient of the coefficients (not in the reference): per edge and head, <dy[d], x[src]> over the head's columns
+    d_w = fastgl.edge_weight_grad(t[0], t[2], t[3], t[4], heads).cpu().numpy()
+    unit = dim // heads
+    dst = np.repeat(np.arange(n_dst), np.diff(indptr))
+    ref = (g[dst].astype(np.float64) * x[src].astype(np.float64)).reshape(E, heads, unit).sum(-1)
+    assert rel_err(d_w, ref) <= AGG_RTOL
+
+
 def test_golden_fixtures_on_gpu(fastgl):
     g = np.load(GOLDEN)
     indptr, indices, seeds = g["indptr"], g["indices"], g["seeds"]

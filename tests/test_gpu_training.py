@@ -101,3 +101,42 @@ def test_cuda_graph_step_matches_the_op_by_op_step(window_layer0):
     for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
         assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
     assert eager.sampled_edges == graphed.sampled_edges
+
+
+def test_gat_layer_matches_a_dense_torch_restatement():
+    """GATConv on the CUDA ops against the same layer written with dense torch algebra (float64), including
+    the gradient of the attention parameters that the reference drops."""
+    from fastgl_b200.block import Block
+    from fastgl_b200.layers import GATConv
+    rng = np.random.default_rng(4)
+    dev = torch.device("cuda", 0)
+    n_dst, n_src, din, dout, heads = 60, 200, 32, 16, 4
+    deg = rng.integers(1, 9, size=n_dst)
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    src = rng.integers(0, n_src, size=int(indptr[-1])).astype(np.int32)
+    dst = np.repeat(np.arange(n_dst), deg)
+    x = torch.from_numpy(rng.standard_normal((n_src, din)).astype(np.float32)).to(dev)
+    blk = Block(torch.from_numpy(indptr).to(dev), torch.from_numpy(src).to(dev), n_src, n_dst)
+    torch.manual_seed(1)
+    layer = GATConv(din, dout, heads, attention_grad=True).to(dev)
+    out = layer(blk, x, 8)
+    target = torch.from_numpy(rng.standard_normal((n_dst, heads * dout)).astype(np.float32)).to(dev)
+    (out * target).sum().backward()
+
+    W = layer.fc.weight.detach().double().cpu().clone().requires_grad_(True)
+    al = layer.attn_l.detach().double().cpu().clone().requires_grad_(True)
+    ar = layer.attn_r.detach().double().cpu().clone().requires_grad_(True)
+    f = (x.double().cpu() @ W.t()).view(-1, heads, dout)
+    el, er = (f * al).sum(-1), (f[:n_dst] * ar).sum(-1)
+    s_idx, d_idx = torch.from_numpy(src.astype(np.int64)), torch.from_numpy(dst)
+    e = torch.nn.functional.leaky_relu(el[s_idx] + er[d_idx], 0.2)
+    A = torch.full((n_dst, len(src), heads), float("-inf"), dtype=torch.float64)
+    A[d_idx, torch.arange(len(src))] = e
+    alpha = torch.softmax(A, dim=1)[d_idx, torch.arange(len(src))]                    # [E, H]
+    ref = torch.zeros((n_dst, heads, dout), dtype=torch.float64).index_add_(0, d_idx, alpha[:, :, None] * f[s_idx])
+    ref = ref.reshape(n_dst, heads * dout)
+    (ref * target.double().cpu()).sum().backward()
+    assert torch.allclose(out.double().cpu(), ref.detach(), rtol=1e-4, atol=1e-5)
+    for got, want in ((layer.fc.weight.grad, W.grad), (layer.attn_l.grad, al.grad), (layer.attn_r.grad, ar.grad)):
+        assert torch.allclose(got.double().cpu(), want, rtol=1e-3, atol=1e-4)

@@ -181,6 +181,31 @@ def test_c_matches_numpy_aggregation(mode):
                        oc.aggregate_bwd(mode, indptr, src, dy, n_src, sdeg, ddeg), rtol=1e-6, atol=1e-6)
 
 
+def test_edge_weighted_aggregation_hand_case_and_restatements_agree():
+    # rows: 0 <- {1, 2}, 1 <- {} (copies its own row), 2 <- {0}; 2 heads over 4 columns
+    indptr = np.array([0, 2, 2, 3], dtype=np.int32)
+    src = np.array([1, 2, 0], dtype=np.int32)
+    x = np.array([[1, 2, 3, 4], [10, 20, 30, 40], [100, 200, 300, 400]], dtype=np.float32)
+    w = np.array([[0.5, 2.0], [0.25, 1.0], [3.0, -1.0]], dtype=np.float32)
+    for mod in (on, oc):
+        out = mod.aggregate_edge_fwd(indptr, src, w, x, 3)
+        assert np.allclose(out, [[5 + 25, 10 + 50, 60 + 300, 80 + 400], [10, 20, 30, 40], [3, 6, -3, -4]])
+        dy = np.ones((3, 4), dtype=np.float32)
+        dx = mod.aggregate_edge_bwd(indptr, src, w, dy, 3)
+        assert np.allclose(dx, [[3, 3, -1, -1], [0.5, 0.5, 2, 2], [0.25, 0.25, 1, 1]])
+    rng = np.random.default_rng(8)
+    n_dst, n_src, D, H = 50, 120, 24, 8
+    deg = rng.integers(0, 7, size=n_dst)
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    src = rng.integers(0, n_src, size=indptr[-1]).astype(np.int32)
+    x = rng.standard_normal((n_src, D)).astype(np.float32)
+    w = rng.random((indptr[-1], H)).astype(np.float32)
+    dy = rng.standard_normal((n_dst, D)).astype(np.float32)
+    assert np.allclose(on.aggregate_edge_fwd(indptr, src, w, x, n_dst), oc.aggregate_edge_fwd(indptr, src, w, x, n_dst), rtol=1e-6, atol=1e-6)
+    assert np.allclose(on.aggregate_edge_bwd(indptr, src, w, dy, n_src), oc.aggregate_edge_bwd(indptr, src, w, dy, n_src), rtol=1e-6, atol=1e-6)
+
+
 def test_gcn_gin_ops_are_adjoint_consistent():
     # <forward(x), dy> == <x, backward(dy)> for the linear aggregation (rows with in-edges only)
     rng = np.random.default_rng(5)
