@@ -59,7 +59,7 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -74,7 +74,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                          "-lms", "50", "-i", str(self.gpu_index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -207,8 +207,8 @@ def time_cpu_steps(step, n_steps):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=48)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=192)
+    ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="fastgl", choices=["fastgl", "reference"])
     ap.add_argument("--config", default="products-like", choices=sorted(CONFIGS))
     ap.add_argument("--window", type=int, default=8, help="mini-batches sampled per kernel launch")
@@ -400,9 +400,10 @@ def main():
     if rank == 0:
         steps_per_epoch = tr.steps_per_epoch()
         # kernels of this library: per window one fused sampling launch and one first-layer aggregation launch,
-        # per step 2 forward + 2 backward aggregations of the inner layers (the backward ones with a memset)
+        # per step one staging launch and (inside the replayed graph) one forward + one backward aggregation for
+        # every inner layer
         n_windows = (args.steps + args.window - 1) // args.window
-        launches = args.steps * 2 * (len(cfg["fanouts"]) - 1) + 2 * n_windows
+        launches = args.steps * (1 + 2 * (len(cfg["fanouts"]) - 1)) + 2 * n_windows
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_json,

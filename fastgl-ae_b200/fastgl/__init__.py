@@ -32,7 +32,7 @@ from ._capi import (AGG_MEAN, AGG_SUM, AGG_SYMNORM, COUNTS_STRIDE, FLAG_MAP_ARRI
 __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
-    "sample_map_fused", "fused_capacity", "stage_segments", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
+    "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -555,7 +555,13 @@ class FusedBatch:
     def counts_host(self) -> torch.Tensor:
         if self._counts_host is None:
             self._counts_host = self.counts.cpu()
+            self._counts_list = self._counts_host.tolist()
         return self._counts_host
+
+    def counts_list(self):
+        """The counts as nested Python lists (one read-back per window)."""
+        self.counts_host()
+        return self._counts_list
 
     def blocks(self, b: int):
         """Blocks of mini-batch ``b``, input layer first (the order FusedMapSampler.sample_blocks returns):
@@ -659,6 +665,23 @@ def stage_segments(copies, words_dst=None, words=()):
     vals = (ctypes.c_int32 * max(1, len(words)))(*[int(w) for w in words])
     with _on_device(dev):
         rc = lib().fgl_stage_segments(segs, ctypes.c_int32(n), _ptr(words_dst), vals, ctypes.c_int32(len(words)), _stream(dev))
+    _raise(rc, "stage_segments")
+
+
+def stage_segments_raw(segments, words_dst_ptr, words, device):
+    """``stage_segments`` for callers that already hold raw addresses: ``segments`` is a list of
+    ``(dst_ptr, src_ptr, n_bytes)`` (addresses and sizes multiples of 4), ``words`` go to ``words_dst_ptr``.  No
+    tensor views are built, which matters when this runs once per training step."""
+    n = len(segments)
+    if n > _capi.MAX_SEGMENTS or len(words) > _capi.MAX_SEGMENTS:
+        raise RuntimeError("at most 8 copies and 8 words per call")
+    segs = (_capi.Segment * max(1, n))()
+    for i, (d, s_, nbytes) in enumerate(segments):
+        segs[i].dst, segs[i].src, segs[i].bytes = d, s_, nbytes
+    vals = (ctypes.c_int32 * max(1, len(words)))(*words)
+    with _on_device(device):
+        rc = lib().fgl_stage_segments(segs, ctypes.c_int32(n), ctypes.c_void_p(words_dst_ptr), vals,
+                                      ctypes.c_int32(len(words)), _stream(device))
     _raise(rc, "stage_segments")
 
 

@@ -90,16 +90,20 @@ class GraphedStep:
         return all(int(counts_row[L - 1 - i]) <= self.pad_dst[i] for i in range(L))
 
     def stage(self, fb, b, counts_row, layer0):
-        """Copy mini-batch ``b`` of the window into the static buffers (one kernel launch)."""
+        """Copy mini-batch ``b`` of the window into the static buffers (one kernel launch; addresses are computed
+        here so that no tensor views are created per step)."""
         L = self.L
         buf, row_off = layer0
         n_dst = [int(counts_row[L - 1 - i]) for i in range(L)]
-        copies = [(self.x0, buf[row_off[b]: row_off[b] + n_dst[0]]), (self.seeds, fb.nodes[b, : self.tr.batch_size])]
+        row_bytes = buf.stride(0) * 4
+        segs = [(self.x0.data_ptr(), buf.data_ptr() + row_off[b] * row_bytes, n_dst[0] * row_bytes),
+                (self.seeds.data_ptr(), fb.nodes.data_ptr() + b * fb.nodes.stride(0) * 4, self.tr.batch_size * 4)]
         for i in range(1, L):
             h = L - 1 - i
-            copies.append((self.blocks[i].indptr, fb.block_indptr[h][b, : n_dst[i] + 1]))
-            copies.append((self.blocks[i].src, fb.block_src[h][b, : int(counts_row[8 + h])]))
-        fastgl.stage_segments(copies, self.sizes, n_dst)
+            ptr, src = fb.block_indptr[h], fb.block_src[h]
+            segs.append((self.blocks[i].indptr.data_ptr(), ptr.data_ptr() + b * ptr.stride(0) * 4, (n_dst[i] + 1) * 4))
+            segs.append((self.blocks[i].src.data_ptr(), src.data_ptr() + b * src.stride(0) * 4, int(counts_row[8 + h]) * 4))
+        fastgl.stage_segments_raw(segs, self.sizes.data_ptr(), n_dst, self.tr.dev)
 
     def _body(self):
         tr = self.tr
@@ -165,6 +169,7 @@ class Trainer:
         self.sampled_edges = 0
         self.last_loss = None
         self.layer0_events = []   # (start, end, block | window) of the first-layer aggregation, when timed
+        self._loss_host = None
         self.sample_events = []   # (start, end, n_batches) of the fused sampling launches, when timed
         self.time_layer0 = False
         # The first layer's [self | neighbour-mean] rows do not depend on the weights, so they are produced for
@@ -185,7 +190,7 @@ class Trainer:
 
     def _graph_step(self, fb, b, layer0):
         """Replay the captured step for batch ``b``; returns None when the batch does not fit the padded shapes."""
-        counts_row = fb.counts_host()[b]
+        counts_row = fb.counts_list()[b]
         L = len(self.fanouts)
         if self.graphed is None:
             if int(counts_row[0]) != self.batch_size:
@@ -246,8 +251,8 @@ class Trainer:
         if self.use_graph and layer0 is not None and labels_of is None:
             loss = self._graph_step(fb, b, layer0)
             if loss is not None:
-                c = fb.counts_host()[b]
-                self.sampled_edges += int(c[8: 8 + len(self.fanouts)].sum())
+                c = fb.counts_list()[b]
+                self.sampled_edges += sum(c[8: 8 + len(self.fanouts)])
                 self.last_loss = loss
                 return loss
         input_nodes, blocks = self.sampler.window_blocks(fb, b)
@@ -277,6 +282,11 @@ class Trainer:
         window copy its seeds from the host inside the loop; ``read_loss_each_step`` reads the loss back per step."""
         done = 0
         losses = []
+        # the loss of every step goes to pinned host memory with an asynchronous copy; it is read one step later,
+        # after the next step has been enqueued, so the read-back does not drain the GPU
+        pending = None
+        if read_loss_each_step and self._loss_host is None:
+            self._loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
         while done < n_steps:
             nb = min(self.window, n_steps - done)
             if host_seeds is not None:
@@ -300,6 +310,16 @@ class Trainer:
             for b in order:
                 loss = self.train_batch(fb, b, layer0=layer0)
                 if read_loss_each_step:
-                    losses.append(float(loss.item()))
+                    slot = len(losses) & 1 if pending is None else 1 - pending[1]
+                    self._loss_host[slot: slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    if pending is not None:
+                        pending[0].synchronize()
+                        losses.append(float(self._loss_host[pending[1]]))
+                    pending = (ev, slot)
             done += nb
+        if pending is not None:
+            pending[0].synchronize()
+            losses.append(float(self._loss_host[pending[1]]))
         return losses
