@@ -356,8 +356,8 @@ def main():
         roofline.update({"achieved": achieved, "frac": achieved / peak, "algorithmic_bytes_per_launch": alg,
                          "launch_ms": mean_ms, "launches_timed": len(agg_ms)})
         if args.config == "products-like" and args.window == 8:
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
-            # ncu capture summarised in profiles/agg_fwd_kernel_window_products-like.md
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, taken from
+            # an ncu capture (ncu --set full) of the same command
             roofline["traffic"] = 744.6e6
         smp = [s.elapsed_time(e) for s, e, nb in tr.sample_events if nb == args.window]
         if smp:
