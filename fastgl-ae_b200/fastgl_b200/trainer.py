@@ -51,8 +51,11 @@ class FlatGrads:
 
     def all_reduce(self, world: int):
         if world > 1:
-            dist.all_reduce(self.buffer)
-            self.buffer.div_(world)
+            if dist.get_backend() == "nccl":
+                dist.all_reduce(self.buffer, op=dist.ReduceOp.AVG)   # one kernel: sum and scale
+            else:
+                dist.all_reduce(self.buffer)
+                self.buffer.div_(world)
 
 
 class GraphedStep:

@@ -254,6 +254,14 @@ def test_fused_int32_indptr_single_batch_two_hops(fastgl, graph):
     run_fused_and_compare(fastgl, indptr, indices, seeds, [10, 25], False, 0, ptr_dtype=torch.int32)
 
 
+def test_fused_wide_fanout_uses_the_warp_per_seed_path(fastgl, graph):
+    # fanouts above 32 take the warp-per-seed sampler inside the fused kernel; the hub (node 0) has 3000+ neighbours
+    indptr, indices = graph
+    seeds = [np.concatenate([[0], np.arange(500, 563)]).astype(np.int32), np.arange(900, 964, dtype=np.int32)]
+    run_fused_and_compare(fastgl, indptr, indices, seeds, [40, 3], False, 2)
+    run_fused_and_compare(fastgl, indptr, indices, seeds, [3, 64], True, 1)
+
+
 def test_fused_frontier_saturates_small_graph(fastgl):
     # the frontier reaches every node: capacities are clamped by the node count
     indptr, indices = make_graph(600, 10, seed=2, hub=100)
