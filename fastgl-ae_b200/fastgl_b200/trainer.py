@@ -10,6 +10,7 @@ window, and trains batch by batch.  The only collective is one all-reduce of the
 from __future__ import annotations
 
 import math
+from concurrent.futures import ThreadPoolExecutor
 
 import torch
 import torch.distributed as dist
@@ -77,6 +78,7 @@ class GraphedStep:
         self.x0 = torch.zeros((self.pad_dst[0], 2 * D), dtype=torch.float32, device=dev)
         self.sizes = torch.zeros(8, dtype=torch.int32, device=dev)
         self.seeds = torch.zeros(tr.batch_size, dtype=torch.int32, device=dev)
+        self.row_ids = torch.arange(tr.batch_size, dtype=torch.int32, device=dev)
         self.blocks = [None]
         for i in range(1, L):
             ptr = torch.zeros(self.pad_dst[i] + 1, dtype=torch.int32, device=dev)
@@ -84,12 +86,13 @@ class GraphedStep:
             self.blocks.append(Block(ptr, src, self.pad_dst[i - 1], self.pad_dst[i], n_dst_dev=self.sizes[i: i + 1]))
         self.graph = None
         self.loss = None
+        # Data-parallel runs keep the gradient all-reduce between two graphs (forward/backward, optimizer step):
+        # every rank then issues the collective the same way whether or not its batch fitted the padded shapes.
         self.step_in_graph = tr.world == 1
+        self.opt_graph = None
 
     def fits(self, counts_row) -> bool:
         L = self.L
-        if int(counts_row[0]) != self.tr.batch_size:
-            return False
         return all(int(counts_row[L - 1 - i]) <= self.pad_dst[i] for i in range(L))
 
     def stage(self, fb, b, counts_row, layer0):
@@ -100,7 +103,8 @@ class GraphedStep:
         n_dst = [int(counts_row[L - 1 - i]) for i in range(L)]
         row_bytes = buf.stride(0) * 4
         segs = [(self.x0.data_ptr(), buf.data_ptr() + row_off[b] * row_bytes, n_dst[0] * row_bytes),
-                (self.seeds.data_ptr(), fb.nodes.data_ptr() + b * fb.nodes.stride(0) * 4, self.tr.batch_size * 4)]
+                # only the batch's own seeds: the rows after a short batch keep earlier (valid) node ids
+                (self.seeds.data_ptr(), fb.nodes.data_ptr() + b * fb.nodes.stride(0) * 4, n_dst[L - 1] * 4)]
         for i in range(1, L):
             h = L - 1 - i
             ptr, src = fb.block_indptr[h], fb.block_src[h]
@@ -108,15 +112,15 @@ class GraphedStep:
             segs.append((self.blocks[i].src.data_ptr(), src.data_ptr() + b * src.stride(0) * 4, int(counts_row[8 + h]) * 4))
         fastgl.stage_segments_raw(segs, self.sizes.data_ptr(), n_dst, self.tr.dev)
 
-    def _body(self):
+    def _forward_backward(self):
         tr = self.tr
         y = tr.labels[self.seeds.long()]
+        # a short last batch of an epoch fills only the first sizes[L-1] rows: the others are left out of the mean
+        y = torch.where(self.row_ids < self.sizes[self.L - 1], y, -100)
         logits = tr.model(self.blocks, None, layer0=self.x0)
-        loss = F.cross_entropy(logits, y)
+        loss = F.cross_entropy(logits, y, ignore_index=-100)
         tr.grads.zero()
         loss.backward()
-        if self.step_in_graph:
-            tr.opt.step()
         return loss
 
     def capture(self):
@@ -127,21 +131,28 @@ class GraphedStep:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(3):
-                self._body()
+                self._forward_backward()
+                tr.opt.step()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        # undo the warm-up steps in place: the graph must capture the very tensors the optimizer will keep using
+        # undo the warm-up steps in place: the graphs must capture the very tensors the optimizer will keep using
         tr.model.load_state_dict(model_state)
         tr.zero_optimizer_state()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.loss = self._body()
+            self.loss = self._forward_backward()
+            if self.step_in_graph:
+                tr.opt.step()
+        if not self.step_in_graph:
+            self.opt_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.opt_graph):
+                tr.opt.step()
 
     def replay(self):
         self.graph.replay()
         if not self.step_in_graph:
             self.tr.grads.all_reduce(self.tr.world)
-            self.tr.opt.step()
+            self.opt_graph.replay()
         return self.loss
 
 
@@ -167,6 +178,9 @@ class Trainer:
         self.graph_fallbacks = 0
         self.reset_optimizer()
         self.train_nids = train_nids
+        self._train_nids_host = train_nids.cpu()
+        self._shuffler = ThreadPoolExecutor(max_workers=1)
+        self._next_seeds = None
         self.epoch = 0
         self._set_epoch_seeds()
         self.sampled_edges = 0
@@ -196,8 +210,6 @@ class Trainer:
         counts_row = fb.counts_list()[b]
         L = len(self.fanouts)
         if self.graphed is None:
-            if int(counts_row[0]) != self.batch_size:
-                return None
             pad = []
             for i in range(L):
                 n = int(fb.counts_host()[:, L - 1 - i].max())
@@ -211,8 +223,15 @@ class Trainer:
         self.graphed.stage(fb, b, counts_row, layer0)
         return self.graphed.replay()
 
+    def _shuffled_share(self, epoch: int) -> torch.Tensor:
+        return shard_seeds(self._train_nids_host, self.rank, self.world, 12345 + epoch)   # host only: no CUDA call
+
     def _set_epoch_seeds(self):
-        self.my_seeds = shard_seeds(self.train_nids, self.rank, self.world, 12345 + self.epoch)
+        """This epoch's share of the shuffled seeds.  The shuffle is a host permutation (the same on every rank
+        and on any device); the next epoch's is drawn on a worker thread while this epoch trains."""
+        share = self._next_seeds.result() if self._next_seeds is not None else self._shuffled_share(self.epoch)
+        self.my_seeds = share.to(self.dev)
+        self._next_seeds = self._shuffler.submit(self._shuffled_share, self.epoch + 1)
         self.cursor = 0
 
     def steps_per_epoch(self) -> int:

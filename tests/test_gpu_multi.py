@@ -1,6 +1,6 @@
-"""Two-GPU test of the row-sharded feature table: every rank keeps half of the rows, opens the other half
-through CUDA IPC, and gathers / aggregates rows that live on both GPUs with peer loads.  Skipped on boxes with
-one GPU.  Ranks are child processes; a rank only leaves between steps (after the final barrier)."""
+"""Two-GPU tests.  (1) The row-sharded feature table: every rank keeps half of the rows, opens the other half
+through CUDA IPC, and gathers / aggregates rows that live on both GPUs with peer loads.  (2) Data-parallel
+training over NCCL with the step replayed from CUDA graphs.  Skipped on boxes with one GPU.  Ranks are child processes; a rank only leaves between steps (after the final barrier)."""
 import os
 import socket
 
@@ -60,3 +60,53 @@ def _worker(rank, world, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_sharded_feature_table_over_two_gpus():
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _train_worker(rank, world, port):
+    """Two data-parallel ranks over NCCL: the step replayed from CUDA graphs (forward/backward, then the all-reduce,
+    then the optimizer step) must train like the op-by-op step, across an epoch boundary with its short last
+    batch, and keep the replicas identical."""
+    from conftest import make_graph
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        n = 6000
+        indptr, indices = make_graph(n, 14, seed=9, hub=400)
+        rng = np.random.default_rng(9)
+        feat = torch.from_numpy(rng.standard_normal((n, 100)).astype(np.float32)).to(dev)
+        labels = torch.from_numpy(rng.integers(0, 7, n)).to(dev)
+        train = torch.from_numpy(np.sort(rng.choice(n, size=n // 2, replace=False)).astype(np.int32)).to(dev)
+        runs = []
+        for graph in (False, True):
+            torch.manual_seed(3)
+            model = GraphSAGE(100, 32, 7, 3, dropout=0.0).to(dev)
+            tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), feat, labels, train, model,
+                         [15, 10, 5], batch_size=256, window=4, cuda_graph=graph, rank=rank, world=world)
+            assert tr.steps_per_epoch() == 6                  # 1500 seeds per rank: five full batches and one of 220
+            losses = tr.run_steps(14, read_loss_each_step=True)
+            runs.append((losses, [p.detach().clone() for p in model.parameters()], tr))
+        (le, pe, _), (lg, pg, tg) = runs
+        assert tg.graphed is not None and tg.graphed.opt_graph is not None and tg.graph_fallbacks <= 2
+        assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
+        for a, b in zip(pe, pg):
+            assert torch.allclose(a, b, rtol=1e-3, atol=1e-4)
+        flat = torch.cat([p.flatten() for p in pg])
+        both = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(both, flat)
+        assert torch.equal(both[0], both[1])                  # the replicas stay bit-identical
+        torch.cuda.synchronize()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_data_parallel_graph_step_over_two_gpus():
+    mp.spawn(_train_worker, args=(2, _free_port()), nprocs=2, join=True)

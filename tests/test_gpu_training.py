@@ -103,6 +103,22 @@ def test_cuda_graph_step_matches_the_op_by_op_step(window_layer0):
     assert eager.sampled_edges == graphed.sampled_edges
 
 
+def test_cuda_graph_step_takes_the_short_last_batch_of_an_epoch():
+    """3000 training seeds in batches of 256: the twelfth batch has 184 seeds and is replayed through the same
+    graph (its missing rows are left out of the loss); the run continues into the next epoch's shuffle."""
+    problem = setup_problem(seed=9)
+    eager = make_trainer(problem, cuda_graph=False)
+    graphed = make_trainer(problem, cuda_graph=True)
+    assert eager.steps_per_epoch() == 12
+    le = eager.run_steps(16, read_loss_each_step=True)
+    lg = graphed.run_steps(16, read_loss_each_step=True)
+    assert graphed.graph_fallbacks == 0 and graphed.epoch == 1
+    assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
+    for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+    assert eager.sampled_edges == graphed.sampled_edges
+
+
 def test_gat_layer_matches_a_dense_torch_restatement():
     """GATConv on the CUDA ops against the same layer written with dense torch algebra (float64), including
     the gradient of the attention parameters that the reference drops."""
