@@ -204,6 +204,34 @@ def time_cpu_steps(step, n_steps):
 
 
 # ----------------------------------------------------------------------------------------------------------
+def run_gates(cfg, args, indptr, indices, feat, train, device):
+    """Sample one window of the workload and check it (raises on a violated gate)."""
+    import fastgl
+    from fastgl_b200.checks import EdgeKeys, check_window, check_window_aggregation
+    nb, batch = args.window, cfg["batch"]
+    if train.numel() < nb * batch:
+        nb = max(1, train.numel() // batch)
+    seeds = train[: nb * batch].to(torch.int32).view(nb, batch).contiguous()
+    counts = torch.full((nb,), batch, dtype=torch.int32, device=device)
+    fan_s = list(reversed(cfg["fanouts"]))
+    fb = fastgl.sample_map_fused(indptr, indices, seeds, counts, fan_s, replace=False, rng_seed=12345, rng_ctr=1 << 40)
+    fastgl.check_status(device)
+    keys = EdgeKeys(indptr, indices)
+    seen = check_window(fb, indptr, indices, seeds, [batch] * nb, replace=False, edge_keys=keys)
+    del keys
+    out = {"window_checked": seen, "status": "ok"}
+    if cfg.get("model") != "gcn" and torch.is_tensor(feat):
+        hop, D = len(fan_s) - 1, feat.size(1)
+        total = int(fb.counts_host()[:, hop].sum())
+        buf = torch.empty((total, 2 * D), dtype=torch.float32, device=device)
+        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, feat, buf[:, D:], self_out=buf[:, :D])
+        out["window_aggregation_rel_err"] = check_window_aggregation(fb, hop, feat, buf, row_off)
+        del buf
+    del fb
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,6 +326,10 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
+
+    # --- correctness gates on one window of this very workload (untimed): the size-independent properties of
+    #     the sampled blocks and, for the SAGE first layer, the window aggregation against float64 torch algebra
+    gates = run_gates(cfg, args, indptr, indices, feat, train, device)
 
     # --- warm-up, then the device-resident timed region ---------------------------------------------------
     tr.run_steps(args.warmup)
@@ -413,7 +445,7 @@ def main():
                 "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": cfg["batch"] * 4 + 4, "d2h_bytes_per_step": 4 + 64},
                 "gpu_launches": launches * world, "roofline": roofline, "roofline_sample_map": sample_roofline,
-                "clocks": clock_info}
+                "gates": gates, "clocks": clock_info}
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line))
