@@ -248,6 +248,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the per-batch step op by op instead of a CUDA graph")
     ap.add_argument("--cpu-steps", type=int, default=3, help="mini-batches of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gates", action="store_true", help="skip the untimed correctness gates (profiler runs)")
+    ap.add_argument("--kernels", action="store_true",
+                    help="print a per-kernel table (time, algorithmic bytes, fraction of the HBM peak) instead of training")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     args.warmup = max(args.warmup, 3) if args.impl == "fastgl" else args.warmup
@@ -304,6 +307,15 @@ def main():
         model = GCN(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
     else:
         model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
+    if args.kernels:
+        # per-kernel roofline table on blocks of this workload (one GPU; no training)
+        from fastgl_b200 import kernel_bench
+        if world > 1 or not torch.is_tensor(feat):
+            raise SystemExit("--kernels runs on one GPU with a dense feature table")
+        peak, peak_kind = load_peaks()
+        table = kernel_bench.run(indptr, indices, feat, train, cfg["fanouts"], cfg["batch"], args.window, peak)
+        print(json.dumps({"kernels": table, "peak_gb_per_s": peak, "peak_kind": peak_kind, "config": config_json}))
+        return
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
                  reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph)
@@ -329,7 +341,7 @@ def main():
 
     # --- correctness gates on one window of this very workload (untimed): the size-independent properties of
     #     the sampled blocks and, for the SAGE first layer, the window aggregation against float64 torch algebra
-    gates = run_gates(cfg, args, indptr, indices, feat, train, device)
+    gates = None if args.no_gates else run_gates(cfg, args, indptr, indices, feat, train, device)
 
     # --- warm-up, then the device-resident timed region ---------------------------------------------------
     tr.run_steps(args.warmup)

@@ -441,6 +441,26 @@ static void launch_bwd_mode(int mode, const AggParams& p, int grid, cudaStream_t
     if (mode == FGL_AGG_EDGE) launch_bwd_nacc<VEC, FGL_AGG_EDGE>(p, grid, st);
 }
 
+// dx[r, :] = dy_self[r, :] for r < n_dst, 0 for n_dst <= r < n_src (start value of the scatter of a layer with a
+// self term).  Scalar columns: the two matrices may have different alignment.
+__global__ void __launch_bounds__(256)
+init_self_rows_kernel(float* __restrict__ dx, int64_t ldx, const float* __restrict__ dy_self, int64_t ld_self, int dim,
+                      int n_dst, int n_src) {
+    const int groups = (dim + 3) / 4;
+    const int64_t total = (int64_t)n_src * groups;
+    const bool vec = dim % 4 == 0 && ldx % 4 == 0 && ld_self % 4 == 0 && (((uintptr_t)dx | (uintptr_t)dy_self) & 15) == 0;
+    for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = g / groups;
+        const int c = (int)(g - r * groups) * 4;
+        if (vec) {
+            const float4 v = r < n_dst ? *reinterpret_cast<const float4*>(dy_self + r * ld_self + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(dx + r * ldx + c) = v;
+        } else {
+            for (int j = c; j < c + 4 && j < dim; ++j) dx[r * ldx + j] = r < n_dst ? dy_self[r * ld_self + j] : 0.f;
+        }
+    }
+}
+
 }  // namespace fgl
 
 using namespace fgl;
@@ -624,16 +644,24 @@ int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
-                const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
-                const int32_t* n_dst_dev, void* stream) {
+static int agg_bwd_impl(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                        const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
+                        int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
+                        void* stream) {
     if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || n_src < 0 || dim < 1 || ldy < dim || ldx < dim)
         return FGL_ERR_INVALID;
+    if (dy_self && (ld_self < dim || n_dst > n_src)) return FGL_ERR_INVALID;
     if (n_src == 0) return FGL_OK;
     if (!dx) return FGL_ERR_INVALID;
     cudaStream_t st = (cudaStream_t)stream;
-    if (cudaMemset2DAsync(dx, sizeof(float) * (size_t)ldx, 0, sizeof(float) * (size_t)dim, (size_t)n_src, st) != cudaSuccess)
+    if (dy_self && n_dst > 0) {
+        const int64_t items = (int64_t)n_src * ((dim + 3) / 4);
+        const int grid = (int)std::min<int64_t>((items + 255) / 256, 148 * 16);
+        init_self_rows_kernel<<<grid, 256, 0, st>>>(dx, ldx, dy_self, ld_self, dim, n_dst, n_src);
+    } else if (cudaMemset2DAsync(dx, sizeof(float) * (size_t)ldx, 0, sizeof(float) * (size_t)dim, (size_t)n_src, st) !=
+               cudaSuccess) {
         return FGL_ERR_CUDA;
+    }
     if (n_dst == 0) return FGL_OK;
     if (!indptr || !dy) return FGL_ERR_INVALID;
     if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
@@ -657,6 +685,22 @@ int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const i
         default: launch_bwd_mode<1>(mode, p, grid, st); break;
     }
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
+                const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
+                const int32_t* n_dst_dev, void* stream) {
+    return agg_bwd_impl(mode, indptr, src, src_deg, dst_deg, dy, ldy, nullptr, 0, dim, n_dst, n_src, dx, ldx, n_dst_dev,
+                        stream);
+}
+
+int fgl_agg_bwd_self(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                     const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
+                     int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
+                     void* stream) {
+    if (!dy_self && n_dst > 0) return FGL_ERR_INVALID;
+    return agg_bwd_impl(mode, indptr, src, src_deg, dst_deg, dy, ldy, dy_self, ld_self, dim, n_dst, n_src, dx, ldx,
+                        n_dst_dev, stream);
 }
 
 }  // extern "C"

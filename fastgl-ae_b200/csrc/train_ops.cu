@@ -1,0 +1,287 @@
+// Element-wise kernels of the training step around the aggregation path: the bias / ReLU / dropout epilogue
+// of a dense layer and its backward (with the bias gradient), softmax cross-entropy with its gradient, and
+// Adam over one flat parameter buffer.  The reference leaves all of these to PyTorch op by op
+// (GraphConv.py:86-99, train_fastgl.py:366-372); here each is one launch, so that a captured training step
+// is a few dozen kernels instead of a few hundred.  All are HBM/L2-bound streaming kernels: 128-bit accesses,
+// grid sized from the element count, no shared-memory staging needed.
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "fastgl_b200.h"
+
+namespace fgl {
+
+constexpr int kEwThreads = 256;
+
+// Dropout decision of element e = row * dim + column: word (e & 3) of the Philox4x32-10 block whose counter is
+// (lo32(e >> 2), hi32(e >> 2), lo32(ctr), hi32(ctr)) under the key (lo32(seed), hi32(seed)).
+__device__ __forceinline__ uint4 dropout_block(uint64_t seed, uint64_t ctr, uint64_t group) {
+    return philox_block(seed, ctr, (uint32_t)(group >> 32), (uint32_t)group);
+}
+
+// y = dropout(relu(y + bias)), in place.  VEC = 4: dim % 4 == 0, ld % 4 == 0, 16-byte aligned base.
+template <int VEC>
+__global__ void __launch_bounds__(kEwThreads)
+bias_relu_dropout_kernel(float* __restrict__ y, int64_t ld, int64_t n_rows, int dim, const float* __restrict__ bias,
+                         uint32_t drop_below, float keep_scale, uint64_t rng_seed, uint64_t rng_ctr,
+                         const int32_t* __restrict__ rng_ctr_dev, int flags) {
+    const int64_t groups_per_row = dim / VEC;
+    const int64_t total = n_rows * groups_per_row;
+    const uint64_t ctr = rng_ctr + (rng_ctr_dev ? (uint64_t)(uint32_t)rng_ctr_dev[0] : 0ull);
+    const bool relu = flags & FGL_EW_RELU, drop = drop_below != 0;
+    for (int64_t g = (int64_t)blockIdx.x * kEwThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kEwThreads) {
+        const int64_t r = g / groups_per_row;
+        const int c = (int)(g - r * groups_per_row) * VEC;
+        float* p = y + r * ld + c;
+        if (VEC == 4) {
+            float4 v = *reinterpret_cast<float4*>(p);
+            const float4 b = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            if (relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+            if (drop) {
+                // element index e = r * dim + c is a multiple of 4: one Philox block serves the four columns
+                const uint4 w = dropout_block(rng_seed, ctr, (uint64_t)(r * dim + c) >> 2);
+                v.x = w.x < drop_below ? 0.f : v.x * keep_scale;
+                v.y = w.y < drop_below ? 0.f : v.y * keep_scale;
+                v.z = w.z < drop_below ? 0.f : v.z * keep_scale;
+                v.w = w.w < drop_below ? 0.f : v.w * keep_scale;
+            }
+            *reinterpret_cast<float4*>(p) = v;
+        } else {
+            float v = *p + (bias ? bias[c] : 0.f);
+            if (relu) v = fmaxf(v, 0.f);
+            if (drop) {
+                const uint64_t e = (uint64_t)(r * dim + c);
+                const uint32_t w = philox_word(dropout_block(rng_seed, ctr, e >> 2), (int)(e & 3));
+                v = w < drop_below ? 0.f : v * keep_scale;
+            }
+            *p = v;
+        }
+    }
+}
+
+// dz = dy * (mask ? (out > 0 ? keep_scale : 0) : 1), in place over dy; dbias[c] += sum over rows of dz[:, c].
+// A CTA owns a band of consecutive rows; thread t owns columns t, t + blockDim, ... so the column sums stay in
+// registers and leave with one atomic per column per CTA.  Rows are taken eight at a time with all sixteen loads
+// issued before the first store, so that the band is bandwidth- rather than latency-bound.
+constexpr int kBwdMaxColsPerThread = 8;   // dim <= 8 * 256
+constexpr int kBwdRowBatch = 8;
+
+__global__ void __launch_bounds__(kEwThreads)
+relu_dropout_bwd_kernel(float* __restrict__ dy, int64_t ldy, const float* __restrict__ out, int64_t ldo, int64_t n_rows,
+                        int rows_per_cta, int dim, float keep_scale, float* __restrict__ dbias, int flags) {
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < n_rows ? r0 + rows_per_cta : n_rows;
+    const bool mask = flags & FGL_EW_RELU;
+    for (int c = threadIdx.x; c < dim; c += kEwThreads) {
+        float acc = 0.f;
+        for (int64_t r = r0; r < r1; r += kBwdRowBatch) {
+            float g[kBwdRowBatch], o[kBwdRowBatch];
+#pragma unroll
+            for (int k = 0; k < kBwdRowBatch; ++k) {
+                const bool in = r + k < r1;
+                g[k] = in ? dy[(r + k) * ldy + c] : 0.f;
+                o[k] = (in && mask) ? out[(r + k) * ldo + c] : 1.f;
+            }
+#pragma unroll
+            for (int k = 0; k < kBwdRowBatch; ++k) {
+                if (mask) {
+                    g[k] = o[k] > 0.f ? g[k] * keep_scale : 0.f;
+                    if (r + k < r1) dy[(r + k) * ldy + c] = g[k];
+                }
+                acc += g[k];
+            }
+        }
+        if (dbias && acc != 0.f) atomicAdd(dbias + c, acc);
+    }
+}
+
+// Mean softmax cross-entropy over the first n_valid rows, and its gradient; a warp per row.
+// row_loss[r] = logsumexp(z_r) - z_r[label_r] (0 for rows that do not count);
+// dlogits[r, c] = (softmax(z_r)[c] - [c == label_r]) / n_valid for r < n_valid and 0 below.
+constexpr int kXentWarps = 8;
+
+__global__ void __launch_bounds__(kXentWarps * 32)
+softmax_xent_rows_kernel(const float* __restrict__ logits, int64_t ld, const int64_t* __restrict__ labels,
+                         const int32_t* __restrict__ label_ids, int64_t n_labels, int n_rows, int n_classes,
+                         const int32_t* __restrict__ n_valid_dev, int n_valid_host, float* __restrict__ row_loss,
+                         float* __restrict__ dlogits, int64_t ldd, int32_t* __restrict__ status) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * kXentWarps + warp;
+    if (r >= n_rows) return;
+    int n_valid = n_valid_dev ? n_valid_dev[0] : n_valid_host;
+    n_valid = n_valid < 0 ? 0 : (n_valid > n_rows ? n_rows : n_valid);
+    const float inv = n_valid > 0 ? 1.f / (float)n_valid : 0.f;
+    const float* z = logits + (int64_t)r * ld;
+    float* d = dlogits + (int64_t)r * ldd;
+    float mine = 0.f;
+    bool counted = false;
+    if (r < n_valid) {
+        const int64_t at = label_ids ? (int64_t)label_ids[r] : (int64_t)r;
+        const int64_t label = at >= 0 && at < n_labels ? labels[at] : -1;
+        if (label < 0 || label >= n_classes) {
+            if (lane == 0) atomicCAS(status, FGL_OK, FGL_ERR_BOUNDS);
+        } else {
+            counted = true;
+            float m = -INFINITY;
+            for (int c = lane; c < n_classes; c += 32) m = fmaxf(m, z[c]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            float s = 0.f;
+            for (int c = lane; c < n_classes; c += 32) s += expf(z[c] - m);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            mine = m + logf(s) - z[label];
+            const float rs = inv / s;
+            for (int c = lane; c < n_classes; c += 32) d[c] = expf(z[c] - m) * rs - (c == (int)label ? inv : 0.f);
+        }
+    }
+    if (!counted)
+        for (int c = lane; c < n_classes; c += 32) d[c] = 0.f;
+    if (lane == 0) row_loss[r] = mine;
+}
+
+// loss[0] = (sum of row_loss in a fixed order) / n_valid: thread t adds rows t, t + 256, ... in order, then the
+// 256 partial sums are folded by a fixed tree, so the loss is reproducible from run to run.
+__global__ void __launch_bounds__(kEwThreads)
+softmax_xent_mean_kernel(const float* __restrict__ row_loss, int n_rows, const int32_t* __restrict__ n_valid_dev,
+                         int n_valid_host, float* __restrict__ loss) {
+    __shared__ float part[kEwThreads];
+    float t = 0.f;
+    for (int r = threadIdx.x; r < n_rows; r += kEwThreads) t += row_loss[r];
+    part[threadIdx.x] = t;
+    __syncthreads();
+    for (int w = kEwThreads / 2; w; w >>= 1) {
+        if ((int)threadIdx.x < w) part[threadIdx.x] += part[threadIdx.x + w];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        int n_valid = n_valid_dev ? n_valid_dev[0] : n_valid_host;
+        n_valid = n_valid < 0 ? 0 : (n_valid > n_rows ? n_rows : n_valid);
+        loss[0] = n_valid > 0 ? part[0] / (float)n_valid : 0.f;
+    }
+}
+
+// Adam with L2 weight decay over flat buffers, torch.optim.Adam's arithmetic:
+//   g += wd * p;  m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2;
+//   p -= lr / (1 - b1^t) * m / (sqrt(v) / sqrt(1 - b2^t) + eps),   t = step[0] + 1.
+// The last CTA to finish stores t back, so that a captured launch advances the step on every replay.
+__global__ void __launch_bounds__(kEwThreads)
+adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, int64_t n,
+            float lr, float b1, float b2, float eps, float wd, int32_t* __restrict__ step, unsigned int* __restrict__ ticket) {
+    const int t = *(volatile int32_t*)step + 1;
+    const float c1 = 1.f - powf(b1, (float)t), c2 = sqrtf(1.f - powf(b2, (float)t));
+    const float step_size = lr / c1;
+    for (int64_t i = ((int64_t)blockIdx.x * kEwThreads + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * kEwThreads * 4) {
+        if (i + 4 <= n) {
+            float4 pp = *reinterpret_cast<float4*>(p + i), gg = *reinterpret_cast<const float4*>(g + i);
+            float4 mm = *reinterpret_cast<float4*>(m + i), vv = *reinterpret_cast<float4*>(v + i);
+#define FGL_ADAM1(P, G, M, V)                                   \
+    {                                                           \
+        const float grad = G + wd * P;                          \
+        M = b1 * M + (1.f - b1) * grad;                         \
+        V = b2 * V + (1.f - b2) * grad * grad;                  \
+        P -= step_size * M / (sqrtf(V) / c2 + eps);             \
+    }
+            FGL_ADAM1(pp.x, gg.x, mm.x, vv.x) FGL_ADAM1(pp.y, gg.y, mm.y, vv.y)
+            FGL_ADAM1(pp.z, gg.z, mm.z, vv.z) FGL_ADAM1(pp.w, gg.w, mm.w, vv.w)
+            *reinterpret_cast<float4*>(p + i) = pp;
+            *reinterpret_cast<float4*>(m + i) = mm;
+            *reinterpret_cast<float4*>(v + i) = vv;
+        } else {
+            for (int64_t j = i; j < n; ++j) {
+                float pj = p[j], mj = m[j], vj = v[j];
+                FGL_ADAM1(pj, g[j], mj, vj)
+                p[j] = pj; m[j] = mj; v[j] = vj;
+            }
+        }
+#undef FGL_ADAM1
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            ticket[0] = 0;
+            step[0] = t;
+        }
+    }
+}
+
+static int ew_grid(int64_t work_items) {
+    const int64_t blocks = (work_items + kEwThreads - 1) / kEwThreads;
+    return (int)(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace fgl
+
+using namespace fgl;
+
+extern "C" {
+
+int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, const float* bias, float p_drop,
+                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, void* stream) {
+    if (n_rows < 0 || dim <= 0 || ld < dim || (n_rows > 0 && !y) || !(p_drop >= 0.f && p_drop < 1.f)) return FGL_ERR_INVALID;
+    if (n_rows == 0) return FGL_OK;
+    // an element is dropped when its 32-bit word is below p * 2^32
+    const double thresh = (double)p_drop * 4294967296.0;
+    const uint32_t drop_below = p_drop > 0.f ? (uint32_t)(thresh >= 4294967295.0 ? 4294967295.0 : thresh) : 0u;
+    const float keep_scale = p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = dim % 4 == 0 && ld % 4 == 0 && aligned16(y) && (!bias || aligned16(bias));
+    if (vec)
+        bias_relu_dropout_kernel<4><<<ew_grid(n_rows * (dim / 4)), kEwThreads, 0, st>>>(
+            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags);
+    else
+        bias_relu_dropout_kernel<1><<<ew_grid(n_rows * dim), kEwThreads, 0, st>>>(
+            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_relu_dropout_bwd(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
+                         float* dbias, int32_t flags, void* stream) {
+    if (n_rows < 0 || dim <= 0 || dim > kBwdMaxColsPerThread * kEwThreads || ldy < dim || (n_rows > 0 && !dy) ||
+        !(p_drop >= 0.f && p_drop < 1.f))
+        return FGL_ERR_INVALID;
+    if ((flags & FGL_EW_RELU) && (!out || ldo < dim)) return FGL_ERR_INVALID;
+    if (n_rows == 0) return FGL_OK;
+    // bands of 8..64 rows, sized so that the grid has at least two CTAs per SM where the matrix allows it
+    int64_t rows_per_cta = (n_rows / (2 * 148)) / kBwdRowBatch * kBwdRowBatch;
+    rows_per_cta = rows_per_cta < kBwdRowBatch ? kBwdRowBatch : (rows_per_cta > 64 ? 64 : rows_per_cta);
+    const int64_t blocks = (n_rows + rows_per_cta - 1) / rows_per_cta;
+    if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
+    relu_dropout_bwd_kernel<<<(unsigned)blocks, kEwThreads, 0, (cudaStream_t)stream>>>(
+        dy, ldy, out, ldo, n_rows, (int)rows_per_cta, dim, p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f, dbias, flags);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_softmax_xent(fgl_ws* ws, const float* logits, int64_t ld, const int64_t* labels, const int32_t* label_ids,
+                     int64_t n_labels, int32_t n_rows, int32_t n_classes, const int32_t* n_valid_dev, int32_t n_valid,
+                     float* loss, float* dlogits, int64_t ldd, float* row_loss, void* stream) {
+    if (!ws || n_rows < 0 || n_classes <= 0 || ld < n_classes || ldd < n_classes || !loss ||
+        (n_rows > 0 && (!logits || !labels || !dlogits || !row_loss)))
+        return FGL_ERR_INVALID;
+    if (n_rows == 0) {
+        return cudaMemsetAsync(loss, 0, sizeof(float), (cudaStream_t)stream) == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    softmax_xent_rows_kernel<<<(n_rows + kXentWarps - 1) / kXentWarps, kXentWarps * 32, 0, st>>>(
+        logits, ld, labels, label_ids, n_labels, n_rows, n_classes, n_valid_dev, n_valid, row_loss, dlogits, ldd, ws->status);
+    softmax_xent_mean_kernel<<<1, kEwThreads, 0, st>>>(row_loss, n_rows, n_valid_dev, n_valid, loss);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, int32_t* step_dev, void* stream) {
+    if (n < 0 || (n > 0 && (!param || !grad || !exp_avg || !exp_avg_sq)) || !step_dev) return FGL_ERR_INVALID;
+    if (n == 0) return FGL_OK;
+    if (!aligned16(param) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq)) return FGL_ERR_INVALID;
+    // step_dev[0] = completed steps, step_dev[1] = the kernel's arrival ticket (zero between launches)
+    adam_kernel<<<ew_grid((n + 3) / 4), kEwThreads, 0, (cudaStream_t)stream>>>(
+        param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, step_dev, (unsigned int*)(step_dev + 1));
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+}  // extern "C"

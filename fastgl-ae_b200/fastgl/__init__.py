@@ -386,25 +386,136 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
 
 
 def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None,
-                       n_dst_dev=None):
+                       n_dst_dev=None, d_self=None, out=None):
     """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim].  ``n_dst_dev`` as in
-    ``aggregate``."""
+    ``aggregate``.  ``d_self`` (float32[n_dst, dim], rows may be a column slice) is the gradient of a self term:
+    d_x starts from it in its first n_dst rows instead of from zero.  ``d_out`` may be a column slice too;
+    ``out`` receives the result when given."""
     _check_i32(edge_ptr, "edge_ptr")
     _check_i32(src_edges, "src_edges")
-    _check_f32(d_out, "d_input")
+    _check_rows_f32(d_out, "d_input")
     for t, n in ((src_norm_degs, "src_norm_degs"), (dst_norm_degs, "dst_norm_degs")):
         if t is not None:
             _check_i32(t, n)
     dev = d_out.device
     n_dst, dim = d_out.size(0), d_out.size(1)
-    d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
+    if out is None:
+        d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
+    else:
+        _check_rows_f32(out, "out")
+        if out.size(0) < int(src_nodes) or out.size(1) != dim:
+            raise RuntimeError("out must be float32[src_nodes, dim]")
+        d_x = out
     with _on_device(dev):
-        rc = lib().fgl_agg_bwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
-                               _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), ctypes.c_int32(dim),
-                               ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
-                               ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
+        if d_self is None:
+            rc = lib().fgl_agg_bwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                                   _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), ctypes.c_int32(dim),
+                                   ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
+                                   ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
+        else:
+            _check_rows_f32(d_self, "d_self")
+            if d_self.size(0) != n_dst or d_self.size(1) != dim:
+                raise RuntimeError("d_self must be float32[n_dst, dim]")
+            rc = lib().fgl_agg_bwd_self(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                                        _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), _ptr(d_self),
+                                        ctypes.c_int64(d_self.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+                                        ctypes.c_int32(int(src_nodes)), _ptr(d_x), ctypes.c_int64(d_x.stride(0)),
+                                        _ptr(n_dst_dev), _stream(dev))
     _raise(rc, "aggregate_backward")
     return d_x
+
+
+# ------------------------------------------------------------------------------------------------
+# element-wise kernels of the training step (no counterpart among the reference's operators)
+# ------------------------------------------------------------------------------------------------
+def bias_relu_dropout_(y, bias=None, p_drop=0.0, relu=True, rng_seed=None, rng_ctr=0, rng_ctr_dev=None):
+    """In place: y = dropout(relu(y + bias)).  ``rng_ctr_dev`` (int32 CUDA tensor) is added to ``rng_ctr`` on the
+    device, so a captured launch draws a new mask per replay.  Returns ``y``."""
+    _check_rows_f32(y, "y")
+    if bias is not None:
+        _check_f32(bias, "bias")
+        if bias.numel() != y.size(1):
+            raise RuntimeError("bias must have one entry per column")
+    dev = y.device
+    with _on_device(dev):
+        rc = lib().fgl_bias_relu_dropout(_ptr(y), ctypes.c_int64(y.stride(0)), ctypes.c_int64(y.size(0)), ctypes.c_int32(y.size(1)),
+                                         _ptr(bias), ctypes.c_float(p_drop),
+                                         ctypes.c_uint64(_config["rng_seed"] if rng_seed is None else rng_seed),
+                                         ctypes.c_uint64(rng_ctr), _ptr(rng_ctr_dev), ctypes.c_int32(1 if relu else 0), _stream(dev))
+    _raise(rc, "bias_relu_dropout_")
+    return y
+
+
+def relu_dropout_backward_(dy, out=None, p_drop=0.0, dbias=None, masked=True):
+    """In place over ``dy``: the gradient through dropout(relu(.)) given the forward output ``out`` (``masked``), and
+    ``dbias += column sums`` of the result.  Returns ``dy``."""
+    _check_rows_f32(dy, "dy")
+    if masked:
+        _check_rows_f32(out, "out")
+        if out.shape != dy.shape:
+            raise RuntimeError("out and dy must have the same shape")
+    if dbias is not None:
+        _check_f32(dbias, "dbias")
+        if dbias.numel() != dy.size(1):
+            raise RuntimeError("dbias must have one entry per column")
+    dev = dy.device
+    with _on_device(dev):
+        rc = lib().fgl_relu_dropout_bwd(_ptr(dy), ctypes.c_int64(dy.stride(0)), _ptr(out if masked else None),
+                                        ctypes.c_int64(out.stride(0) if masked else dy.size(1)), ctypes.c_int64(dy.size(0)),
+                                        ctypes.c_int32(dy.size(1)), ctypes.c_float(p_drop), _ptr(dbias),
+                                        ctypes.c_int32(1 if masked else 0), _stream(dev))
+    _raise(rc, "relu_dropout_backward_")
+    return dy
+
+
+def softmax_xent(logits, labels, label_ids=None, n_valid=None, loss=None, dlogits=None, row_loss=None):
+    """Mean softmax cross-entropy over the first ``n_valid`` rows (an int, an int32 CUDA tensor read on the device, or
+    all rows) and its gradient: returns (loss float32[1], dlogits).  ``row_loss`` (float32[n_rows]) is scratch.  Row r's label is ``labels[label_ids[r]]`` when
+    ``label_ids`` (int32) is given, else ``labels[r]``; ``labels`` is int64."""
+    _check_rows_f32(logits, "logits")
+    _check_input(labels, "labels")
+    if labels.dtype != torch.int64:
+        raise RuntimeError("labels must be int64")
+    if label_ids is not None:
+        _check_i32(label_ids, "label_ids")
+    dev = logits.device
+    n_rows, n_classes = logits.size(0), logits.size(1)
+    loss = torch.empty(1, dtype=torch.float32, device=dev) if loss is None else loss
+    dlogits = torch.empty((n_rows, n_classes), dtype=torch.float32, device=dev) if dlogits is None else dlogits
+    _check_rows_f32(dlogits, "dlogits")
+    row_loss = torch.empty(max(n_rows, 1), dtype=torch.float32, device=dev) if row_loss is None else row_loss
+    _check_f32(row_loss, "row_loss")
+    if row_loss.numel() < n_rows:
+        raise RuntimeError("row_loss must hold one float per row")
+    n_valid_dev = n_valid if torch.is_tensor(n_valid) else None
+    if n_valid_dev is not None:
+        _check_i32(n_valid_dev, "n_valid")
+    ws = _ws(dev)
+    with _on_device(dev):
+        rc = lib().fgl_softmax_xent(ws, _ptr(logits), ctypes.c_int64(logits.stride(0)), _ptr(labels), _ptr(label_ids),
+                                    ctypes.c_int64(labels.numel()), ctypes.c_int32(n_rows), ctypes.c_int32(n_classes),
+                                    _ptr(n_valid_dev), ctypes.c_int32(n_rows if n_valid is None or n_valid_dev is not None else int(n_valid)),
+                                    _ptr(loss), _ptr(dlogits), ctypes.c_int64(dlogits.stride(0)), _ptr(row_loss), _stream(dev))
+    _raise(rc, "softmax_xent", ws)
+    return loss, dlogits
+
+
+def adam_step_(param, grad, exp_avg, exp_avg_sq, step_dev, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
+    """One Adam step (torch.optim.Adam's arithmetic, L2 weight decay) over flat float32 buffers, in place.
+    ``step_dev``: int32[2] CUDA tensor, zero before the first step; the launch itself advances ``step_dev[0]``."""
+    for t, n in ((param, "param"), (grad, "grad"), (exp_avg, "exp_avg"), (exp_avg_sq, "exp_avg_sq")):
+        _check_f32(t, n)
+        if t.numel() != param.numel():
+            raise RuntimeError("param, grad and the two moment buffers must have the same length")
+    _check_i32(step_dev, "step_dev")
+    if step_dev.numel() < 2:
+        raise RuntimeError("step_dev must hold two int32 words")
+    dev = param.device
+    with _on_device(dev):
+        rc = lib().fgl_adam_step(_ptr(param), _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq), ctypes.c_int64(param.numel()),
+                                 ctypes.c_float(lr), ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps),
+                                 ctypes.c_float(weight_decay), _ptr(step_dev), _stream(dev))
+    _raise(rc, "adam_step_")
 
 
 def forward_gat(edge_ptr, edge_data, src_edges, input_feat, neighbor_num, dst_nodes, num_heads):

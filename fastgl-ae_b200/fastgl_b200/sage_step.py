@@ -1,0 +1,102 @@
+"""The GraphSAGE-mean training step as an explicit sequence of launches over static buffers.
+
+PyTorch's autograd runs the same step as ~70 kernels (bias epilogues, ReLU, dropout, concatenations, padded
+slice gradients, gradient accumulations, a single-CTA loss, a 7-CTA optimizer).  Written out by hand the step is
+per layer one GEMM, one fused bias/ReLU/dropout launch, one aggregation (and a copy of the self rows) forward;
+one loss launch; and per layer two GEMMs, one scatter that starts from the self gradient, and one fused
+ReLU/dropout backward that also produces the bias gradient.  The dense products stay with cuBLAS (torch.mm), as
+in the reference (aggregate_acc_kernel.cu:237,368); everything else is a kernel of this library.
+
+The model is the one of ``layers.GraphSAGE``: layer i computes ``z_i = [h_i[:n_dst] | mean_N(h_i)] W_i + b_i`` and
+``h_{i+1} = dropout(relu(z_i))``; the last z is the logits.  ``layers.GraphSAGE`` under autograd is the reference
+the tests compare this program with.
+"""
+from __future__ import annotations
+
+import torch
+
+import fastgl
+
+
+class SageStepProgram:
+    def __init__(self, model, grads, labels, x0, seeds, sizes, blocks, pad_dst, step_word, rng_seed=12345):
+        """``x0``: float32[pad_dst[0], 2*in] rows [self | neighbour mean] of the input layer; ``blocks[i]`` (i >= 1) the
+        padded block of layer i with its real row count in ``sizes[i]``; ``seeds``: int32 node ids of the output rows
+        (their labels are ``labels[seeds]``); ``sizes[len(blocks) - 1]`` = number of valid output rows;
+        ``step_word``: int32[1] view that differs from step to step (the dropout counter)."""
+        self.layers = list(model.layers)
+        self.L = len(self.layers)
+        self.p_drop = float(model.dropout.p) if model.training else 0.0
+        self.model = model
+        self.grads = grads
+        self.labels, self.x0, self.seeds, self.sizes, self.blocks = labels, x0, seeds, sizes, blocks
+        self.pad_dst = list(pad_dst)
+        self.step_word = step_word
+        self.rng_seed = rng_seed
+        dev = x0.device
+        L = self.L
+        outs = [layer.weight.size(1) for layer in self.layers]
+        ins = [layer.input_dim for layer in self.layers]
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.z = [torch.zeros((self.pad_dst[i], outs[i]), **f32) for i in range(L)]
+        self.cat = [x0] + [torch.zeros((self.pad_dst[i], 2 * ins[i]), **f32) for i in range(1, L)]
+        self.dcat = [None] + [torch.zeros((self.pad_dst[i], 2 * ins[i]), **f32) for i in range(1, L)]
+        self.dh = [None] + [torch.zeros((self.pad_dst[i - 1], ins[i]), **f32) for i in range(1, L)]
+        self.dlogits = torch.zeros((self.pad_dst[L - 1], outs[L - 1]), **f32)
+        self.loss = torch.zeros(1, **f32)
+        self.row_loss = torch.zeros(self.pad_dst[L - 1], **f32)
+        # split-K of the tall weight-gradient products: S slabs of rows, folded by a [1 x S] product
+        self.slabs, self.part, self.ones = [], [], []
+        for i in range(L):
+            n = self.pad_dst[i]
+            s = next((s for s in (16, 8) if n % s == 0 and n // s >= 512), 0)
+            self.slabs.append(s)
+            self.part.append(torch.zeros((s, 2 * ins[i], outs[i]), **f32) if s else None)
+            self.ones.append(torch.ones((1, s), **f32) if s else None)
+
+    def forward_backward(self) -> torch.Tensor:
+        """Forward, loss and backward; the parameter gradients land in the flat gradient buffer.  Returns the loss
+        (float32[1], a static buffer)."""
+        L, p = self.L, self.p_drop
+        training = self.model.training
+        for i, layer in enumerate(self.layers):
+            torch.mm(self.cat[i], layer.weight, out=self.z[i])
+            if i < L - 1:
+                fastgl.bias_relu_dropout_(self.z[i], layer.bias, p if training else 0.0, relu=True, rng_seed=self.rng_seed,
+                                          rng_ctr=(i + 1) << 40, rng_ctr_dev=self.step_word)
+                blk = self.blocks[i + 1]
+                d = self.layers[i + 1].input_dim
+                nxt = self.cat[i + 1]
+                nxt[:, :d].copy_(self.z[i][: self.pad_dst[i + 1]])
+                fastgl.aggregate(fastgl.AGG_MEAN, blk.indptr, blk.src, self.z[i], self.pad_dst[i + 1],
+                                 zero_deg_passthrough=False, out=nxt[:, d:], n_dst_dev=blk.n_dst_dev)
+            else:
+                fastgl.bias_relu_dropout_(self.z[i], layer.bias, 0.0, relu=False)
+        fastgl.softmax_xent(self.z[L - 1], self.labels, label_ids=self.seeds, n_valid=self.sizes[L - 1: L], loss=self.loss,
+                            dlogits=self.dlogits, row_loss=self.row_loss)
+        self.grads.zero()
+        dz = self.dlogits
+        for i in reversed(range(L)):
+            layer = self.layers[i]
+            if i == L - 1:
+                fastgl.relu_dropout_backward_(dz, masked=False, dbias=layer.bias.grad)
+            self._weight_grad(i, dz)
+            if i > 0:
+                d = layer.input_dim
+                blk = self.blocks[i]
+                torch.mm(dz, layer.weight.t(), out=self.dcat[i])
+                fastgl.aggregate_backward(fastgl.AGG_MEAN, blk.indptr, blk.src, self.dcat[i][:, d:], self.pad_dst[i - 1],
+                                          n_dst_dev=blk.n_dst_dev, d_self=self.dcat[i][:, :d], out=self.dh[i])
+                dz = fastgl.relu_dropout_backward_(self.dh[i], out=self.z[i - 1], p_drop=p if training else 0.0,
+                                                   dbias=self.layers[i - 1].bias.grad)
+        return self.loss
+
+    def _weight_grad(self, i: int, dz: torch.Tensor) -> None:
+        x, gw = self.cat[i], self.layers[i].weight.grad
+        s = self.slabs[i]
+        if s:
+            n, k, m = x.size(0), x.size(1), dz.size(1)
+            torch.bmm(x.view(s, n // s, k).transpose(1, 2), dz.view(s, n // s, m), out=self.part[i])
+            torch.mm(self.ones[i], self.part[i].view(s, k * m), out=gw.view(1, k * m))
+        else:
+            torch.mm(x.t(), dz, out=gw)

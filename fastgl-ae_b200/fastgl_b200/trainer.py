@@ -19,6 +19,7 @@ import torch.nn.functional as F
 import fastgl
 
 from .block import Block
+from .sage_step import SageStepProgram
 from .sampler import FusedMapSampler
 from .scheduler import MatchReorder
 
@@ -59,13 +60,45 @@ class FlatGrads:
                 self.buffer.div_(world)
 
 
+class FlatAdam:
+    """Adam (torch.optim.Adam's arithmetic, L2 weight decay) as one launch over all parameters: the parameters are
+    moved into one flat buffer (each ``p.data`` becomes a view of it, in the order of ``FlatGrads``) next to flat
+    first- and second-moment buffers.  The step count lives on the device and the launch advances it, so the launch
+    can be captured in a CUDA graph."""
+
+    def __init__(self, grads: FlatGrads, lr, weight_decay, betas=(0.9, 0.999), eps=1e-8):
+        self.grads = grads
+        self.lr, self.weight_decay, self.betas, self.eps = lr, weight_decay, betas, eps
+        self.flat = torch.empty_like(grads.buffer)
+        off = 0
+        with torch.no_grad():
+            for p in grads.params:
+                view = self.flat[off: off + p.numel()].view_as(p)
+                view.copy_(p.data)
+                p.data = view
+                off += p.numel()
+        self.exp_avg = torch.zeros_like(self.flat)
+        self.exp_avg_sq = torch.zeros_like(self.flat)
+        self.step_dev = torch.zeros(2, dtype=torch.int32, device=self.flat.device)
+
+    def step(self):
+        fastgl.adam_step_(self.flat, self.grads.buffer, self.exp_avg, self.exp_avg_sq, self.step_dev, lr=self.lr,
+                          betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)
+
+    def zero_state(self):
+        self.exp_avg.zero_()
+        self.exp_avg_sq.zero_()
+        self.step_dev.zero_()
+
+
 class GraphedStep:
     """The per-mini-batch part of a training step -- inner layers forward, loss, backward and (single GPU) the
     optimizer step -- captured once as a CUDA graph over buffers of fixed, padded shape and replayed for every
     mini-batch.  A staging kernel copies the batch's first-layer rows and inner blocks into those buffers and
-    writes the real row counts, which the aggregation kernels read on the device.  This removes the ~60 host
-    launches per step that otherwise bound the step time (the reference even blocks on an event three times
-    per step, train_fastgl.py:348,362,373)."""
+    writes the real row counts, which the aggregation kernels read on the device.  The captured work is the
+    hand-written launch sequence of ``sage_step.SageStepProgram`` (29 launches).  This removes the host launches
+    that otherwise bound the step time (the reference even blocks on an event three times per step,
+    train_fastgl.py:348,362,373)."""
 
     def __init__(self, trainer, pad_dst):
         self.tr = trainer
@@ -76,9 +109,9 @@ class GraphedStep:
         self.pad_dst = list(pad_dst)            # padded destination count of block i (input layer first)
         assert len(self.pad_dst) == L and self.pad_dst[-1] == tr.batch_size
         self.x0 = torch.zeros((self.pad_dst[0], 2 * D), dtype=torch.float32, device=dev)
-        self.sizes = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.sizes = torch.zeros(8, dtype=torch.int32, device=dev)   # [0, L): real row counts; [L]: step index
         self.seeds = torch.zeros(tr.batch_size, dtype=torch.int32, device=dev)
-        self.row_ids = torch.arange(tr.batch_size, dtype=torch.int32, device=dev)
+        self.steps_staged = 0
         self.blocks = [None]
         for i in range(1, L):
             ptr = torch.zeros(self.pad_dst[i] + 1, dtype=torch.int32, device=dev)
@@ -90,6 +123,8 @@ class GraphedStep:
         # every rank then issues the collective the same way whether or not its batch fitted the padded shapes.
         self.step_in_graph = tr.world == 1
         self.opt_graph = None
+        self.program = SageStepProgram(tr.model, tr.grads, tr.labels, self.x0, self.seeds, self.sizes, self.blocks,
+                                       self.pad_dst, self.sizes[L: L + 1], rng_seed=tr.sampler.rng_seed)
 
     def fits(self, counts_row) -> bool:
         L = self.L
@@ -110,18 +145,12 @@ class GraphedStep:
             ptr, src = fb.block_indptr[h], fb.block_src[h]
             segs.append((self.blocks[i].indptr.data_ptr(), ptr.data_ptr() + b * ptr.stride(0) * 4, (n_dst[i] + 1) * 4))
             segs.append((self.blocks[i].src.data_ptr(), src.data_ptr() + b * src.stride(0) * 4, int(counts_row[8 + h]) * 4))
-        fastgl.stage_segments_raw(segs, self.sizes.data_ptr(), n_dst, self.tr.dev)
+        self.steps_staged += 1
+        fastgl.stage_segments_raw(segs, self.sizes.data_ptr(), n_dst + [self.steps_staged & 0x7fffffff], self.tr.dev)
 
     def _forward_backward(self):
-        tr = self.tr
-        y = tr.labels[self.seeds.long()]
-        # a short last batch of an epoch fills only the first sizes[L-1] rows: the others are left out of the mean
-        y = torch.where(self.row_ids < self.sizes[self.L - 1], y, -100)
-        logits = tr.model(self.blocks, None, layer0=self.x0)
-        loss = F.cross_entropy(logits, y, ignore_index=-100)
-        tr.grads.zero()
-        loss.backward()
-        return loss
+        with torch.no_grad():
+            return self.program.forward_backward()
 
     def capture(self):
         """Warm up on a side stream (restoring model and optimizer afterwards) and capture the step."""
@@ -173,7 +202,9 @@ class Trainer:
         self.matcher = MatchReorder(self.n_nodes) if reorder else None
         self.grads = FlatGrads(model.parameters())
         self.lr, self.weight_decay = lr, weight_decay
-        self.use_graph = bool(cuda_graph) and hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
+        # GraphSAGE (layers with a self term and a stacked weight) has the hand-written step and the flat optimizer
+        self.sage = hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
+        self.use_graph = bool(cuda_graph) and self.sage
         self.graphed = None
         self.graph_fallbacks = 0
         self.reset_optimizer()
@@ -191,15 +222,19 @@ class Trainer:
         self.time_layer0 = False
         # The first layer's [self | neighbour-mean] rows do not depend on the weights, so they are produced for
         # the whole window by one launch straight from the feature table.
-        self.sage = hasattr(model, "layers") and hasattr(model.layers[0], "input_dim")
         self.window_layer0 = bool(window_layer0) and self.sage
         self._layer0_buf = None
 
     def reset_optimizer(self):
-        self.opt = torch.optim.Adam(self.model.parameters(), lr=self.lr, weight_decay=self.weight_decay, fused=True,
-                                    capturable=self.use_graph)
+        if self.sage:
+            self.opt = FlatAdam(self.grads, self.lr, self.weight_decay)
+        else:
+            self.opt = torch.optim.Adam(self.model.parameters(), lr=self.lr, weight_decay=self.weight_decay, fused=True)
 
     def zero_optimizer_state(self):
+        if isinstance(self.opt, FlatAdam):
+            self.opt.zero_state()
+            return
         for state in self.opt.state.values():
             for v in state.values():
                 if torch.is_tensor(v):

@@ -48,6 +48,9 @@ extern "C" {
 #define FGL_AGG_EDGE 3    /* out[d, h] = sum_e w[e, h] * x[src[e], h]: per-edge, per-head weights (GAT, K12);
                              only through fgl_agg_edge_fwd / fgl_agg_edge_bwd */
 
+/* flags of fgl_bias_relu_dropout / fgl_relu_dropout_bwd */
+#define FGL_EW_RELU 1     /* apply ReLU (forward) / the ReLU-and-dropout mask (backward) */
+
 #define FGL_MAX_HOPS 7
 #define FGL_COUNTS_STRIDE 16 /* per mini-batch: [0..7] node counts n_0..n_L, [8..15] edge counts per hop */
 #define FGL_MAX_FANOUT 512
@@ -239,6 +242,56 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
 int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                 const int32_t* dst_deg, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst,
                 int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev, void* stream);
+
+/* fgl_agg_bwd for a layer that also feeds each destination's own row forward (GraphSAGE: [h_dst | aggregate]):
+ * dx starts as dy_self in its first n_dst rows (the destinations are the first n_dst sources) and zero below,
+ * then receives the scattered dy as above -- one pass instead of a zero-fill, a scatter, a padded copy and an
+ * add.  dy_self is float32 [n_dst][dim] with leading dimension ld_self; n_dst <= n_src.  No counterpart in the
+ * reference, whose models have no self term (GraphConv.py:86-99). */
+int fgl_agg_bwd_self(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                     const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
+                     int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
+                     void* stream);
+
+/* ---- Element-wise kernels of the training step around the aggregation path -----------------------------
+ * None of these has a counterpart among the reference's CUDA operators: the reference leaves them to PyTorch,
+ * op by op (model code GraphConv.py:86-99,182-195; loss and optimizer train_fastgl.py:366-372).  They exist so
+ * that a whole training step can be a short, capturable sequence of launches. */
+
+/* y[r, c] = dropout(relu(y[r, c] + bias[c])) in place over n_rows x dim (leading dimension ld).  bias may be NULL;
+ * FGL_EW_RELU in flags applies the ReLU; p_drop in [0, 1) (0 = no dropout; survivors are scaled by 1 / (1 - p)).
+ * Element e = r * dim + c is dropped when word (e & 3) of the Philox4x32-10 block with key rng_seed and counter
+ * (lo32(e >> 2), hi32(e >> 2), lo32(ctr), hi32(ctr)) is below p_drop * 2^32, where ctr = rng_ctr plus, when
+ * rng_ctr_dev is not NULL, the unsigned value rng_ctr_dev[0] read on the device (a per-step counter that lets a
+ * captured launch draw a fresh mask on every replay). */
+int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, const float* bias, float p_drop,
+                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, void* stream);
+
+/* Backward of fgl_bias_relu_dropout: with FGL_EW_RELU, dy[r, c] becomes dy[r, c] / (1 - p_drop) where the
+ * forward output out[r, c] is positive and 0 elsewhere (an element is positive exactly when it passed both the
+ * ReLU and the dropout); without the flag dy is left as it is.  dbias (may be NULL; dim <= 2048) is incremented
+ * by the column sums of the resulting dy: the caller zeroes it. */
+int fgl_relu_dropout_bwd(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
+                         float* dbias, int32_t flags, void* stream);
+
+/* Mean softmax cross-entropy over the first n_valid rows and its gradient.  The label of row r is
+ * labels[label_ids ? label_ids[r] : r] (labels: int64[n_labels], values in [0, n_classes); an index or a label
+ * outside its range records FGL_ERR_BOUNDS in the workspace's status word and the row contributes nothing).  n_valid is read from n_valid_dev[0] when that is not NULL.
+ * loss[0] = mean over valid rows of logsumexp(z_r) - z_r[label]; dlogits[r, :] = (softmax(z_r) - onehot) / n_valid
+ * for valid rows and 0 for the others.  row_loss is caller-owned scratch of n_rows floats (it receives the per-row
+ * losses, which are then summed in a fixed order: the loss is reproducible).  The workspace only lends its
+ * status word. */
+int fgl_softmax_xent(fgl_ws* ws, const float* logits, int64_t ld, const int64_t* labels, const int32_t* label_ids,
+                     int64_t n_labels, int32_t n_rows, int32_t n_classes, const int32_t* n_valid_dev, int32_t n_valid,
+                     float* loss, float* dlogits, int64_t ldd, float* row_loss, void* stream);
+
+/* One Adam step with L2 weight decay over flat fp32 buffers of n elements (16-byte aligned), with the arithmetic
+ * of torch.optim.Adam: g += wd * p; m = b1 m + (1 - b1) g; v = b2 v + (1 - b2) g^2;
+ * p -= lr / (1 - b1^t) * m / (sqrt(v) / sqrt(1 - b2^t) + eps), t = step_dev[0] + 1.  step_dev is two int32 words
+ * in device memory, zero before the first step: [0] counts completed steps and is advanced by the launch itself
+ * (so a captured launch advances on every replay), [1] is scratch that is zero between launches. */
+int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, int32_t* step_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,149 @@
+"""The element-wise kernels of the training step (no counterpart among the reference's operators) against plain
+PyTorch fp32/fp64 algebra, and the dropout mask against the oracle's Philox restatement."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle_np as onp
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def fastgl():
+    import fastgl as f
+    return f
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 4), (37, 47), (300, 256), (1025, 100)])
+def test_bias_relu_without_dropout(fastgl, rows, dim):
+    g = torch.Generator(device=DEV).manual_seed(rows)
+    y = torch.randn((rows, dim), generator=g, device=DEV)
+    b = torch.randn(dim, generator=g, device=DEV)
+    want = torch.relu(y + b)
+    got = fastgl.bias_relu_dropout_(y.clone(), b, 0.0, relu=True)
+    assert torch.equal(got, want)
+    assert torch.equal(fastgl.bias_relu_dropout_(y.clone(), b, 0.0, relu=False), y + b)
+    wide = torch.randn((rows, 2 * dim + 4), generator=g, device=DEV)          # a column slice of a wider buffer
+    view = wide[:, 4: 4 + dim]
+    want = torch.relu(view + b)
+    fastgl.bias_relu_dropout_(view, b, 0.0)
+    assert torch.equal(wide[:, 4: 4 + dim], want)
+
+
+@pytest.mark.parametrize("dim", [8, 47])
+def test_dropout_mask_is_the_documented_philox_stream(fastgl, dim):
+    rows, p, seed, ctr = 9, 0.3, 0x1234567890ABCDEF, 5
+    y = torch.ones((rows, dim), device=DEV)
+    step = torch.tensor([7], dtype=torch.int32, device=DEV)
+    got = fastgl.bias_relu_dropout_(y, None, p, relu=False, rng_seed=seed, rng_ctr=ctr, rng_ctr_dev=step).cpu().numpy()
+    thresh = int(float(np.float32(p)) * 4294967296.0)
+    want = np.empty((rows, dim), dtype=np.float32)
+    for e in range(rows * dim):
+        word = onp.draw(seed, ctr + 7, 0, e)
+        want.flat[e] = 0.0 if word < thresh else 1.0 / (1.0 - p)
+    assert np.allclose(got, want, rtol=1e-6)
+
+
+def test_dropout_rate_and_fresh_masks_per_step(fastgl):
+    y = torch.ones((4096, 256), device=DEV)
+    step = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = fastgl.bias_relu_dropout_(y.clone(), None, 0.5, relu=False, rng_ctr_dev=step)
+    step += 1
+    b = fastgl.bias_relu_dropout_(y.clone(), None, 0.5, relu=False, rng_ctr_dev=step)
+    kept = float((a > 0).float().mean())
+    assert abs(kept - 0.5) < 0.005 and float(a.max()) == 2.0
+    assert 0.45 < float(((a > 0) == (b > 0)).float().mean()) < 0.55          # independent masks
+
+
+@pytest.mark.parametrize("rows,dim,p", [(1, 4, 0.0), (70, 47, 0.5), (5000, 256, 0.5), (129, 600, 0.2)])
+def test_relu_dropout_backward_and_bias_gradient(fastgl, rows, dim, p):
+    g = torch.Generator(device=DEV).manual_seed(dim)
+    z = torch.randn((rows, dim), generator=g, device=DEV)
+    b = torch.randn(dim, generator=g, device=DEV)
+    out = fastgl.bias_relu_dropout_(z.clone(), b, p, relu=True, rng_ctr=3)
+    dy = torch.randn((rows, dim), generator=g, device=DEV)
+    want = torch.where(out > 0, dy / (1.0 - p), torch.zeros_like(dy))
+    dbias = torch.zeros(dim, device=DEV)
+    got = fastgl.relu_dropout_backward_(dy.clone(), out, p, dbias=dbias)
+    assert torch.allclose(got, want, rtol=1e-6, atol=0)
+    ref = want.double().sum(0)
+    assert float((dbias.double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max()))
+    # unmasked: only the column sums
+    dbias.zero_()
+    same = fastgl.relu_dropout_backward_(dy.clone(), masked=False, dbias=dbias)
+    assert torch.equal(same, dy)
+    ref = dy.double().sum(0)
+    assert float((dbias.double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("rows,classes,n_valid", [(1024, 47, 1024), (1024, 47, 700), (33, 7, 33), (5, 172, 3), (64, 10, 0)])
+def test_softmax_cross_entropy_and_gradient(fastgl, rows, classes, n_valid):
+    g = torch.Generator(device=DEV).manual_seed(rows + classes)
+    logits = (4 * torch.randn((rows, classes), generator=g, device=DEV)).requires_grad_(True)
+    table = torch.randint(0, classes, (5000,), generator=g, device=DEV)
+    ids = torch.randint(0, 5000, (rows,), generator=g, device=DEV).to(torch.int32)
+    for n_arg in (n_valid, torch.tensor([n_valid], dtype=torch.int32, device=DEV)):
+        loss, dlogits = fastgl.softmax_xent(logits.detach(), table, label_ids=ids, n_valid=n_arg)
+        fastgl.check_status()
+        if n_valid == 0:
+            assert float(loss) == 0.0 and float(dlogits.abs().max()) == 0.0
+            continue
+        y = table[ids.long()]
+        ref = torch.nn.functional.cross_entropy(logits[:n_valid].double(), y[:n_valid])
+        (grad,) = torch.autograd.grad(ref, logits)
+        assert abs(float(loss) - float(ref.detach())) <= 1e-5 * max(1.0, abs(float(ref.detach())))
+        assert float((dlogits.double() - grad.double()).abs().max()) <= 1e-6
+        assert float(dlogits[n_valid:].abs().max()) == 0.0 if n_valid < rows else True
+    # labels given row by row
+    y = table[ids.long()].contiguous()
+    loss2, _ = fastgl.softmax_xent(logits.detach(), y, n_valid=n_valid)
+    assert float(loss2) == float(loss)
+
+
+def test_softmax_cross_entropy_reports_a_bad_label(fastgl):
+    logits = torch.zeros((4, 3), device=DEV)
+    labels = torch.tensor([0, 1, 7, 2], device=DEV)
+    fastgl.softmax_xent(logits, labels)
+    with pytest.raises(RuntimeError):
+        fastgl.check_status()
+    fastgl.check_status()                                                       # the status word was cleared
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 200_003])
+def test_adam_step_matches_torch_adam(fastgl, n):
+    g = torch.Generator(device=DEV).manual_seed(n)
+    p0 = torch.randn(n, generator=g, device=DEV)
+    ref = p0.clone().double().requires_grad_(True)
+    opt = torch.optim.Adam([ref], lr=0.01, weight_decay=5e-4)
+    p, m, v = p0.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    step = torch.zeros(2, dtype=torch.int32, device=DEV)
+    for _ in range(5):
+        grad = torch.randn(n, generator=g, device=DEV)
+        ref.grad = grad.double()
+        opt.step()
+        fastgl.adam_step_(p, grad, m, v, step, lr=0.01, weight_decay=5e-4)
+    assert step.tolist() == [5, 0]
+    assert float((p.double() - ref.detach()).abs().max()) <= 2e-6
+
+
+def test_aggregate_backward_starting_from_the_self_gradient(fastgl):
+    rng = np.random.default_rng(5)
+    n_dst, n_src, deg, dim = 700, 3000, 9, 256
+    indptr = torch.arange(0, (n_dst + 1) * deg, deg, dtype=torch.int32, device=DEV)
+    src = torch.from_numpy(rng.integers(0, n_src, n_dst * deg).astype(np.int32)).to(DEV)
+    dcat = torch.randn((n_dst, 2 * dim), device=DEV)
+    plain = fastgl.aggregate_backward(fastgl.AGG_MEAN, indptr, src, dcat[:, dim:].contiguous(), n_src)
+    want = plain.clone()
+    want[:n_dst] += dcat[:, :dim]
+    out = torch.full((n_src, dim), 9.0, device=DEV)
+    got = fastgl.aggregate_backward(fastgl.AGG_MEAN, indptr, src, dcat[:, dim:], n_src, d_self=dcat[:, :dim], out=out)
+    assert got.data_ptr() == out.data_ptr()
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    # odd width: scalar path
+    d2 = torch.randn((n_dst, 2 * 47), device=DEV)
+    plain = fastgl.aggregate_backward(fastgl.AGG_SUM, indptr, src, d2[:, 47:].contiguous(), n_src)
+    plain[:n_dst] += d2[:, :47]
+    got = fastgl.aggregate_backward(fastgl.AGG_SUM, indptr, src, d2[:, 47:], n_src, d_self=d2[:, :47])
+    assert float((got - plain).abs().max()) <= 1e-5 * float(plain.abs().max())
