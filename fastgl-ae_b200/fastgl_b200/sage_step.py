@@ -45,11 +45,12 @@ class SageStepProgram:
         self.dlogits = torch.zeros((self.pad_dst[L - 1], outs[L - 1]), **f32)
         self.loss = torch.zeros(1, **f32)
         self.row_loss = torch.zeros(self.pad_dst[L - 1], **f32)
-        # split-K of the tall weight-gradient products: S slabs of rows, folded by a [1 x S] product
+        # split-K of the tall weight-gradient products: S slabs of rows, folded by a [1 x S] product.  The output is
+        # only a few 128 x 64 tiles, so S is what fills the 148 SMs.
         self.slabs, self.part, self.ones = [], [], []
         for i in range(L):
             n = self.pad_dst[i]
-            s = next((s for s in (16, 8) if n % s == 0 and n // s >= 512), 0)
+            s = next((s for s in (32, 16, 8) if n % s == 0 and n // s >= 256), 0)
             self.slabs.append(s)
             self.part.append(torch.zeros((s, 2 * ins[i], outs[i]), **f32) if s else None)
             self.ones.append(torch.ones((1, s), **f32) if s else None)
