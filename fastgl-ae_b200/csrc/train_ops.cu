@@ -20,12 +20,14 @@ __device__ __forceinline__ uint4 dropout_block(uint64_t seed, uint64_t ctr, uint
     return philox_block(seed, ctr, (uint32_t)(group >> 32), (uint32_t)group);
 }
 
-// y = dropout(relu(y + bias)), in place.  VEC = 4: dim % 4 == 0, ld % 4 == 0, 16-byte aligned base.
+// y = dropout(relu(y + bias)), in place; the first n_copy_rows rows also go to copy_out (the self operand of the
+// next layer).  VEC = 4: dim % 4 == 0, leading dimensions % 4 == 0, 16-byte aligned bases.
 template <int VEC>
 __global__ void __launch_bounds__(kEwThreads)
 bias_relu_dropout_kernel(float* __restrict__ y, int64_t ld, int64_t n_rows, int dim, const float* __restrict__ bias,
                          uint32_t drop_below, float keep_scale, uint64_t rng_seed, uint64_t rng_ctr,
-                         const int32_t* __restrict__ rng_ctr_dev, int flags) {
+                         const int32_t* __restrict__ rng_ctr_dev, int flags, float* __restrict__ copy_out,
+                         int64_t ld_copy, int64_t n_copy_rows) {
     const int64_t groups_per_row = dim / VEC;
     const int64_t total = n_rows * groups_per_row;
     const uint64_t ctr = rng_ctr + (rng_ctr_dev ? (uint64_t)(uint32_t)rng_ctr_dev[0] : 0ull);
@@ -48,6 +50,7 @@ bias_relu_dropout_kernel(float* __restrict__ y, int64_t ld, int64_t n_rows, int 
                 v.w = w.w < drop_below ? 0.f : v.w * keep_scale;
             }
             *reinterpret_cast<float4*>(p) = v;
+            if (r < n_copy_rows) *reinterpret_cast<float4*>(copy_out + r * ld_copy + c) = v;
         } else {
             float v = *p + (bias ? bias[c] : 0.f);
             if (relu) v = fmaxf(v, 0.f);
@@ -57,6 +60,7 @@ bias_relu_dropout_kernel(float* __restrict__ y, int64_t ld, int64_t n_rows, int 
                 v = w < drop_below ? 0.f : v * keep_scale;
             }
             *p = v;
+            if (r < n_copy_rows) copy_out[r * ld_copy + c] = v;
         }
     }
 }
@@ -222,21 +226,27 @@ using namespace fgl;
 extern "C" {
 
 int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, const float* bias, float p_drop,
-                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, void* stream) {
+                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, float* copy_out,
+                          int64_t ld_copy, int64_t n_copy_rows, void* stream) {
     if (n_rows < 0 || dim <= 0 || ld < dim || (n_rows > 0 && !y) || !(p_drop >= 0.f && p_drop < 1.f)) return FGL_ERR_INVALID;
+    if (!copy_out) n_copy_rows = 0;
+    if (n_copy_rows < 0 || n_copy_rows > n_rows || (n_copy_rows > 0 && ld_copy < dim)) return FGL_ERR_INVALID;
     if (n_rows == 0) return FGL_OK;
     // an element is dropped when its 32-bit word is below p * 2^32
     const double thresh = (double)p_drop * 4294967296.0;
     const uint32_t drop_below = p_drop > 0.f ? (uint32_t)(thresh >= 4294967295.0 ? 4294967295.0 : thresh) : 0u;
     const float keep_scale = p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f;
     cudaStream_t st = (cudaStream_t)stream;
-    const bool vec = dim % 4 == 0 && ld % 4 == 0 && aligned16(y) && (!bias || aligned16(bias));
+    const bool vec = dim % 4 == 0 && ld % 4 == 0 && aligned16(y) && (!bias || aligned16(bias)) &&
+                     (n_copy_rows == 0 || (ld_copy % 4 == 0 && aligned16(copy_out)));
     if (vec)
         bias_relu_dropout_kernel<4><<<ew_grid(n_rows * (dim / 4)), kEwThreads, 0, st>>>(
-            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags);
+            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags, copy_out, ld_copy,
+            n_copy_rows);
     else
         bias_relu_dropout_kernel<1><<<ew_grid(n_rows * dim), kEwThreads, 0, st>>>(
-            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags);
+            y, ld, n_rows, dim, bias, drop_below, keep_scale, rng_seed, rng_ctr, rng_ctr_dev, flags, copy_out, ld_copy,
+            n_copy_rows);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

@@ -335,6 +335,11 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     if edge_ptr.numel() < n_dst + 1:
         raise RuntimeError("edge_ptr is shorter than dst_nodes + 1")
     x, shards, rps, ld, dim, dev = _table_args(input_feat)
+    if mode == AGG_SYMNORM:
+        n_src = row_map.numel() if row_map is not None else (input_feat.size(0) if torch.is_tensor(input_feat) else None)
+        if (src_norm_degs is None or dst_norm_degs is None or dst_norm_degs.numel() < n_dst
+                or (n_src is not None and src_norm_degs.numel() < n_src)):
+            raise RuntimeError("sym-norm needs src_norm_degs[n_src] and dst_norm_degs[n_dst]")
     if out is None:
         out = torch.empty((n_dst, dim), dtype=torch.float32, device=dev)
     else:
@@ -399,6 +404,11 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
             _check_i32(t, n)
     dev = d_out.device
     n_dst, dim = d_out.size(0), d_out.size(1)
+    if mode == AGG_SYMNORM and (src_norm_degs is None or dst_norm_degs is None or src_norm_degs.numel() < int(src_nodes)
+                                or dst_norm_degs.numel() < n_dst):
+        raise RuntimeError("sym-norm needs src_norm_degs[src_nodes] and dst_norm_degs[n_dst]")
+    if edge_ptr.numel() < n_dst + 1:
+        raise RuntimeError("edge_ptr is shorter than n_dst + 1")
     if out is None:
         d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
     else:
@@ -428,10 +438,15 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
 # ------------------------------------------------------------------------------------------------
 # element-wise kernels of the training step (no counterpart among the reference's operators)
 # ------------------------------------------------------------------------------------------------
-def bias_relu_dropout_(y, bias=None, p_drop=0.0, relu=True, rng_seed=None, rng_ctr=0, rng_ctr_dev=None):
+def bias_relu_dropout_(y, bias=None, p_drop=0.0, relu=True, rng_seed=None, rng_ctr=0, rng_ctr_dev=None, copy_out=None):
     """In place: y = dropout(relu(y + bias)).  ``rng_ctr_dev`` (int32 CUDA tensor) is added to ``rng_ctr`` on the
-    device, so a captured launch draws a new mask per replay.  Returns ``y``."""
+    device, so a captured launch draws a new mask per replay.  ``copy_out`` (float32[k, dim], k <= rows, may be a
+    column slice) also receives the first k result rows.  Returns ``y``."""
     _check_rows_f32(y, "y")
+    if copy_out is not None:
+        _check_rows_f32(copy_out, "copy_out")
+        if copy_out.size(1) != y.size(1) or copy_out.size(0) > y.size(0):
+            raise RuntimeError("copy_out must be float32[k <= rows, dim]")
     if bias is not None:
         _check_f32(bias, "bias")
         if bias.numel() != y.size(1):
@@ -441,7 +456,9 @@ def bias_relu_dropout_(y, bias=None, p_drop=0.0, relu=True, rng_seed=None, rng_c
         rc = lib().fgl_bias_relu_dropout(_ptr(y), ctypes.c_int64(y.stride(0)), ctypes.c_int64(y.size(0)), ctypes.c_int32(y.size(1)),
                                          _ptr(bias), ctypes.c_float(p_drop),
                                          ctypes.c_uint64(_config["rng_seed"] if rng_seed is None else rng_seed),
-                                         ctypes.c_uint64(rng_ctr), _ptr(rng_ctr_dev), ctypes.c_int32(1 if relu else 0), _stream(dev))
+                                         ctypes.c_uint64(rng_ctr), _ptr(rng_ctr_dev), ctypes.c_int32(1 if relu else 0),
+                                         _ptr(copy_out), ctypes.c_int64(copy_out.stride(0) if copy_out is not None else 0),
+                                         ctypes.c_int64(copy_out.size(0) if copy_out is not None else 0), _stream(dev))
     _raise(rc, "bias_relu_dropout_")
     return y
 
@@ -658,14 +675,30 @@ class FusedBatch:
         self.block_src = block_src
         self._arena = arena
         self._counts_host = None
+        self._counts_pinned = None
+        self._readback = None
 
     @property
     def n_batches(self) -> int:
         return self.nodes.size(0)
 
+    def start_readback(self) -> None:
+        """Enqueue the copy of the counts to pinned host memory on the current stream, without waiting: the next
+        ``counts_host()`` waits for that copy only, not for work enqueued after it."""
+        if self._counts_pinned is None:
+            self._counts_pinned = torch.empty(self.counts.shape, dtype=self.counts.dtype).pin_memory()
+        self._counts_pinned.copy_(self.counts, non_blocking=True)
+        self._readback = torch.cuda.Event()
+        self._readback.record(torch.cuda.current_stream(self.counts.device))
+
     def counts_host(self) -> torch.Tensor:
         if self._counts_host is None:
-            self._counts_host = self.counts.cpu()
+            if self._readback is not None:
+                self._readback.synchronize()
+                self._counts_host = self._counts_pinned.clone()
+                self._readback = None
+            else:
+                self._counts_host = self.counts.cpu()
             self._counts_list = self._counts_host.tolist()
         return self._counts_host
 
@@ -722,6 +755,7 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
             off += nb * s
         out = FusedBatch(fanouts, views[0], views[1], views[2: 2 + L], views[2 + L: 2 + 2 * L], arena)
     out._counts_host = None
+    out._readback = None
     a = FusedArgs()
     a.indptr = edge_ptr.data_ptr()
     a.indices = src_edges.data_ptr()

@@ -28,22 +28,63 @@ def block_csr(block):
     return fastgl.exclusive_sum(deg), src.int().contiguous()
 
 
+def gcn_aggregate_first(n_src: int, n_dst: int, n_edges: int, in_dim: int, out_dim: int) -> bool:
+    """Whether ``(A x) W`` is cheaper than ``A (x W)``.  Both give the layer's output (aggregation is linear); the
+    reference always updates first (aggregate_acc_kernel.cu:237), which multiplies all ``n_src`` gathered rows by W
+    although only ``n_dst`` output rows exist.  Cost model: fp32 GEMM at 40 TFLOP/s, aggregation at 3 TB/s of
+    row traffic."""
+    update_first = 2.0 * n_src * in_dim * out_dim / 40e12 + 4.0 * n_edges * out_dim / 3e12
+    aggregate_first = 4.0 * n_edges * in_dim / 3e12 + 2.0 * n_dst * in_dim * out_dim / 40e12
+    return aggregate_first < update_first
+
+
 class MA_Function(torch.autograd.Function):
-    """GraphConv.py:19-40."""
+    """GraphConv.py:19-40, with the order of update and aggregation chosen by cost.
+
+    Update-first is the reference's op pair (``forward_gcn`` / ``backward_gcn``).  Aggregate-first computes
+    ``tmp = A x`` (sym-normalised, rows without in-edges copy their own input row, as the reference's forward does),
+    ``out = tmp W``; backward ``d_w = tmp^T d``, ``d_x = A^T (d W^T)`` only if the input takes a gradient, where
+    ``d`` is the incoming gradient with the rows of destinations without in-edges zeroed, because the reference's
+    backward skips those rows (aggregate_acc_kernel.cu:498-500).  With ``row_map`` the input is the whole feature
+    table addressed through the block's global ids (no gathered copy of the input rows exists)."""
 
     @staticmethod
-    def forward(ctx, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, weight, neighbor_num):
-        ctx.save_for_backward(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat)
-        return fastgl.forward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, input_feat, weight, neighbor_num,
-                                  dst_nodes)[0]
+    def forward(ctx, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, weight, neighbor_num,
+                row_map=None):
+        n_src = src_norm_degs.numel()
+        ctx.aggregate_first = row_map is not None or gcn_aggregate_first(n_src, dst_nodes, src_edges.numel(),
+                                                                        weight.size(0), weight.size(1))
+        if not ctx.aggregate_first:
+            ctx.save_for_backward(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat)
+            return fastgl.forward_gcn(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, input_feat, weight, neighbor_num,
+                                      dst_nodes)[0]
+        tmp = fastgl.aggregate(fastgl.AGG_SYMNORM, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs, dst_norm_degs,
+                               zero_deg_passthrough=True, row_map=row_map)
+        ctx.n_src = n_src
+        ctx.mapped = row_map is not None
+        ctx.save_for_backward(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, tmp)
+        return torch.mm(tmp, weight)
 
     @staticmethod
     def backward(ctx, d_input):
-        edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat = ctx.saved_tensors
-        # destination degrees third, source degrees fourth: GraphConv.py:37
-        d_x, d_w = fastgl.backward_gcn(edge_ptr, src_edges, dst_norm_degs, src_norm_degs, d_input.contiguous(), weight,
-                                       input_feat)
-        return None, None, None, None, None, d_x, d_w, None
+        if not ctx.aggregate_first:
+            edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, input_feat = ctx.saved_tensors
+            # destination degrees third, source degrees fourth: GraphConv.py:37
+            d_x, d_w = fastgl.backward_gcn(edge_ptr, src_edges, dst_norm_degs, src_norm_degs, d_input.contiguous(), weight,
+                                           input_feat)
+            return None, None, None, None, None, d_x, d_w, None, None
+        edge_ptr, src_edges, src_norm_degs, dst_norm_degs, weight, tmp = ctx.saved_tensors
+        n_dst = tmp.size(0)
+        has_edges = (edge_ptr[1: n_dst + 1] > edge_ptr[:n_dst]).unsqueeze(1)
+        d = d_input * has_edges
+        d_w = torch.mm(tmp.t(), d)
+        d_x = None
+        if ctx.needs_input_grad[5]:
+            if ctx.mapped:
+                raise RuntimeError("no gradient flows into a feature table that is aggregated through a row map")
+            d_x = fastgl.aggregate_backward(fastgl.AGG_SYMNORM, edge_ptr, src_edges, torch.mm(d, weight.t()), ctx.n_src,
+                                            src_norm_degs=src_norm_degs, dst_norm_degs=dst_norm_degs)
+        return None, None, None, None, None, d_x, d_w, None, None
 
 
 class MA_Function_GIN(torch.autograd.Function):
@@ -76,9 +117,9 @@ class _Conv(nn.Module):
 
 
 class GCNConv(_Conv):
-    def forward(self, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, neighbor_num):
+    def forward(self, edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, neighbor_num, row_map=None):
         return MA_Function.apply(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, dst_nodes, input_feat, self.weights,
-                                 neighbor_num)
+                                 neighbor_num, row_map)
 
 
 class GINConv(_Conv):
@@ -100,7 +141,10 @@ class GCN(_Stack):
     """GraphConv.py:63-99: a linear stack (the reference accepts ``activation`` and never applies it)."""
     conv = GCNConv
 
-    def forward(self, blocks, features, neighbor_list=(5, 10, 15)):
+    def forward(self, blocks, features, neighbor_list=(5, 10, 15), input_nodes=None):
+        """``features``: the gathered input rows float32[n_src_0, in] (train_fastgl.py:357,365), or, with
+        ``input_nodes`` (int32 global ids of block 0's sources), the whole feature table, which the first layer then
+        aggregates in place."""
         h = features
         for i, layer in enumerate(self.layers):
             if i != 0:
@@ -110,7 +154,8 @@ class GCN(_Stack):
             edge_ptr, src_edges = block_csr(block)
             dst_norm_degs = (edge_ptr[1: n_dst + 1] - edge_ptr[:n_dst]).clamp(min=1)         # GraphConv.py:93,97
             src_norm_degs = fastgl.cal_deg(src_edges, block.num_src_nodes()).clamp(min=1)    # GraphConv.py:96
-            h = layer(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, n_dst, h, neighbor_list[i])
+            h = layer(edge_ptr, src_edges, src_norm_degs, dst_norm_degs, n_dst, h, neighbor_list[i],
+                      row_map=input_nodes if i == 0 else None)
         return h
 
 

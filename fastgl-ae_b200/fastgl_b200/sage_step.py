@@ -2,7 +2,8 @@
 
 PyTorch's autograd runs the same step as ~70 kernels (bias epilogues, ReLU, dropout, concatenations, padded
 slice gradients, gradient accumulations, a single-CTA loss, a 7-CTA optimizer).  Written out by hand the step is
-per layer one GEMM, one fused bias/ReLU/dropout launch, one aggregation (and a copy of the self rows) forward;
+per layer one GEMM, one fused bias/ReLU/dropout launch (which also stores the next layer's self rows) and one
+aggregation forward;
 one loss launch; and per layer two GEMMs, one scatter that starts from the self gradient, and one fused
 ReLU/dropout backward that also produces the bias gradient.  The dense products stay with cuBLAS (torch.mm), as
 in the reference (aggregate_acc_kernel.cu:237,368); everything else is a kernel of this library.
@@ -63,12 +64,11 @@ class SageStepProgram:
         for i, layer in enumerate(self.layers):
             torch.mm(self.cat[i], layer.weight, out=self.z[i])
             if i < L - 1:
-                fastgl.bias_relu_dropout_(self.z[i], layer.bias, p if training else 0.0, relu=True, rng_seed=self.rng_seed,
-                                          rng_ctr=(i + 1) << 40, rng_ctr_dev=self.step_word)
                 blk = self.blocks[i + 1]
                 d = self.layers[i + 1].input_dim
                 nxt = self.cat[i + 1]
-                nxt[:, :d].copy_(self.z[i][: self.pad_dst[i + 1]])
+                fastgl.bias_relu_dropout_(self.z[i], layer.bias, p if training else 0.0, relu=True, rng_seed=self.rng_seed,
+                                          rng_ctr=(i + 1) << 40, rng_ctr_dev=self.step_word, copy_out=nxt[:, :d])
                 fastgl.aggregate(fastgl.AGG_MEAN, blk.indptr, blk.src, self.z[i], self.pad_dst[i + 1],
                                  zero_deg_passthrough=False, out=nxt[:, d:], n_dst_dev=blk.n_dst_dev)
             else:

@@ -49,12 +49,15 @@ class FusedMapSampler:
         return cur, output_nodes, blocks
 
     # --- B200 path: a window of mini-batches per launch -----------------------------------------------
-    def sample_window(self, seeds: torch.Tensor, seed_counts: torch.Tensor, n_teams: int = 0, reuse: bool = True):
+    def sample_window(self, seeds: torch.Tensor, seed_counts: torch.Tensor, n_teams: int = 0, reuse: bool = True,
+                      slot: int = 0):
         """``seeds`` int32[n_batches, batch_size] on the GPU, ``seed_counts`` int32[n_batches].
 
         Returns the device-resident ``fastgl.FusedBatch``; batch ``b`` draws with the same Philox counters
-        ``sample_blocks`` would use for the ``b``-th call, so both paths give identical blocks."""
-        key = (seeds.size(0), seeds.size(1), seeds.device)
+        ``sample_blocks`` would use for the ``b``-th call, so both paths give identical blocks.  With ``reuse`` the
+        result lives in buffers kept per geometry and ``slot``: a caller that samples the next window while the
+        previous one is still being consumed alternates the slot."""
+        key = (seeds.size(0), seeds.size(1), seeds.device, slot)
         out = self._window_out.get(key) if reuse else None
         ctr = self.batch_counter * 8
         self.batch_counter += seeds.size(0)

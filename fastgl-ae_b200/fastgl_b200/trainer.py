@@ -19,6 +19,7 @@ import torch.nn.functional as F
 import fastgl
 
 from .block import Block
+from .layers import GCN
 from .sage_step import SageStepProgram
 from .sampler import FusedMapSampler
 from .scheduler import MatchReorder
@@ -188,7 +189,7 @@ class GraphedStep:
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
                  lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
-                 window_layer0=True, cuda_graph=False):
+                 window_layer0=True, cuda_graph=False, table_direct=True):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -196,6 +197,7 @@ class Trainer:
         self.batch_size, self.window = int(batch_size), int(window)
         self.rank, self.world = rank, world
         self.n_teams = n_teams
+        self.table_direct = bool(table_direct)   # GCN: first layer reads the feature table through the block's ids
         self.n_nodes = indptr.numel() - 1
         self.sampler = FusedMapSampler(self.fanouts, replace=False, rng_seed=rng_seed + 7919 * rank)
         self.sampler.edge_src, self.sampler.edge_ptr, self.sampler.nodes_num = indices, indptr, self.n_nodes
@@ -321,6 +323,9 @@ class Trainer:
         elif self.sage:
             self.model.layer0_timer = self.layer0_events if self.time_layer0 else None
             logits = self.model(blocks, self.feat, input_nodes=input_nodes)
+        elif isinstance(self.model, GCN) and self.table_direct:
+            # GCN's first layer aggregates straight from the feature table: no gathered copy of the input rows
+            logits = self.model(blocks, self.feat, neighbor_list=self.fanouts, input_nodes=input_nodes)
         else:
             # the reference's models (GCN / GIN) take the gathered input rows (train_fastgl.py:357,365)
             batch_inputs = fastgl.gather_rows(self.feat, input_nodes)
@@ -344,27 +349,42 @@ class Trainer:
         pending = None
         if read_loss_each_step and self._loss_host is None:
             self._loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
-        while done < n_steps:
-            nb = min(self.window, n_steps - done)
+        # The next window is sampled two steps before the current one ends, and only its counts are waited for:
+        # the host then prepares that window while the GPU still has steps to run, so the GPU never waits for it.
+        windows_sampled = 0
+
+        def sample_next(first_step):
+            nonlocal windows_sampled
+            nb = min(self.window, n_steps - first_step)
             if host_seeds is not None:
                 seeds_h, counts_h = host_seeds
-                seeds = seeds_h[done: done + nb].to(self.dev, non_blocking=True)
-                counts = counts_h[done: done + nb].to(self.dev, non_blocking=True)
+                seeds = seeds_h[first_step: first_step + nb].to(self.dev, non_blocking=True)
+                counts = counts_h[first_step: first_step + nb].to(self.dev, non_blocking=True)
             else:
                 seeds, counts = self._next_window_seeds(nb)
                 counts = counts.to(self.dev, non_blocking=True)
             if self.time_layer0:
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
-            fb = self.sampler.sample_window(seeds, counts, n_teams=self.n_teams)
+            fb = self.sampler.sample_window(seeds, counts, n_teams=self.n_teams, slot=windows_sampled & 1)
             if self.time_layer0:
                 end.record()
                 self.sample_events.append((start, end, nb))
+            fb.start_readback()
+            windows_sampled += 1
+            return fb, nb
+
+        nxt = sample_next(0) if n_steps > 0 else None
+        while done < n_steps:
+            fb, nb = nxt
+            nxt = None
             layer0 = self.aggregate_window_layer0(fb) if self.window_layer0 else None
             order = list(range(nb))
             if self.matcher is not None:
                 order = self.matcher.reorder([fb.input_nodes(b) for b in range(nb)])
-            for b in order:
+            for i, b in enumerate(order):
+                if i == max(0, nb - 2) and done + nb < n_steps:
+                    nxt = sample_next(done + nb)
                 loss = self.train_batch(fb, b, layer0=layer0)
                 if read_loss_each_step:
                     slot = len(losses) & 1 if pending is None else 1 - pending[1]

@@ -263,9 +263,11 @@ int fgl_agg_bwd_self(int32_t mode, const int32_t* indptr, const int32_t* src, co
  * Element e = r * dim + c is dropped when word (e & 3) of the Philox4x32-10 block with key rng_seed and counter
  * (lo32(e >> 2), hi32(e >> 2), lo32(ctr), hi32(ctr)) is below p_drop * 2^32, where ctr = rng_ctr plus, when
  * rng_ctr_dev is not NULL, the unsigned value rng_ctr_dev[0] read on the device (a per-step counter that lets a
- * captured launch draw a fresh mask on every replay). */
+ * captured launch draw a fresh mask on every replay).  When copy_out is not NULL the first n_copy_rows result
+ * rows are also stored to copy_out (leading dimension ld_copy): the self operand of the next GraphSAGE layer. */
 int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, const float* bias, float p_drop,
-                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, void* stream);
+                          uint64_t rng_seed, uint64_t rng_ctr, const int32_t* rng_ctr_dev, int32_t flags, float* copy_out,
+                          int64_t ld_copy, int64_t n_copy_rows, void* stream);
 
 /* Backward of fgl_bias_relu_dropout: with FGL_EW_RELU, dy[r, c] becomes dy[r, c] / (1 - p_drop) where the
  * forward output out[r, c] is positive and 0 elsewhere (an element is positive exactly when it passed both the

@@ -20,15 +20,15 @@ def setup_problem(n=6000, feat_dim=100, classes=7, seed=5):
     return indptr, indices, feat, labels, train
 
 
-def make_trainer(problem, cuda_graph, window=4, window_layer0=True, hidden=32, batch=256):
+def make_trainer(problem, cuda_graph, window=4, window_layer0=True, hidden=32, batch=256, fanouts=(15, 10, 5), dropout=0.0):
     from fastgl_b200.layers import GraphSAGE
     from fastgl_b200.trainer import Trainer
     indptr, indices, feat, labels, train = problem
     dev = torch.device("cuda", 0)
     torch.manual_seed(3)
-    model = GraphSAGE(feat.shape[1], hidden, 7, 3, dropout=0.0).to(dev)
+    model = GraphSAGE(feat.shape[1], hidden, 7, len(fanouts), dropout=dropout).to(dev)
     tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), torch.from_numpy(feat).to(dev),
-                 torch.from_numpy(labels).to(dev), torch.from_numpy(train).to(dev), model, [15, 10, 5], batch_size=batch,
+                 torch.from_numpy(labels).to(dev), torch.from_numpy(train).to(dev), model, list(fanouts), batch_size=batch,
                  window=window, cuda_graph=cuda_graph, window_layer0=window_layer0)
     return tr
 
@@ -117,6 +117,79 @@ def test_cuda_graph_step_takes_the_short_last_batch_of_an_epoch():
     for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
         assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
     assert eager.sampled_edges == graphed.sampled_edges
+
+
+@pytest.mark.parametrize("fanouts,hidden", [((10, 5), 64), ((6, 5, 4, 3), 32)])
+def test_step_program_with_other_depths(fanouts, hidden):
+    problem = setup_problem(seed=11)
+    eager = make_trainer(problem, cuda_graph=False, fanouts=fanouts, hidden=hidden)
+    graphed = make_trainer(problem, cuda_graph=True, fanouts=fanouts, hidden=hidden)
+    le = eager.run_steps(8, read_loss_each_step=True)
+    lg = graphed.run_steps(8, read_loss_each_step=True)
+    assert graphed.graphed is not None and graphed.graph_fallbacks <= 2
+    assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
+    for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+
+
+def test_step_program_trains_with_dropout():
+    """With dropout the captured step draws a new mask on every replay (the loss of a repeated batch changes) and
+    still learns."""
+    problem = setup_problem(seed=13)
+    tr = make_trainer(problem, cuda_graph=True, dropout=0.5, hidden=64)
+    losses = tr.run_steps(60, read_loss_each_step=True)
+    assert tr.graphed is not None and all(np.isfinite(losses))
+    assert np.mean(losses[-10:]) < np.mean(losses[:10]) - 0.02
+    g = tr.graphed
+    torch.cuda.synchronize()
+    before = [p.detach().clone() for p in tr.model.parameters()]
+    a = float(g._forward_backward())
+    g.sizes[g.L] += 1                                  # what staging the next step does to the dropout counter
+    b = float(g._forward_backward())
+    assert a != b
+    for p, q in zip(tr.model.parameters(), before):    # forward_backward alone leaves the parameters alone
+        assert torch.equal(p, q)
+
+
+def test_gcn_layer_gives_the_same_result_in_either_order(monkeypatch):
+    """A (x W) (the reference's order) and (A x) W, forward and backward, including destinations without in-edges
+    (copied forward, skipped backward, as aggregate_acc_kernel.cu:307-308,:498-500) and the table-direct first layer."""
+    import fastgl
+    from fastgl_b200 import layers
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(21)
+    n_dst, n_src, fin, fout = 500, 4000, 96, 40
+    deg = rng.integers(0, 12, n_dst)
+    deg[::7] = 0
+    indptr = torch.from_numpy(np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)).to(dev)
+    src = torch.from_numpy(rng.integers(0, n_src, int(deg.sum())).astype(np.int32)).to(dev)
+    dst_deg = (indptr[1:] - indptr[:-1]).clamp(min=1)
+    src_deg = fastgl.cal_deg(src, n_src).clamp(min=1)
+    x0 = torch.randn((n_src, fin), device=dev)
+    w0 = torch.randn((fin, fout), device=dev) / 8
+    g = torch.randn((n_dst, fout), device=dev)
+    results = []
+    for first in (False, True):
+        monkeypatch.setattr(layers, "gcn_aggregate_first", lambda *a, first=first: first)
+        x, w = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+        out = layers.MA_Function.apply(indptr, src, src_deg, dst_deg, n_dst, x, w, 12, None)
+        out.backward(g)
+        results.append((out.detach(), x.grad, w.grad))
+    for a, b in zip(*results):
+        assert float((a - b).abs().max()) <= 2e-5 * float(a.abs().max())
+    # the whole feature table through global ids: same output and weight gradient, no input gradient
+    n_nodes = 20_000
+    ids = torch.from_numpy(rng.permutation(n_nodes)[:n_src].astype(np.int32)).to(dev)
+    table = torch.randn((n_nodes, fin), device=dev)
+    w = w0.clone().requires_grad_(True)
+    out_t = layers.MA_Function.apply(indptr, src, src_deg, dst_deg, n_dst, table, w, 12, ids)
+    out_t.backward(g)
+    monkeypatch.setattr(layers, "gcn_aggregate_first", lambda *a: False)
+    xg, w2 = table[ids.long()].clone(), w0.clone().requires_grad_(True)
+    out_g = layers.MA_Function.apply(indptr, src, src_deg, dst_deg, n_dst, xg, w2, 12, None)
+    out_g.backward(g)
+    assert float((out_t - out_g).detach().abs().max()) <= 2e-5 * float(out_g.detach().abs().max())
+    assert float((w.grad - w2.grad).abs().max()) <= 2e-5 * float(w2.grad.abs().max())
 
 
 def test_gat_layer_matches_a_dense_torch_restatement():

@@ -25,6 +25,10 @@ def test_bias_relu_without_dropout(fastgl, rows, dim):
     got = fastgl.bias_relu_dropout_(y.clone(), b, 0.0, relu=True)
     assert torch.equal(got, want)
     assert torch.equal(fastgl.bias_relu_dropout_(y.clone(), b, 0.0, relu=False), y + b)
+    k = max(1, rows // 3)
+    side = torch.full((k, 2 * dim), 7.0, device=DEV)                          # the first k rows also go to a column slice
+    got = fastgl.bias_relu_dropout_(y.clone(), b, 0.0, relu=True, copy_out=side[:, :dim])
+    assert torch.equal(side[:, :dim], got[:k]) and float(side[:, dim:].min()) == 7.0
     wide = torch.randn((rows, 2 * dim + 4), generator=g, device=DEV)          # a column slice of a wider buffer
     view = wide[:, 4: 4 + dim]
     want = torch.relu(view + b)
