@@ -241,6 +241,8 @@ def main():
     ap.add_argument("--config", default="products-like", choices=sorted(CONFIGS))
     ap.add_argument("--window", type=int, default=8, help="mini-batches sampled per kernel launch")
     ap.add_argument("--teams", type=int, default=0)
+    ap.add_argument("--table-slots", type=int, default=-1,
+                    help="cap of the sampler's per-team hashtable (0: worst-case size; default: learnt from the first window)")
     ap.add_argument("--reorder", action="store_true", help="Match-Reorder each window")
     ap.add_argument("--matmul", default="fp32", choices=["fp32", "tf32"],
                     help="arithmetic of the dense-layer GEMMs that stay in PyTorch (tf32 is what the reference's "
@@ -318,7 +320,8 @@ def main():
         return
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
-                 reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph)
+                 reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph,
+                 table_slots=None if args.table_slots < 0 else args.table_slots)
 
     def barrier():
         if world > 1:

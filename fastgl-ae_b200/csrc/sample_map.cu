@@ -93,13 +93,26 @@ __device__ __forceinline__ unsigned long long ld_slot(const unsigned long long* 
     return *(const volatile unsigned long long*)p;
 }
 
+// A probe sequence gives up after kProbeLimit slots (or the whole table, if smaller): at the load factors the
+// tables are sized for (<= 2/3) clusters are a few slots long, so only a table that is too small for its
+// mini-batch gets there.  The failure is recorded and the launch is told to stop at its next team barrier, so an
+// undersized table costs milliseconds, not a scan of the table per key.
+constexpr uint32_t kProbeLimit = 1u << 13;
+
+__device__ __forceinline__ uint32_t probe_limit(const Table& t) { return t.mask < kProbeLimit ? t.mask : kProbeLimit; }
+
+__device__ __forceinline__ void probe_failed(int32_t* status) {
+    set_status(status, FGL_ERR_PROBE);
+    atomicExch(status + 1, 1);
+}
+
 // Seed i gets local id i; of two equal seeds the later position wins, as a sequential run of
 // id_map.cu:259-287 leaves it.
 // Returns the slot position, or -1 when the table is full.
 __device__ __forceinline__ int table_insert_seed(const Table& t, uint32_t key, uint32_t local, int32_t* status) {
     const unsigned long long mine = ((unsigned long long)key << 32) | local;
     uint32_t pos = hash_pos(t, key);
-    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+    for (uint32_t probe = 0; probe <= probe_limit(t); ++probe) {
         unsigned long long cur = ld_slot(t.slots + pos);
         if (cur == kEmpty) {
             cur = atomicCAS(t.slots + pos, kEmpty, mine);
@@ -111,7 +124,7 @@ __device__ __forceinline__ int table_insert_seed(const Table& t, uint32_t key, u
         }
         pos = (pos + 1) & t.mask;
     }
-    set_status(status, FGL_ERR_PROBE);
+    probe_failed(status);
     return -1;
 }
 
@@ -122,7 +135,7 @@ __device__ __forceinline__ int table_insert_from(const Table& t, uint32_t key, u
                                                  int32_t* status, bool& created) {
     created = false;
     const unsigned long long mine = ((unsigned long long)key << 32) | (ARRIVAL ? kPending : (kPending | edge));
-    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+    for (uint32_t probe = 0; probe <= probe_limit(t); ++probe) {
         unsigned long long cur = ld_slot(t.slots + pos);
         if (cur == kEmpty) {
             cur = atomicCAS(t.slots + pos, kEmpty, mine);
@@ -139,7 +152,7 @@ __device__ __forceinline__ int table_insert_from(const Table& t, uint32_t key, u
         }
         pos = (pos + 1) & t.mask;
     }
-    set_status(status, FGL_ERR_PROBE);
+    probe_failed(status);
     return 0;
 }
 
@@ -152,7 +165,7 @@ __device__ __forceinline__ int table_insert(const Table& t, uint32_t key, uint32
 // Value of a key that must be present (a seed); missing keys report FGL_ERR_BOUNDS and map to 0.
 __device__ __forceinline__ int table_lookup(const Table& t, uint32_t key, int32_t* status) {
     uint32_t pos = hash_pos(t, key);
-    for (uint32_t probe = 0; probe <= t.mask; ++probe) {
+    for (uint32_t probe = 0; probe <= probe_limit(t); ++probe) {
         const unsigned long long cur = ld_slot(t.slots + pos);
         if (cur == kEmpty) break;
         if ((uint32_t)(cur >> 32) == key) return (int)((uint32_t)cur & ~kPending);

@@ -130,4 +130,12 @@ int fgl_ws_check(fgl_ws* ws, void* stream) {
     return code;
 }
 
+int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream) {
+    if (!ws || !host_dst) return FGL_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(ws->mu);
+    fgl::DeviceGuard guard(ws->device);
+    FGL_CUDA_OK(ws, cudaMemcpyAsync(host_dst, ws->status, sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return FGL_OK;
+}
+
 }  // extern "C"

@@ -676,7 +676,9 @@ class FusedBatch:
         self._arena = arena
         self._counts_host = None
         self._counts_pinned = None
+        self._status_pinned = None
         self._readback = None
+        self.device_status = 0   # the workspace's status word as of the last asynchronous read-back (0 = no error)
 
     @property
     def n_batches(self) -> int:
@@ -685,9 +687,13 @@ class FusedBatch:
     def start_readback(self) -> None:
         """Enqueue the copy of the counts to pinned host memory on the current stream, without waiting: the next
         ``counts_host()`` waits for that copy only, not for work enqueued after it."""
+        dev = self.counts.device
         if self._counts_pinned is None:
             self._counts_pinned = torch.empty(self.counts.shape, dtype=self.counts.dtype).pin_memory()
+            self._status_pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._counts_pinned.copy_(self.counts, non_blocking=True)
+        ws = _ws(dev)
+        _raise(lib().fgl_ws_status_peek(ws, ctypes.c_void_p(self._status_pinned.data_ptr()), _stream(dev)), "status_peek", ws)
         self._readback = torch.cuda.Event()
         self._readback.record(torch.cuda.current_stream(self.counts.device))
 
@@ -696,6 +702,7 @@ class FusedBatch:
             if self._readback is not None:
                 self._readback.synchronize()
                 self._counts_host = self._counts_pinned.clone()
+                self.device_status = int(self._status_pinned[0])
                 self._readback = None
             else:
                 self._counts_host = self.counts.cpu()
@@ -828,6 +835,10 @@ def stage_segments_raw(segments, words_dst_ptr, words, device):
         rc = lib().fgl_stage_segments(segs, ctypes.c_int32(n), ctypes.c_void_p(words_dst_ptr), vals,
                                       ctypes.c_int32(len(words)), _stream(device))
     _raise(rc, "stage_segments")
+
+
+def status_str(code: int) -> str:
+    return _capi.status_str(code)
 
 
 def check_status(device=None) -> None:

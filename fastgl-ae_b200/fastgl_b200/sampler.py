@@ -50,19 +50,21 @@ class FusedMapSampler:
 
     # --- B200 path: a window of mini-batches per launch -----------------------------------------------
     def sample_window(self, seeds: torch.Tensor, seed_counts: torch.Tensor, n_teams: int = 0, reuse: bool = True,
-                      slot: int = 0):
+                      slot: int = 0, table_slots: int = 0):
         """``seeds`` int32[n_batches, batch_size] on the GPU, ``seed_counts`` int32[n_batches].
 
         Returns the device-resident ``fastgl.FusedBatch``; batch ``b`` draws with the same Philox counters
         ``sample_blocks`` would use for the ``b``-th call, so both paths give identical blocks.  With ``reuse`` the
         result lives in buffers kept per geometry and ``slot``: a caller that samples the next window while the
-        previous one is still being consumed alternates the slot."""
+        previous one is still being consumed alternates the slot.  ``table_slots`` caps the per-team hashtable
+        (0 = sized for the worst case); a table that turns out too small is reported through the status word."""
         key = (seeds.size(0), seeds.size(1), seeds.device, slot)
         out = self._window_out.get(key) if reuse else None
         ctr = self.batch_counter * 8
         self.batch_counter += seeds.size(0)
         fb = fastgl.sample_map_fused(self.edge_ptr, self.edge_src, seeds, seed_counts, list(reversed(self.fanouts)),
-                                     replace=self.replace, rng_seed=self.rng_seed, rng_ctr=ctr, n_teams=n_teams, out=out)
+                                     replace=self.replace, rng_seed=self.rng_seed, rng_ctr=ctr, n_teams=n_teams, out=out,
+                                     table_slots=table_slots)
         if reuse:
             self._window_out[key] = fb
         return fb

@@ -189,7 +189,7 @@ class GraphedStep:
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
                  lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
-                 window_layer0=True, cuda_graph=False, table_direct=True):
+                 window_layer0=True, cuda_graph=False, table_direct=True, table_slots=None):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -198,6 +198,10 @@ class Trainer:
         self.rank, self.world = rank, world
         self.n_teams = n_teams
         self.table_direct = bool(table_direct)   # GCN: first layer reads the feature table through the block's ids
+        # cap of the sampler's per-team hashtable: None = learn it from the first window, 0 = worst-case size
+        self._auto_table = table_slots is None
+        self.table_slots = 0 if table_slots is None else int(table_slots)
+        self.table_overflows = 0
         self.n_nodes = indptr.numel() - 1
         self.sampler = FusedMapSampler(self.fanouts, replace=False, rng_seed=rng_seed + 7919 * rank)
         self.sampler.edge_src, self.sampler.edge_ptr, self.sampler.nodes_num = indices, indptr, self.n_nodes
@@ -241,6 +245,14 @@ class Trainer:
             for v in state.values():
                 if torch.is_tensor(v):
                     v.zero_()
+
+    def _sampler_teams(self) -> int:
+        """Teams of the fused sampler: as many mini-batches in flight as the window has (up to 16) once the tables
+        are small enough for all of them to stay in L2 together, else the library's default."""
+        if self.n_teams > 0 or self.table_slots == 0:
+            return self.n_teams
+        teams = min(self.window, 16)
+        return teams if teams * self.table_slots * 8 <= (64 << 20) else 0
 
     def _graph_step(self, fb, b, layer0):
         """Replay the captured step for batch ``b``; returns None when the batch does not fit the padded shapes."""
@@ -353,6 +365,19 @@ class Trainer:
         # the host then prepares that window while the GPU still has steps to run, so the GPU never waits for it.
         windows_sampled = 0
 
+        def launch_sampler(seeds, counts, slot):
+            nb = seeds.size(0)
+            if self.time_layer0:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+            fb = self.sampler.sample_window(seeds, counts, n_teams=self._sampler_teams(), slot=slot,
+                                            table_slots=self.table_slots)
+            if self.time_layer0:
+                end.record()
+                self.sample_events.append((start, end, nb))
+            fb.start_readback()
+            return fb
+
         def sample_next(first_step):
             nonlocal windows_sampled
             nb = min(self.window, n_steps - first_step)
@@ -363,21 +388,37 @@ class Trainer:
             else:
                 seeds, counts = self._next_window_seeds(nb)
                 counts = counts.to(self.dev, non_blocking=True)
-            if self.time_layer0:
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                start.record()
-            fb = self.sampler.sample_window(seeds, counts, n_teams=self.n_teams, slot=windows_sampled & 1)
-            if self.time_layer0:
-                end.record()
-                self.sample_events.append((start, end, nb))
-            fb.start_readback()
+            slot = windows_sampled & 1
             windows_sampled += 1
-            return fb, nb
+            return launch_sampler(seeds, counts, slot), nb, seeds, counts, slot
 
         nxt = sample_next(0) if n_steps > 0 else None
         while done < n_steps:
-            fb, nb = nxt
+            fb, nb, seeds, counts, slot = nxt
             nxt = None
+            fb.counts_host()
+            if fb.device_status != 0:
+                # The capped hashtable was too small for this window (or another device-side check fired): clear the
+                # status, drop the cap and sample the same window again -- same seeds, same Philox counters.
+                code = fb.device_status
+                try:
+                    fastgl.check_status(self.dev)
+                except RuntimeError:
+                    pass
+                if self.table_slots == 0:
+                    raise RuntimeError(f"fused sampling failed: {fastgl.status_str(code)}")
+                self.table_slots, self._auto_table = 0, False
+                self.table_overflows += 1
+                self.sampler.batch_counter -= nb
+                fb = launch_sampler(seeds, counts, slot)
+                fb.counts_host()
+                if fb.device_status != 0:
+                    fastgl.check_status(self.dev)
+            elif self._auto_table and self.table_slots == 0:
+                # size the table from what a window really holds: 2.5 slots per node of the largest batch seen,
+                # which keeps it L2-resident (the worst-case size is 16 MB per team at the benchmark shapes)
+                most = int(fb.counts_host()[:, len(self.fanouts)].max())
+                self.table_slots = 1 << max(12, math.ceil(math.log2(max(1.0, 2.5 * most))))
             layer0 = self.aggregate_window_layer0(fb) if self.window_layer0 else None
             order = list(range(nb))
             if self.matcher is not None:

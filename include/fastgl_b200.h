@@ -73,6 +73,10 @@ const char* fgl_last_error(fgl_ws* ws);
 /* Reads back (synchronising the stream) and clears the device status word set by the kernels of this
  * workspace: FGL_OK or the first FGL_ERR_* a kernel recorded. */
 int fgl_ws_check(fgl_ws* ws, void* stream);
+/* Enqueues a copy of the status word to host_dst (pinned host memory, one int32) on the stream, without
+ * synchronising and without clearing it: a caller that already waits for another read-back of the same stream
+ * learns of device-side errors at that point for free.  After a non-zero value, fgl_ws_check clears the word. */
+int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream);
 
 /* Neighbour sampling; replaces sample_node_cuda (sample.cu:102-203; binding aggregate_acc.cpp:491-512).
  * indptr has n_nodes + 1 entries of int32 (indptr_is_64 = 0, as the reference) or int64.  For seed i

@@ -211,7 +211,8 @@ def test_map_without_edges_and_with_repeated_sources(fastgl):
 # ----------------------------------------------------------------------------------------------
 # fused multi-hop, multi-mini-batch
 # ----------------------------------------------------------------------------------------------
-def run_fused_and_compare(fastgl, indptr, indices, seed_lists, fanouts_sampling, replace, n_teams, ptr_dtype=torch.int64):
+def run_fused_and_compare(fastgl, indptr, indices, seed_lists, fanouts_sampling, replace, n_teams, ptr_dtype=torch.int64,
+                          table_slots=0):
     nb = len(seed_lists)
     stride = max(len(s) for s in seed_lists)
     seeds = np.zeros((nb, stride), dtype=np.int32)
@@ -221,7 +222,7 @@ def run_fused_and_compare(fastgl, indptr, indices, seed_lists, fanouts_sampling,
         counts[b] = len(s)
     fb = fastgl.sample_map_fused(to_dev(indptr, ptr_dtype), to_dev(indices), to_dev(seeds), to_dev(counts),
                                  fanouts_sampling, replace=replace, arrival_order=False, rng_seed=31337, rng_ctr=800,
-                                 n_teams=n_teams)
+                                 n_teams=n_teams, table_slots=table_slots)
     fastgl.check_status()
     L = len(fanouts_sampling)
     for b, s in enumerate(seed_lists):
@@ -246,6 +247,27 @@ def test_fused_matches_oracle(fastgl, graph, replace, n_teams):
     seed_lists = [rng.choice(len(indptr) - 1, size=n, replace=False).astype(np.int32) for n in (256, 256, 100, 1, 256)]
     seed_lists[0][0] = 0
     run_fused_and_compare(fastgl, indptr, indices, seed_lists, [5, 10, 15], replace, n_teams)
+
+
+def test_fused_with_a_capped_table_and_recovery_from_a_table_that_is_too_small(fastgl, graph):
+    """A table capped at 4x the node count gives the same blocks; one that cannot hold the mini-batch is reported
+    (no fault, the launch stops early), the asynchronous read-back shows the status, and the next launch with a
+    large enough table is correct again."""
+    indptr, indices = graph
+    rng = np.random.default_rng(23)
+    seed_lists = [rng.choice(len(indptr) - 1, size=256, replace=False).astype(np.int32) for _ in range(3)]
+    fb = run_fused_and_compare(fastgl, indptr, indices, seed_lists, [5, 10, 15], False, 3, table_slots=1 << 16)
+    assert int(fb.counts_host()[:, 3].max()) > 2048
+    seeds = to_dev(np.stack(seed_lists))
+    counts = to_dev(np.full(3, 256, dtype=np.int32))
+    small = fastgl.sample_map_fused(to_dev(indptr, torch.int64), to_dev(indices), seeds, counts, [5, 10, 15], rng_seed=31337,
+                                    rng_ctr=800, n_teams=3, table_slots=2048)
+    small.start_readback()
+    small.counts_host()
+    assert small.device_status != 0
+    with pytest.raises(RuntimeError, match="probe"):
+        fastgl.check_status()
+    run_fused_and_compare(fastgl, indptr, indices, seed_lists, [5, 10, 15], False, 3)
 
 
 def test_fused_int32_indptr_single_batch_two_hops(fastgl, graph):

@@ -151,6 +151,21 @@ def test_step_program_trains_with_dropout():
         assert torch.equal(p, q)
 
 
+def test_trainer_recovers_from_a_hashtable_cap_that_is_too_small():
+    """With a cap no window fits, the trainer notices at the window's read-back, drops the cap, samples the window
+    again with the same counters and trains exactly as without a cap."""
+    problem = setup_problem(seed=15)
+    plain = make_trainer(problem, cuda_graph=True)
+    capped = make_trainer(problem, cuda_graph=True)
+    capped.table_slots, capped._auto_table = 1024, False
+    lp = plain.run_steps(9, read_loss_each_step=True)
+    lc = capped.run_steps(9, read_loss_each_step=True)
+    assert capped.table_overflows == 1 and capped.table_slots == 0
+    assert plain.table_slots > 0 and plain.table_overflows == 0          # learnt from the first window
+    assert np.allclose(lp, lc, rtol=1e-5, atol=1e-6), (lp, lc)
+    assert plain.sampled_edges == capped.sampled_edges
+
+
 def test_gcn_layer_gives_the_same_result_in_either_order(monkeypatch):
     """A (x W) (the reference's order) and (A x) W, forward and backward, including destinations without in-edges
     (copied forward, skipped backward, as aggregate_acc_kernel.cu:307-308,:498-500) and the table-direct first layer."""
