@@ -413,7 +413,8 @@ def main():
                                "achieved": sm_bytes / (smp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
                                "launch_ms": smp_ms, "launches_timed": len(smp),
-                               "traffic": 428.1e6 if (args.config == "products-like" and args.window == 8) else None,
+                               "traffic": 338.7e6 if (args.config == "products-like" and args.window == 8 and args.teams == 0
+                                                       and args.table_slots < 0) else None,
                                "note": "event-timed on the launching stream; includes the host gap before the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
