@@ -115,3 +115,13 @@ def test_gradient_all_reduce_and_seed_split_on_two_gloo_ranks(tmp_path):
     mp.spawn(_ddp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     g0, g1 = torch.load(tmp_path / "g0.pt"), torch.load(tmp_path / "g1.pt")
     assert torch.equal(g0, g1)                                      # both ranks hold the same averaged gradient
+
+
+def test_gcn_order_cost_model():
+    """Aggregate-first wins where many gathered rows feed few output rows of a narrower layer (the first layer of
+    the 602-d workload); update-first wins where the layer shrinks the rows a lot and the block is not much
+    smaller on the destination side."""
+    from fastgl_b200.layers import gcn_aggregate_first
+    assert gcn_aggregate_first(n_src=233_000, n_dst=11_000, n_edges=281_000, in_dim=602, out_dim=256)
+    assert gcn_aggregate_first(n_src=60_000, n_dst=6_000, n_edges=61_000, in_dim=256, out_dim=256)
+    assert not gcn_aggregate_first(n_src=1_200, n_dst=1_000, n_edges=400_000, in_dim=1024, out_dim=8)
