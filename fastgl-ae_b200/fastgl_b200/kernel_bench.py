@@ -93,6 +93,24 @@ def run(indptr, indices, feat, train, fanouts, batch: int, window: int, peak_gbs
     entry("sample_map_kernel (fgl_sample_map_fused)", f"window {window} x {batch} seeds, fanouts {fan_s}, {edges} edges",
           nbytes, ms, note=f"{edges / (ms * 1e-3) / 1e6:.0f} M sampled edges/s")
 
+    # what the trainer does from its second window on: tables capped at 2.5 slots per node of the largest mini-batch
+    # (L2-resident), every mini-batch of the window in flight
+    import math
+    most = max(c[b][L] for b in range(window))
+    cap_slots = 1 << max(12, math.ceil(math.log2(2.5 * most)))
+    capped = {"fb": None}
+
+    def fused_capped(i):
+        capped["fb"] = fastgl.sample_map_fused(indptr, indices, seeds_list[i % reps], counts, fan_s, replace=False,
+                                               rng_seed=12345, rng_ctr=1000 * i, n_teams=min(window, 16),
+                                               table_slots=cap_slots, out=capped["fb"])
+    ms_cap = _timed(fused_capped, reps, flush)
+    fastgl.check_status(dev)
+    entry("sample_map_kernel, tables sized from the data (fgl_sample_map_fused)",
+          f"window {window} x {batch} seeds, {min(window, 16)} teams, {cap_slots} slots per table", nbytes, ms_cap,
+          note=f"{edges / (ms_cap * 1e-3) / 1e6:.0f} M sampled edges/s; the default above uses 4 teams and worst-case tables")
+    del capped
+
     # the reference's own numbering (atomic arrival order) skips the two ranking phases
     arr = {"fb": None}
 
