@@ -239,7 +239,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="fastgl", choices=["fastgl", "reference"])
     ap.add_argument("--config", default="products-like", choices=sorted(CONFIGS))
-    ap.add_argument("--window", type=int, default=8, help="mini-batches sampled per kernel launch")
+    ap.add_argument("--window", type=int, default=16, help="mini-batches sampled per kernel launch")
     ap.add_argument("--teams", type=int, default=0)
     ap.add_argument("--table-slots", type=int, default=-1,
                     help="cap of the sampler's per-team hashtable (0: worst-case size; default: learnt from the first window)")
@@ -402,10 +402,12 @@ def main():
         achieved = alg / (mean_ms * 1e-3) / 1e9
         roofline.update({"achieved": achieved, "frac": achieved / peak, "algorithmic_bytes_per_launch": alg,
                          "launch_ms": mean_ms, "launches_timed": len(agg_ms)})
-        if args.config == "products-like" and args.window == 8:
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, taken from
-            # an ncu capture (ncu --set full) of the same command
-            roofline["traffic"] = 744.6e6
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the two window-level kernels on this workload,
+        # taken from ncu captures (ncu --set full) of the same command at these window sizes (profiles/)
+        ncu_traffic = {8: (744.6e6, 338.7e6), 16: (1467.5e6, 1011.0e6)}
+        default_run = args.config == "products-like" and args.teams == 0 and args.table_slots < 0
+        if default_run and args.window in ncu_traffic:
+            roofline["traffic"] = ncu_traffic[args.window][0]
         smp = [s.elapsed_time(e) for s, e, nb in tr.sample_events if nb == args.window]
         if smp:
             smp_ms = statistics.mean(smp)
@@ -413,8 +415,7 @@ def main():
                                "achieved": sm_bytes / (smp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
                                "launch_ms": smp_ms, "launches_timed": len(smp),
-                               "traffic": 338.7e6 if (args.config == "products-like" and args.window == 8 and args.teams == 0
-                                                       and args.table_slots < 0) else None,
+                               "traffic": ncu_traffic[args.window][1] if (default_run and args.window in ncu_traffic) else None,
                                "note": "event-timed on the launching stream; includes the host gap before the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
@@ -458,7 +459,7 @@ def main():
         launches = args.steps * per_step + 2 * n_windows
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_json,
+                "vs_baseline": None, "dtype": "f32" if args.matmul == "fp32" else "tf32", "data": "synthetic", "config": config_json,
                 "per_gpu_value": value / world, "epoch_time_s": steps_per_epoch * ms / args.steps * 1e-3,
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
                 "dense_matmul": args.matmul, "cuda_graph": not args.no_graph, "graph_fallback_steps": tr.graph_fallbacks,

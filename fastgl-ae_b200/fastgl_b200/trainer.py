@@ -288,6 +288,12 @@ class Trainer:
 
     def _next_window_seeds(self, n_batches: int):
         """int32[n_batches, batch_size] seeds (wrapping into the next epoch's shuffle) and their counts."""
+        span = n_batches * self.batch_size
+        if 0 < span <= self.my_seeds.numel() - self.cursor:
+            # the whole window lies inside this epoch's shuffle: a view, no kernels
+            seeds = self.my_seeds[self.cursor: self.cursor + span].view(n_batches, self.batch_size)
+            self.cursor += span
+            return seeds, torch.full((n_batches,), self.batch_size, dtype=torch.int32)
         rows, counts = [], []
         for _ in range(n_batches):
             if self.cursor >= self.my_seeds.numel():
@@ -419,6 +425,11 @@ class Trainer:
                 # which keeps it L2-resident (the worst-case size is 16 MB per team at the benchmark shapes)
                 most = int(fb.counts_host()[:, len(self.fanouts)].max())
                 self.table_slots = 1 << max(12, math.ceil(math.log2(max(1.0, 2.5 * most))))
+                # let the library size its workspace for the new team count now (an empty window through the
+                # other set of buffers), not in front of the next window's launch
+                self.sampler.sample_window(seeds, torch.zeros_like(counts), n_teams=self._sampler_teams(), slot=slot ^ 1,
+                                           table_slots=self.table_slots)
+                self.sampler.batch_counter -= nb
             layer0 = self.aggregate_window_layer0(fb) if self.window_layer0 else None
             order = list(range(nb))
             if self.matcher is not None:
