@@ -450,12 +450,12 @@ def main():
         steps_per_epoch = tr.steps_per_epoch()
         # kernels of this library: per window one fused sampling launch and one first-layer aggregation launch; per
         # step one staging launch and, inside the replayed step program, per inner layer one forward aggregation, one
-        # self-gradient initialisation and one backward scatter, per layer one bias/ReLU/dropout epilogue and one
-        # backward of it, two loss launches and one Adam launch (5 L + 1).  The op-by-op path (--no-graph) launches
-        # one forward and one backward aggregation per inner layer.
+        # self-gradient initialisation and one backward scatter, per hidden layer one bias/ReLU/dropout epilogue and
+        # one backward of it, two launches for the output layer with its loss, and one Adam launch (5 L - 1).  The
+        # op-by-op path (--no-graph) launches one forward and one backward aggregation per inner layer.
         n_windows = (args.steps + args.window - 1) // args.window
         n_layers = len(cfg["fanouts"])
-        per_step = (5 * n_layers + 1) if tr.graphed is not None else 2 * (n_layers - 1)
+        per_step = (5 * n_layers - 1) if tr.graphed is not None else 2 * (n_layers - 1)
         launches = args.steps * per_step + 2 * n_windows
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",

@@ -146,6 +146,139 @@ softmax_xent_rows_kernel(const float* __restrict__ logits, int64_t ld, const int
     if (lane == 0) row_loss[r] = mine;
 }
 
+// The output layer and its loss in one pass: logits = x W + b for a narrow W (n_classes <= 32 * CPL), then the
+// softmax cross-entropy row loss, the gradient of the logits and the bias gradient.  Replaces a small GEMM that
+// runs at a few TFLOP/s, a bias add, the loss and a column sum.
+// A CTA of eight warps owns kLinXentRows rows.  Warp w multiplies the w-th eighth of the k range for all of the
+// CTA's rows at once: lane l keeps x[row][k0 + l] of a 32-column chunk and hands it around by shuffle, every lane
+// owns the classes lane, lane + 32, ... and reads W row by row (coalesced over the classes; W is k x n_classes
+// floats and stays in L1/L2), so one W load feeds kLinXentRows FMAs.  The eight partial products meet in shared
+// memory; warp r then finishes row r.
+constexpr int kLinXentWarps = 8;
+constexpr int kLinXentRows = 4;
+
+template <int CPL>
+__global__ void __launch_bounds__(kLinXentWarps * 32)
+linear_xent_kernel(const float* __restrict__ x, int64_t ldx, int k, const float* __restrict__ w, int64_t ldw,
+                   const float* __restrict__ bias, const int64_t* __restrict__ labels, const int32_t* __restrict__ label_ids,
+                   int64_t n_labels, int n_rows, int n_classes, const int32_t* __restrict__ n_valid_dev, int n_valid_host,
+                   float* __restrict__ row_loss, float* __restrict__ dlogits, int64_t ldd, float* __restrict__ dbias,
+                   float* __restrict__ logits_out, int64_t ldl, int32_t* __restrict__ status) {
+    __shared__ float part[kLinXentWarps][kLinXentRows][32 * CPL];
+    __shared__ float db[32 * CPL];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = blockIdx.x * kLinXentRows;
+    for (int c = threadIdx.x; c < 32 * CPL; c += blockDim.x) db[c] = 0.f;
+    int n_valid = n_valid_dev ? n_valid_dev[0] : n_valid_host;
+    n_valid = n_valid < 0 ? 0 : (n_valid > n_rows ? n_rows : n_valid);
+    const float inv = n_valid > 0 ? 1.f / (float)n_valid : 0.f;
+    // rows that need their logits: the valid ones, or all of them when the caller wants the logits
+    const int rows_here = min(kLinXentRows, (logits_out ? n_rows : n_valid) - row0);
+
+    float acc[kLinXentRows][CPL];
+#pragma unroll
+    for (int r = 0; r < kLinXentRows; ++r)
+#pragma unroll
+        for (int q = 0; q < CPL; ++q) acc[r][q] = 0.f;
+    if (rows_here > 0) {
+        const int slice = ((k + kLinXentWarps - 1) / kLinXentWarps + 31) / 32 * 32;   // columns per warp, whole chunks
+        const int k_lo = warp * slice, k_hi = min(k, k_lo + slice);
+        for (int kb = k_lo; kb < k_hi; kb += 32) {
+            float xr[kLinXentRows];
+#pragma unroll
+            for (int r = 0; r < kLinXentRows; ++r)
+                xr[r] = (r < rows_here && kb + lane < k_hi) ? x[(int64_t)(row0 + r) * ldx + kb + lane] : 0.f;
+            const int cols = min(32, k_hi - kb);
+#pragma unroll 8
+            for (int t = 0; t < cols; ++t) {
+                const float* wr = w + (int64_t)(kb + t) * ldw;
+                float wv[CPL];
+#pragma unroll
+                for (int q = 0; q < CPL; ++q) wv[q] = (lane + 32 * q < n_classes) ? __ldg(wr + lane + 32 * q) : 0.f;
+#pragma unroll
+                for (int r = 0; r < kLinXentRows; ++r) {
+                    const float xv = __shfl_sync(0xffffffffu, xr[r], t);
+#pragma unroll
+                    for (int q = 0; q < CPL; ++q) acc[r][q] = fmaf(xv, wv[q], acc[r][q]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kLinXentRows; ++r)
+#pragma unroll
+        for (int q = 0; q < CPL; ++q) part[warp][r][lane + 32 * q] = acc[r][q];
+    __syncthreads();
+
+    // warp r finishes row row0 + r
+    const int r = row0 + warp;
+    if (warp < kLinXentRows && r < n_rows) {
+        float* d = dlogits + (int64_t)r * ldd;
+        float z[CPL];
+#pragma unroll
+        for (int q = 0; q < CPL; ++q) {
+            const int c = lane + 32 * q;
+            float t = (bias && c < n_classes) ? bias[c] : 0.f;
+#pragma unroll
+            for (int ww = 0; ww < kLinXentWarps; ++ww) t += part[ww][warp][c];
+            z[q] = t;
+        }
+        if (logits_out) {
+#pragma unroll
+            for (int q = 0; q < CPL; ++q)
+                if (lane + 32 * q < n_classes) logits_out[(int64_t)r * ldl + lane + 32 * q] = z[q];
+        }
+        float mine = 0.f;
+        bool counted = false;
+        if (r < n_valid) {
+            const int64_t at = label_ids ? (int64_t)label_ids[r] : (int64_t)r;
+            const int64_t label = at >= 0 && at < n_labels ? labels[at] : -1;
+            if (label < 0 || label >= n_classes) {
+                if (lane == 0) atomicCAS(status, FGL_OK, FGL_ERR_BOUNDS);
+            } else {
+                counted = true;
+                float m = -INFINITY;
+#pragma unroll
+                for (int q = 0; q < CPL; ++q)
+                    if (lane + 32 * q < n_classes) m = fmaxf(m, z[q]);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                float e[CPL], sum = 0.f, at_label = 0.f;
+#pragma unroll
+                for (int q = 0; q < CPL; ++q) {
+                    const int c = lane + 32 * q;
+                    e[q] = c < n_classes ? expf(z[q] - m) : 0.f;
+                    sum += e[q];
+                    if (c == (int)label) at_label = z[q];
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                    at_label += __shfl_xor_sync(0xffffffffu, at_label, o);
+                }
+                mine = m + logf(sum) - at_label;
+                const float rs = inv / sum;
+#pragma unroll
+                for (int q = 0; q < CPL; ++q) {
+                    const int c = lane + 32 * q;
+                    if (c < n_classes) {
+                        const float g = e[q] * rs - (c == (int)label ? inv : 0.f);
+                        d[c] = g;
+                        if (dbias) atomicAdd(&db[c], g);
+                    }
+                }
+            }
+        }
+        if (!counted)
+            for (int c = lane; c < n_classes; c += 32) d[c] = 0.f;
+        if (lane == 0) row_loss[r] = mine;
+    }
+    __syncthreads();
+    if (dbias)
+        for (int c = threadIdx.x; c < n_classes; c += blockDim.x)
+            if (db[c] != 0.f) atomicAdd(dbias + c, db[c]);
+}
+
 // loss[0] = (sum of row_loss in a fixed order) / n_valid: thread t adds rows t, t + 256, ... in order, then the
 // 256 partial sums are folded by a fixed tree, so the loss is reproducible from run to run.
 __global__ void __launch_bounds__(kEwThreads)
@@ -279,6 +412,28 @@ int fgl_softmax_xent(fgl_ws* ws, const float* logits, int64_t ld, const int64_t*
     cudaStream_t st = (cudaStream_t)stream;
     softmax_xent_rows_kernel<<<(n_rows + kXentWarps - 1) / kXentWarps, kXentWarps * 32, 0, st>>>(
         logits, ld, labels, label_ids, n_labels, n_rows, n_classes, n_valid_dev, n_valid, row_loss, dlogits, ldd, ws->status);
+    softmax_xent_mean_kernel<<<1, kEwThreads, 0, st>>>(row_loss, n_rows, n_valid_dev, n_valid, loss);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_linear_softmax_xent(fgl_ws* ws, const float* x, int64_t ldx, int32_t k, const float* w, int64_t ldw, const float* bias,
+                            const int64_t* labels, const int32_t* label_ids, int64_t n_labels, int32_t n_rows,
+                            int32_t n_classes, const int32_t* n_valid_dev, int32_t n_valid, float* loss, float* dlogits,
+                            int64_t ldd, float* dbias, float* logits_out, int64_t ldl, float* row_loss, void* stream) {
+    if (!ws || n_rows < 0 || k <= 0 || n_classes <= 0 || n_classes > 128 || ldx < k || ldw < n_classes || ldd < n_classes ||
+        !loss || (logits_out && ldl < n_classes) || (n_rows > 0 && (!x || !w || !labels || !dlogits || !row_loss)))
+        return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_rows == 0) return cudaMemsetAsync(loss, 0, sizeof(float), st) == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+    const int grid = (n_rows + kLinXentRows - 1) / kLinXentRows;
+#define FGL_LINXENT(CPL)                                                                                              \
+    linear_xent_kernel<CPL><<<grid, kLinXentWarps * 32, 0, st>>>(x, ldx, k, w, ldw, bias, labels, label_ids, n_labels, \
+                                                                 n_rows, n_classes, n_valid_dev, n_valid, row_loss,   \
+                                                                 dlogits, ldd, dbias, logits_out, ldl, ws->status)
+    if (n_classes <= 32) FGL_LINXENT(1);
+    else if (n_classes <= 64) FGL_LINXENT(2);
+    else FGL_LINXENT(4);
+#undef FGL_LINXENT
     softmax_xent_mean_kernel<<<1, kEwThreads, 0, st>>>(row_loss, n_rows, n_valid_dev, n_valid, loss);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }

@@ -517,6 +517,51 @@ def softmax_xent(logits, labels, label_ids=None, n_valid=None, loss=None, dlogit
     return loss, dlogits
 
 
+def linear_softmax_xent(x, weight, bias, labels, label_ids=None, n_valid=None, loss=None, dlogits=None, row_loss=None,
+                        dbias=None, logits=None):
+    """``softmax_xent(x @ weight + bias, ...)`` in one pass for at most 128 classes: returns (loss, dlogits); ``dbias``
+    (float32[n_classes], zeroed by the caller) also receives the bias gradient and ``logits`` the logits."""
+    _check_rows_f32(x, "x")
+    _check_rows_f32(weight, "weight")
+    if weight.size(0) != x.size(1) or weight.size(1) > 128:
+        raise RuntimeError("weight must be float32[x.size(1), n_classes <= 128]")
+    _check_input(labels, "labels")
+    if labels.dtype != torch.int64:
+        raise RuntimeError("labels must be int64")
+    for t, n in ((bias, "bias"), (dbias, "dbias")):
+        if t is not None:
+            _check_f32(t, n)
+            if t.numel() != weight.size(1):
+                raise RuntimeError(f"{n} must have one entry per class")
+    if label_ids is not None:
+        _check_i32(label_ids, "label_ids")
+    dev = x.device
+    n_rows, k, n_classes = x.size(0), x.size(1), weight.size(1)
+    loss = torch.empty(1, dtype=torch.float32, device=dev) if loss is None else loss
+    dlogits = torch.empty((n_rows, n_classes), dtype=torch.float32, device=dev) if dlogits is None else dlogits
+    _check_rows_f32(dlogits, "dlogits")
+    row_loss = torch.empty(max(n_rows, 1), dtype=torch.float32, device=dev) if row_loss is None else row_loss
+    _check_f32(row_loss, "row_loss")
+    if logits is not None:
+        _check_rows_f32(logits, "logits")
+    if row_loss.numel() < n_rows or dlogits.size(0) < n_rows or (logits is not None and logits.size(0) < n_rows):
+        raise RuntimeError("row_loss, dlogits and logits must hold one row per row of x")
+    n_valid_dev = n_valid if torch.is_tensor(n_valid) else None
+    if n_valid_dev is not None:
+        _check_i32(n_valid_dev, "n_valid")
+    ws = _ws(dev)
+    with _on_device(dev):
+        rc = lib().fgl_linear_softmax_xent(
+            ws, _ptr(x), ctypes.c_int64(x.stride(0)), ctypes.c_int32(k), _ptr(weight), ctypes.c_int64(weight.stride(0)),
+            _ptr(bias), _ptr(labels), _ptr(label_ids), ctypes.c_int64(labels.numel()), ctypes.c_int32(n_rows),
+            ctypes.c_int32(n_classes), _ptr(n_valid_dev),
+            ctypes.c_int32(n_rows if n_valid is None or n_valid_dev is not None else int(n_valid)), _ptr(loss), _ptr(dlogits),
+            ctypes.c_int64(dlogits.stride(0)), _ptr(dbias), _ptr(logits),
+            ctypes.c_int64(logits.stride(0) if logits is not None else n_classes), _ptr(row_loss), _stream(dev))
+    _raise(rc, "linear_softmax_xent", ws)
+    return loss, dlogits
+
+
 def adam_step_(param, grad, exp_avg, exp_avg_sq, step_dev, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
     """One Adam step (torch.optim.Adam's arithmetic, L2 weight decay) over flat float32 buffers, in place.
     ``step_dev``: int32[2] CUDA tensor, zero before the first step; the launch itself advances ``step_dev[0]``."""

@@ -61,7 +61,12 @@ class SageStepProgram:
         (float32[1], a static buffer)."""
         L, p = self.L, self.p_drop
         training = self.model.training
+        self.grads.zero()
+        last = self.layers[L - 1]
+        fused_head = last.weight.size(1) <= 128        # output layer and loss in one launch
         for i, layer in enumerate(self.layers):
+            if i == L - 1 and fused_head:
+                break
             torch.mm(self.cat[i], layer.weight, out=self.z[i])
             if i < L - 1:
                 blk = self.blocks[i + 1]
@@ -73,13 +78,17 @@ class SageStepProgram:
                                  zero_deg_passthrough=False, out=nxt[:, d:], n_dst_dev=blk.n_dst_dev)
             else:
                 fastgl.bias_relu_dropout_(self.z[i], layer.bias, 0.0, relu=False)
-        fastgl.softmax_xent(self.z[L - 1], self.labels, label_ids=self.seeds, n_valid=self.sizes[L - 1: L], loss=self.loss,
-                            dlogits=self.dlogits, row_loss=self.row_loss)
-        self.grads.zero()
+        if fused_head:
+            fastgl.linear_softmax_xent(self.cat[L - 1], last.weight, last.bias, self.labels, label_ids=self.seeds,
+                                       n_valid=self.sizes[L - 1: L], loss=self.loss, dlogits=self.dlogits,
+                                       row_loss=self.row_loss, dbias=last.bias.grad)
+        else:
+            fastgl.softmax_xent(self.z[L - 1], self.labels, label_ids=self.seeds, n_valid=self.sizes[L - 1: L], loss=self.loss,
+                                dlogits=self.dlogits, row_loss=self.row_loss)
         dz = self.dlogits
         for i in reversed(range(L)):
             layer = self.layers[i]
-            if i == L - 1:
+            if i == L - 1 and not fused_head:
                 fastgl.relu_dropout_backward_(dz, masked=False, dbias=layer.bias.grad)
             self._weight_grad(i, dz)
             if i > 0:

@@ -291,6 +291,15 @@ int fgl_softmax_xent(fgl_ws* ws, const float* logits, int64_t ld, const int64_t*
                      int64_t n_labels, int32_t n_rows, int32_t n_classes, const int32_t* n_valid_dev, int32_t n_valid,
                      float* loss, float* dlogits, int64_t ldd, float* row_loss, void* stream);
 
+/* The output layer and its loss in one pass, for n_classes <= 128: logits = x W + bias (x float32[n_rows][k], W
+ * float32[k][n_classes] row-major, bias may be NULL), then exactly what fgl_softmax_xent computes from those
+ * logits (same label lookup, masking, loss and dlogits).  dbias (may be NULL) is incremented by the column sums of
+ * dlogits (the caller zeroes it); logits_out (may be NULL) receives the logits of every row. */
+int fgl_linear_softmax_xent(fgl_ws* ws, const float* x, int64_t ldx, int32_t k, const float* w, int64_t ldw, const float* bias,
+                            const int64_t* labels, const int32_t* label_ids, int64_t n_labels, int32_t n_rows,
+                            int32_t n_classes, const int32_t* n_valid_dev, int32_t n_valid, float* loss, float* dlogits,
+                            int64_t ldd, float* dbias, float* logits_out, int64_t ldl, float* row_loss, void* stream);
+
 /* One Adam step with L2 weight decay over flat fp32 buffers of n elements (16-byte aligned), with the arithmetic
  * of torch.optim.Adam: g += wd * p; m = b1 m + (1 - b1) g; v = b2 v + (1 - b2) g^2;
  * p -= lr / (1 - b1^t) * m / (sqrt(v) / sqrt(1 - b2^t) + eps), t = step_dev[0] + 1.  step_dev is two int32 words

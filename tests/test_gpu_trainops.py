@@ -106,6 +106,38 @@ def test_softmax_cross_entropy_and_gradient(fastgl, rows, classes, n_valid):
     assert float(loss2) == float(loss)
 
 
+@pytest.mark.parametrize("rows,k,classes,n_valid", [(1024, 512, 47, 1024), (1024, 512, 47, 700), (50, 37, 7, 50), (300, 128, 100, 299),
+                                                    (64, 256, 128, 64), (9, 3, 33, 0)])
+def test_output_layer_and_loss_in_one_pass(fastgl, rows, k, classes, n_valid):
+    g = torch.Generator(device=DEV).manual_seed(rows + k)
+    x = torch.randn((rows, k), generator=g, device=DEV)
+    w = (torch.randn((k, classes), generator=g, device=DEV) / k ** 0.5).requires_grad_(True)
+    b = torch.randn(classes, generator=g, device=DEV).requires_grad_(True)
+    table = torch.randint(0, classes, (3000,), generator=g, device=DEV)
+    ids = torch.randint(0, 3000, (rows,), generator=g, device=DEV).to(torch.int32)
+    dbias = torch.zeros(classes, device=DEV)
+    logits = torch.empty((rows, classes), device=DEV)
+    loss, dlogits = fastgl.linear_softmax_xent(x, w.detach(), b.detach(), table, label_ids=ids,
+                                               n_valid=torch.tensor([n_valid], dtype=torch.int32, device=DEV), dbias=dbias,
+                                               logits=logits)
+    fastgl.check_status()
+    ref_logits = x.double() @ w.double() + b.double()
+    assert float((logits.double() - ref_logits.detach()).abs().max()) <= 2e-5 * max(1.0, float(ref_logits.abs().max()))
+    if n_valid == 0:
+        assert float(loss) == 0.0 and float(dlogits.abs().max()) == 0.0 and float(dbias.abs().max()) == 0.0
+        return
+    y = table[ids.long()]
+    ref = torch.nn.functional.cross_entropy(ref_logits[:n_valid], y[:n_valid])
+    gw, gb = torch.autograd.grad(ref, (w, b))
+    assert abs(float(loss) - float(ref.detach())) <= 1e-5 * max(1.0, abs(float(ref.detach())))
+    assert float((dbias.double() - gb.double()).abs().max()) <= 1e-6
+    got_gw = x.double().t() @ dlogits.double()                 # the weight gradient the step computes from dlogits
+    assert float((got_gw - gw.double()).abs().max()) <= 1e-5 * max(1.0, float(gw.abs().max()))
+    # the unfused pair gives the same numbers
+    loss2, dl2 = fastgl.softmax_xent(logits, table, label_ids=ids, n_valid=n_valid)
+    assert abs(float(loss2) - float(loss)) <= 1e-6 and float((dl2 - dlogits).abs().max()) <= 1e-7
+
+
 def test_softmax_cross_entropy_reports_a_bad_label(fastgl):
     logits = torch.zeros((4, 3), device=DEV)
     labels = torch.tensor([0, 1, 7, 2], device=DEV)
