@@ -97,7 +97,7 @@ class GraphedStep:
     optimizer step -- captured once as a CUDA graph over buffers of fixed, padded shape and replayed for every
     mini-batch.  A staging kernel copies the batch's first-layer rows and inner blocks into those buffers and
     writes the real row counts, which the aggregation kernels read on the device.  The captured work is the
-    hand-written launch sequence of ``sage_step.SageStepProgram`` (29 launches).  This removes the host launches
+    hand-written launch sequence of ``sage_step.SageStepProgram`` (about 25 launches).  This removes the host launches
     that otherwise bound the step time (the reference even blocks on an event three times per step,
     train_fastgl.py:348,362,373)."""
 
