@@ -248,7 +248,7 @@ def main():
                     help="arithmetic of the dense-layer GEMMs that stay in PyTorch (tf32 is what the reference's "
                          "pinned PyTorch 1.10.1 used by default on Ampere)")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-batch step op by op instead of a CUDA graph")
-    ap.add_argument("--cpu-steps", type=int, default=3, help="mini-batches of the CPU baseline sample")
+    ap.add_argument("--cpu-steps", type=int, default=150, help="mini-batches of the CPU baseline sample (about 10 s of CPU work)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gates", action="store_true", help="skip the untimed correctness gates (profiler runs)")
     ap.add_argument("--kernels", action="store_true",
