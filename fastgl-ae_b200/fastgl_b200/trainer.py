@@ -254,23 +254,57 @@ class Trainer:
         teams = min(self.window, 16)
         return teams if teams * self.table_slots * 8 <= (64 << 20) else 0
 
+    def _ensure_graph(self, fb, b, layer0):
+        """Build and capture the step program on the shapes of window ``fb`` (staged with its batch ``b``)."""
+        if self.graphed is not None:
+            return
+        L = len(self.fanouts)
+        pad = []
+        for i in range(L):
+            n = int(fb.counts_host()[:, L - 1 - i].max())
+            pad.append(self.batch_size if i == L - 1 else ((int(n * 1.12) + 255) // 256) * 256)
+        self.graphed = GraphedStep(self, pad)
+        self.graphed.stage(fb, b, fb.counts_list()[b], layer0)
+        self.graphed.capture()
+
     def _graph_step(self, fb, b, layer0):
         """Replay the captured step for batch ``b``; returns None when the batch does not fit the padded shapes."""
         counts_row = fb.counts_list()[b]
-        L = len(self.fanouts)
-        if self.graphed is None:
-            pad = []
-            for i in range(L):
-                n = int(fb.counts_host()[:, L - 1 - i].max())
-                pad.append(self.batch_size if i == L - 1 else ((int(n * 1.12) + 255) // 256) * 256)
-            self.graphed = GraphedStep(self, pad)
-            self.graphed.stage(fb, b, counts_row, layer0)
-            self.graphed.capture()
+        self._ensure_graph(fb, b, layer0)
         if not self.graphed.fits(counts_row):
             self.graph_fallbacks += 1
             return None
         self.graphed.stage(fb, b, counts_row, layer0)
         return self.graphed.replay()
+
+    def prime(self):
+        """One-time set-up that would otherwise happen inside the first windows of training: sample one full window
+        of this rank's seeds (without consuming them or their random-number counters), size the sampler's tables and
+        workspace from it, and capture the step program on its shapes.  Parameters and optimizer state are left as
+        they were."""
+        if not self.my_seeds.numel():
+            return
+        nb = self.window
+        need = nb * self.batch_size
+        reps = -(-need // self.my_seeds.numel())
+        seeds = self.my_seeds.repeat(reps)[:need].view(nb, self.batch_size).contiguous()
+        counts = torch.full((nb,), self.batch_size, dtype=torch.int32, device=self.dev)
+        counter = self.sampler.batch_counter
+        fb = self.sampler.sample_window(seeds, counts, n_teams=self._sampler_teams(), slot=0, table_slots=self.table_slots)
+        fb.start_readback()
+        fb.counts_host()
+        if fb.device_status != 0:
+            fastgl.check_status(self.dev)
+        if self._auto_table and self.table_slots == 0:
+            most = int(fb.counts_host()[:, len(self.fanouts)].max())
+            self.table_slots = 1 << max(12, math.ceil(math.log2(max(1.0, 2.5 * most))))
+            self.sampler.sample_window(seeds, torch.zeros_like(counts), n_teams=self._sampler_teams(), slot=1,
+                                       table_slots=self.table_slots)
+        if self.use_graph and self.window_layer0:
+            layer0 = self.aggregate_window_layer0(fb)
+            self._ensure_graph(fb, 0, layer0)
+        self.sampler.batch_counter = counter
+        torch.cuda.synchronize(self.dev)
 
     def _shuffled_share(self, epoch: int) -> torch.Tensor:
         return shard_seeds(self._train_nids_host, self.rank, self.world, 12345 + epoch)   # host only: no CUDA call

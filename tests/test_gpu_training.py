@@ -166,6 +166,21 @@ def test_trainer_recovers_from_a_hashtable_cap_that_is_too_small():
     assert plain.sampled_edges == capped.sampled_edges
 
 
+def test_prime_changes_nothing_but_the_set_up():
+    problem = setup_problem(seed=17)
+    plain = make_trainer(problem, cuda_graph=True)
+    primed = make_trainer(problem, cuda_graph=True)
+    before = [p.detach().clone() for p in primed.model.parameters()]
+    primed.prime()
+    assert primed.graphed is not None and primed.table_slots > 0 and primed.sampler.batch_counter == 0
+    for p, q in zip(primed.model.parameters(), before):
+        assert torch.equal(p, q)
+    lp = plain.run_steps(9, read_loss_each_step=True)
+    lq = primed.run_steps(9, read_loss_each_step=True)
+    assert np.allclose(lp, lq, rtol=1e-5, atol=1e-6), (lp, lq)
+    assert plain.sampled_edges == primed.sampled_edges
+
+
 def test_gcn_layer_gives_the_same_result_in_either_order(monkeypatch):
     """A (x W) (the reference's order) and (A x) W, forward and backward, including destinations without in-edges
     (copied forward, skipped backward, as aggregate_acc_kernel.cu:307-308,:498-500) and the table-direct first layer."""
