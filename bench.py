@@ -25,6 +25,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "fastgl-ae_b200"))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))   # the size-independent gates (tests/checks.py)
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
@@ -207,7 +208,7 @@ def time_cpu_steps(step, n_steps):
 def run_gates(cfg, args, indptr, indices, feat, train, device):
     """Sample one window of the workload and check it (raises on a violated gate)."""
     import fastgl
-    from fastgl_b200.checks import EdgeKeys, check_window, check_window_aggregation
+    from checks import EdgeKeys, check_window, check_window_aggregation
     nb, batch = args.window, cfg["batch"]
     if train.numel() < nb * batch:
         nb = max(1, train.numel() // batch)
@@ -311,7 +312,7 @@ def main():
         model = GraphSAGE(cfg["feat_dim"], cfg["hidden"], cfg["n_classes"], len(cfg["fanouts"]), dropout=0.5).to(device)
     if args.kernels:
         # per-kernel roofline table on blocks of this workload (one GPU; no training)
-        from fastgl_b200 import kernel_bench
+        import bench_kernels as kernel_bench
         if world > 1 or not torch.is_tensor(feat):
             raise SystemExit("--kernels runs on one GPU with a dense feature table")
         peak, peak_kind = load_peaks()

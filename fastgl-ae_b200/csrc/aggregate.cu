@@ -88,7 +88,35 @@ struct AggParams {
     // FGL_AGG_EDGE: one weight per (edge, head), edge_w[e * n_heads + h]; head h covers dim / n_heads columns
     const float* edge_w;
     int32_t n_heads;
+    // bounds of the ids the kernels dereference: x (or the sharded table) has n_rows rows; with a row map the local
+    // ids index a map of n_map entries.  An id outside its range is never dereferenced: the edge (or the gathered
+    // row) contributes zeros and FGL_ERR_BOUNDS goes to *status (may be NULL).
+    int64_t n_rows;
+    int64_t n_map;
+    int32_t* status;
 };
+
+__device__ __forceinline__ void agg_bad_id(const AggParams& p) {
+    if (p.status) set_status(p.status, FGL_ERR_BOUNDS);
+}
+
+// Row of x that local id s stands for, or -1 (recorded) when s or the mapped row is out of range.
+template <bool HAS_MAP>
+__device__ __forceinline__ int64_t checked_row(const AggParams& p, const int32_t* row_map, int s) {
+    int64_t r = (int64_t)s;
+    if (HAS_MAP) {
+        if (s < 0 || (int64_t)s >= p.n_map) {
+            agg_bad_id(p);
+            return -1;
+        }
+        r = (int64_t)__ldg(row_map + s);
+    }
+    if (r < 0 || r >= p.n_rows) {
+        agg_bad_id(p);
+        return -1;
+    }
+    return r;
+}
 
 // Start of input row r: in the single table, or in the shard (possibly another GPU's HBM, read with plain
 // peer loads over NVLink) that owns it.
@@ -126,11 +154,13 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
     int64_t lo_n = 0, hi_n = window ? __ldg(p.out_row_off + 1) : total;
     int64_t row_n = 0, self_n = 0;
     float w_n = 1.0f;
+    unsigned bad_n = 0;  // neighbours (of the first 32) whose id is out of range: loaded from row 0, never added
     auto prefetch = [&](int64_t g) {
         a_n = 0;
         e_n = 0;
         row_n = 0;
         w_n = 1.0f;
+        bad_n = 0;
         if (g >= total) return;
         while (g >= hi_n) {  // window mode only: step to the mini-batch that holds row g
             ++b_n;
@@ -143,31 +173,42 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
         const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b_n * p.row_map_stride : nullptr;
         a_n = __ldg(indptr + d_n);
         e_n = __ldg(indptr + d_n + 1);
+        bool bad = false;
         if (lane < e_n - a_n) {
             const int s = __ldg(src + a_n + lane);
-            row_n = HAS_MAP ? (int64_t)__ldg(row_map + s) : (int64_t)s;
-            if (MODE == FGL_AGG_SYMNORM) w_n = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+            row_n = checked_row<HAS_MAP>(p, row_map, s);
+            bad = row_n < 0;
+            if (bad) row_n = 0;
+            if (MODE == FGL_AGG_SYMNORM && !bad) w_n = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
         }
-        self_n = HAS_MAP ? (int64_t)__ldg(row_map + d_n) : (int64_t)d_n;
+        bad_n = __ballot_sync(0xffffffffu, bad);
+        // the row's own input row, only validated where it is used (self copy, zero-degree pass-through)
+        self_n = HAS_MAP ? ((int64_t)d_n < p.n_map ? (int64_t)__ldg(row_map + d_n) : -1) : (int64_t)d_n;
     };
     prefetch(warp_global);
 
     for (int64_t g = warp_global; g < total; g += n_warps) {
         const int b = b_n, d = d_n, a = a_n, e_end = e_n;
-        const int64_t first_row = row_n, self_row = self_n;  // neighbours a .. a+31 and the row's own source
+        const int64_t first_row = row_n;  // neighbours a .. a+31
+        int64_t self_row = self_n;        // the row's own source row
         const float first_w = w_n;
+        const unsigned first_bad = bad_n;
+        if ((p.self_out || (a >= e_end && p.passthrough)) && (self_row < 0 || self_row >= p.n_rows)) {
+            agg_bad_id(p);
+            self_row = -1;
+        }
         prefetch(g + n_warps);
         const int32_t* src = p.src + (int64_t)b * p.src_stride;
         const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b * p.row_map_stride : nullptr;
         T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
         if (p.self_out) {
-            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row));
+            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
             T* srow = reinterpret_cast<T*>(p.self_out + g * p.ld_self);
-            for (int c = lane; c < chunks; c += 32) srow[c] = __ldg(xr + c);
+            for (int c = lane; c < chunks; c += 32) srow[c] = self_row < 0 ? V::zero() : __ldg(xr + c);
         }
         if (a >= e_end) {  // aggregate_acc_kernel.cu:307-308, :405-406
-            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row));
-            for (int c = lane; c < chunks; c += 32) orow[c] = p.passthrough ? __ldg(xr + c) : V::zero();
+            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
+            for (int c = lane; c < chunks; c += 32) orow[c] = (p.passthrough && self_row >= 0) ? __ldg(xr + c) : V::zero();
             continue;
         }
         float scale = 1.0f;
@@ -186,14 +227,19 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                 const int cnt = min(32, e_end - e0);
                 int64_t my_row = first_row;
                 float my_w = first_w;
+                unsigned bad_mask = first_bad;
                 if (e0 != a) {
                     my_row = 0;
                     my_w = 1.0f;
+                    bool bad = false;
                     if (lane < cnt) {
                         const int s = __ldg(src + e0 + lane);
-                        my_row = HAS_MAP ? (int64_t)__ldg(row_map + s) : (int64_t)s;
-                        if (MODE == FGL_AGG_SYMNORM) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+                        my_row = checked_row<HAS_MAP>(p, row_map, s);
+                        bad = my_row < 0;
+                        if (bad) my_row = 0;
+                        if (MODE == FGL_AGG_SYMNORM && !bad) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
                     }
+                    bad_mask = __ballot_sync(0xffffffffu, bad);
                 }
                 for (int j0 = 0; j0 < cnt; j0 += UNR) {
                     T v[UNR][NACC];
@@ -212,7 +258,7 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                     }
 #pragma unroll
                     for (int u = 0; u < UNR; ++u) {
-                        if (j0 + u < cnt) {  // warp-uniform
+                        if (j0 + u < cnt && !((bad_mask >> (j0 + u)) & 1u)) {  // warp-uniform
 #pragma unroll
                             for (int k = 0; k < NACC; ++k) {
                                 const float wk = (MODE == FGL_AGG_EDGE)
@@ -245,10 +291,14 @@ __global__ void __launch_bounds__(kAggThreads) gather_rows_kernel(const AggParam
     constexpr int UNR = 4;
     for (int64_t i0 = warp_global * UNR; i0 < n_ids; i0 += n_warps * UNR) {
         const T* src[UNR];
+        bool ok[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             const int64_t i = i0 + u < n_ids ? i0 + u : n_ids - 1;
-            src[u] = reinterpret_cast<const T*>(x_row(p, (int64_t)__ldg(ids + i)));
+            const int64_t r = (int64_t)__ldg(ids + i);
+            ok[u] = r >= 0 && r < p.n_rows;
+            if (!ok[u]) agg_bad_id(p);
+            src[u] = reinterpret_cast<const T*>(x_row(p, ok[u] ? r : 0));
         }
         for (int c = lane; c < chunks; c += 32) {
             T v[UNR];
@@ -256,7 +306,7 @@ __global__ void __launch_bounds__(kAggThreads) gather_rows_kernel(const AggParam
             for (int u = 0; u < UNR; ++u) v[u] = __ldg(src[u] + c);
 #pragma unroll
             for (int u = 0; u < UNR; ++u)
-                if (i0 + u < n_ids) reinterpret_cast<T*>(p.out + (i0 + u) * p.ldo)[c] = v[u];
+                if (i0 + u < n_ids) reinterpret_cast<T*>(p.out + (i0 + u) * p.ldo)[c] = ok[u] ? v[u] : Vec<VEC>::zero();
         }
     }
 }
@@ -299,12 +349,15 @@ __global__ void __launch_bounds__(kAggThreads) agg_bwd_kernel(const AggParams p)
                 float my_w = 1.0f;
                 if (lane < cnt) {
                     my_s = __ldg(p.src + e0 + lane);
-                    if (MODE == FGL_AGG_SYMNORM) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + my_s));
+                    if (MODE == FGL_AGG_SYMNORM && my_s >= 0 && my_s < p.n_src) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + my_s));
                 }
                 for (int j = 0; j < cnt; ++j) {
                     const int s = __shfl_sync(0xffffffffu, my_s, j);
                     const float w = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, j) : 1.0f;
-                    if (s < 0 || s >= p.n_src) continue;  // warp-uniform
+                    if (s < 0 || s >= p.n_src) {  // warp-uniform
+                        agg_bad_id(p);
+                        continue;
+                    }
                     T* xr = reinterpret_cast<T*>(p.out + (int64_t)s * p.ldo);
 #pragma unroll
                     for (int k = 0; k < NACC; ++k) {
@@ -346,6 +399,10 @@ __global__ void __launch_bounds__(kAggThreads) agg_edge_wgrad_kernel(const AggPa
             const bool leader = live && (lane == 0 || prev_head != head);
             for (int e = a; e < b; ++e) {
                 const int s = __ldg(p.src + e);
+                if (s < 0 || s >= p.n_src) {  // warp-uniform: dw[e, :] stays zero
+                    agg_bad_id(p);
+                    continue;
+                }
                 float v = 0.0f;
                 if (live) {
                     const T xv = __ldg(reinterpret_cast<const T*>(p.x + (int64_t)s * p.ldx) + c);
@@ -441,11 +498,13 @@ static void launch_bwd_mode(int mode, const AggParams& p, int grid, cudaStream_t
     if (mode == FGL_AGG_EDGE) launch_bwd_nacc<VEC, FGL_AGG_EDGE>(p, grid, st);
 }
 
-// dx[r, :] = dy_self[r, :] for r < n_dst, 0 for n_dst <= r < n_src (start value of the scatter of a layer with a
-// self term).  Scalar columns: the two matrices may have different alignment.
+// dx[r, :] = dy_self[r, :] for r < n_dst (the real count when n_dst_dev is given), 0 for n_dst <= r < n_src: the
+// start value of the scatter of a layer with a self term.  Scalar columns: the two matrices may have different
+// alignment.
 __global__ void __launch_bounds__(256)
 init_self_rows_kernel(float* __restrict__ dx, int64_t ldx, const float* __restrict__ dy_self, int64_t ld_self, int dim,
-                      int n_dst, int n_src) {
+                      int n_dst, int n_src, const int32_t* __restrict__ n_dst_dev) {
+    if (n_dst_dev) n_dst = min(max(__ldg(n_dst_dev), 0), n_dst);  // padded launch: rows at or beyond the real count are zero
     const int groups = (dim + 3) / 4;
     const int64_t total = (int64_t)n_src * groups;
     const bool vec = dim % 4 == 0 && ldx % 4 == 0 && ld_self % 4 == 0 && (((uintptr_t)dx | (uintptr_t)dy_self) & 15) == 0;
@@ -465,22 +524,26 @@ init_self_rows_kernel(float* __restrict__ dx, int64_t ldx, const float* __restri
 
 using namespace fgl;
 
+static int32_t* status_of(fgl_ws* ws) { return ws ? ws->status : nullptr; }
+
 extern "C" {
 
-int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
-                const int32_t* row_map, const float* x, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags,
-                float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream) {
-    return fgl_agg_fwd_sharded(mode, indptr, src, src_deg, dst_deg, row_map, x, nullptr, 0, ldx, dim, n_dst, flags, out, ldo,
-                               n_dst_dev, stream);
+int fgl_agg_fwd(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                const int32_t* dst_deg, const int32_t* row_map, int64_t n_map, const float* x, int64_t n_rows, int64_t ldx,
+                int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream) {
+    return fgl_agg_fwd_sharded(ws, mode, indptr, src, src_deg, dst_deg, row_map, n_map, x, nullptr, 0, n_rows, ldx, dim, n_dst,
+                               flags, out, ldo, n_dst_dev, stream);
 }
 
-int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
-                        const int32_t* dst_deg, const int32_t* row_map, const float* x, const float* const* shards,
-                        int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
-                        int64_t ldo, const int32_t* n_dst_dev, void* stream) {
-    if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || dim < 1 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
+int fgl_agg_fwd_sharded(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                        const int32_t* dst_deg, const int32_t* row_map, int64_t n_map, const float* x,
+                        const float* const* shards, int64_t rows_per_shard, int64_t n_rows, int64_t ldx, int32_t dim,
+                        int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream) {
+    if (mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || dim < 1 || ldx < dim || ldo < dim || n_rows < 0 ||
+        (row_map && n_map < 0))
+        return FGL_ERR_INVALID;
     if (n_dst == 0) return FGL_OK;
-    if (!indptr || (!x && !shards) || (shards && rows_per_shard < 1) || !out) return FGL_ERR_INVALID;
+    if (!indptr || (!x && !shards) || (shards && rows_per_shard < 1) || !out || n_rows < 1) return FGL_ERR_INVALID;
     if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
     AggParams p{};
     p.indptr = indptr;
@@ -497,20 +560,25 @@ int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src,
     p.n_dst_dev = n_dst_dev;
     p.shards = shards;
     p.rows_per_shard = rows_per_shard;
+    p.n_rows = n_rows;
+    p.n_map = n_map;
+    p.status = status_of(ws);
     p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
     return launch_fwd_any(mode, p, dim3(agg_grid_x(n_dst, 1), 1), pick_vec(dim, shards ? nullptr : x, ldx, out, ldo),
                           (cudaStream_t)stream);
 }
 
-int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride, const int32_t* src,
-                       int64_t src_stride, const int32_t* row_map, int64_t row_map_stride, const int64_t* out_row_off,
-                       int64_t total_rows, const float* x, const float* const* shards, int64_t rows_per_shard, int64_t ldx,
-                       int32_t dim, int32_t flags, float* out, int64_t ldo, float* self_out, int64_t ld_self, void* stream) {
+int fgl_agg_fwd_window(fgl_ws* ws, int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride,
+                       const int32_t* src, int64_t src_stride, const int32_t* row_map, int64_t row_map_stride,
+                       const int64_t* out_row_off, int64_t total_rows, const float* x, const float* const* shards,
+                       int64_t rows_per_shard, int64_t n_rows, int64_t ldx, int32_t dim, int32_t flags, float* out,
+                       int64_t ldo, float* self_out, int64_t ld_self, void* stream) {
     if ((mode != FGL_AGG_SUM && mode != FGL_AGG_MEAN) || n_batches < 0 || total_rows < 0 || total_rows > 0x7fffffffLL ||
-        dim < 1 || ldx < dim || ldo < dim || (self_out && ld_self < dim))
+        dim < 1 || ldx < dim || ldo < dim || (self_out && ld_self < dim) || n_rows < 0)
         return FGL_ERR_INVALID;
     if (n_batches == 0 || total_rows == 0) return FGL_OK;
-    if (!indptr || !src || !out_row_off || (!x && !shards) || (shards && rows_per_shard < 1) || !out) return FGL_ERR_INVALID;
+    if (!indptr || !src || !out_row_off || (!x && !shards) || (shards && rows_per_shard < 1) || !out || n_rows < 1)
+        return FGL_ERR_INVALID;
     AggParams p{};
     p.indptr = indptr;
     p.src = src;
@@ -518,6 +586,9 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
     p.x = x;
     p.shards = shards;
     p.rows_per_shard = rows_per_shard;
+    p.n_rows = n_rows;
+    p.n_map = row_map_stride;  // a batch's local ids index its own row of the map
+    p.status = status_of(ws);
     p.out = out;
     p.self_out = self_out;
     p.ldx = ldx;
@@ -534,11 +605,12 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
     return launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
 }
 
-int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* x, int64_t ldx,
-                     int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream) {
-    if (n_dst < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
+int fgl_agg_edge_fwd(fgl_ws* ws, const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads,
+                     const float* x, int32_t n_src, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
+                     int64_t ldo, void* stream) {
+    if (n_dst < 0 || n_src < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldo < dim) return FGL_ERR_INVALID;
     if (n_dst == 0) return FGL_OK;
-    if (!indptr || !x || !out || !edge_w) return FGL_ERR_INVALID;
+    if (!indptr || !x || !out || !edge_w || n_src < 1) return FGL_ERR_INVALID;
     AggParams p{};
     p.indptr = indptr;
     p.src = src;
@@ -548,6 +620,8 @@ int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edg
     p.ldo = ldo;
     p.dim = dim;
     p.n_dst = n_dst;
+    p.n_rows = n_src;
+    p.status = status_of(ws);
     p.edge_w = edge_w;
     p.n_heads = n_heads;
     p.passthrough = (flags & FGL_AGG_ZERO_DEG_PASSTHROUGH) ? 1 : 0;
@@ -556,8 +630,9 @@ int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edg
     return launch_fwd_any(FGL_AGG_EDGE, p, dim3(agg_grid_x(n_dst, 1), 1), vec, (cudaStream_t)stream);
 }
 
-int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* dy, int64_t ldy,
-                     int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, void* stream) {
+int fgl_agg_edge_bwd(fgl_ws* ws, const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads,
+                     const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
+                     void* stream) {
     if (n_dst < 0 || n_src < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldy < dim || ldx < dim) return FGL_ERR_INVALID;
     if (n_src == 0) return FGL_OK;
     if (!dx) return FGL_ERR_INVALID;
@@ -576,6 +651,7 @@ int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edg
     p.dim = dim;
     p.n_dst = n_dst;
     p.n_src = n_src;
+    p.status = status_of(ws);
     p.edge_w = edge_w;
     p.n_heads = n_heads;
     int vec = pick_vec(dim, dy, ldy, dx, ldx);
@@ -589,9 +665,11 @@ int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edg
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x, int64_t ldx, const float* dy,
-                       int64_t ldy, int32_t dim, int32_t n_dst, int64_t n_edges, float* dw, void* stream) {
-    if (n_dst < 0 || n_edges < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldy < dim) return FGL_ERR_INVALID;
+int fgl_agg_edge_wgrad(fgl_ws* ws, const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x, int32_t n_src,
+                       int64_t ldx, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int64_t n_edges, float* dw,
+                       void* stream) {
+    if (n_dst < 0 || n_src < 0 || n_edges < 0 || dim < 1 || n_heads < 1 || dim % n_heads != 0 || ldx < dim || ldy < dim)
+        return FGL_ERR_INVALID;
     if (n_edges == 0) return FGL_OK;
     if (!dw) return FGL_ERR_INVALID;
     cudaStream_t st = (cudaStream_t)stream;
@@ -607,6 +685,8 @@ int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_head
     p.ldo = ldy;
     p.dim = dim;
     p.n_dst = n_dst;
+    p.n_src = n_src;
+    p.status = status_of(ws);
     p.n_heads = n_heads;
     int vec = pick_vec(dim, x, ldx, dy, ldy);
     while (vec > 1 && (dim / n_heads) % vec != 0) vec /= 2;
@@ -619,15 +699,18 @@ int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_head
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows_per_shard, int64_t ld, int32_t dim,
-                    const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream) {
-    if ((!table && !shards) || (shards && rows_per_shard < 1) || dim < 1 || ld < dim || ldo < dim || n_ids < 0) return FGL_ERR_INVALID;
+int fgl_gather_rows(fgl_ws* ws, const float* table, const float* const* shards, int64_t rows_per_shard, int64_t n_rows,
+                    int64_t ld, int32_t dim, const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream) {
+    if ((!table && !shards) || (shards && rows_per_shard < 1) || dim < 1 || ld < dim || ldo < dim || n_ids < 0 || n_rows < 0)
+        return FGL_ERR_INVALID;
     if (n_ids == 0) return FGL_OK;
-    if (!ids || !out) return FGL_ERR_INVALID;
+    if (!ids || !out || n_rows < 1) return FGL_ERR_INVALID;
     AggParams p{};
     p.x = table;
     p.shards = shards;
     p.rows_per_shard = rows_per_shard;
+    p.n_rows = n_rows;
+    p.status = status_of(ws);
     p.out = out;
     p.ldx = ld;
     p.ldo = ldo;
@@ -644,7 +727,7 @@ int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-static int agg_bwd_impl(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+static int agg_bwd_impl(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                         const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
                         int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
                         void* stream) {
@@ -657,7 +740,7 @@ static int agg_bwd_impl(int32_t mode, const int32_t* indptr, const int32_t* src,
     if (dy_self && n_dst > 0) {
         const int64_t items = (int64_t)n_src * ((dim + 3) / 4);
         const int grid = (int)std::min<int64_t>((items + 255) / 256, 148 * 16);
-        init_self_rows_kernel<<<grid, 256, 0, st>>>(dx, ldx, dy_self, ld_self, dim, n_dst, n_src);
+        init_self_rows_kernel<<<grid, 256, 0, st>>>(dx, ldx, dy_self, ld_self, dim, n_dst, n_src, n_dst_dev);
     } else if (cudaMemset2DAsync(dx, sizeof(float) * (size_t)ldx, 0, sizeof(float) * (size_t)dim, (size_t)n_src, st) !=
                cudaSuccess) {
         return FGL_ERR_CUDA;
@@ -678,6 +761,7 @@ static int agg_bwd_impl(int32_t mode, const int32_t* indptr, const int32_t* src,
     p.n_dst = n_dst;
     p.n_src = n_src;
     p.n_dst_dev = n_dst_dev;
+    p.status = status_of(ws);
     const int grid = agg_grid_x(n_dst, 1);
     switch (pick_vec(dim, dy, ldy, dx, ldx)) {
         case 4: launch_bwd_mode<4>(mode, p, grid, st); break;
@@ -687,19 +771,19 @@ static int agg_bwd_impl(int32_t mode, const int32_t* indptr, const int32_t* src,
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg, const int32_t* dst_deg,
-                const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
-                const int32_t* n_dst_dev, void* stream) {
-    return agg_bwd_impl(mode, indptr, src, src_deg, dst_deg, dy, ldy, nullptr, 0, dim, n_dst, n_src, dx, ldx, n_dst_dev,
+int fgl_agg_bwd(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                const int32_t* dst_deg, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx,
+                int64_t ldx, const int32_t* n_dst_dev, void* stream) {
+    return agg_bwd_impl(ws, mode, indptr, src, src_deg, dst_deg, dy, ldy, nullptr, 0, dim, n_dst, n_src, dx, ldx, n_dst_dev,
                         stream);
 }
 
-int fgl_agg_bwd_self(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+int fgl_agg_bwd_self(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                      const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
                      int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
                      void* stream) {
     if (!dy_self && n_dst > 0) return FGL_ERR_INVALID;
-    return agg_bwd_impl(mode, indptr, src, src_deg, dst_deg, dy, ldy, dy_self, ld_self, dim, n_dst, n_src, dx, ldx,
+    return agg_bwd_impl(ws, mode, indptr, src, src_deg, dst_deg, dy, ldy, dy_self, ld_self, dim, n_dst, n_src, dx, ldx,
                         n_dst_dev, stream);
 }
 

@@ -150,6 +150,7 @@ struct Team {
     unsigned epoch;
     unsigned long long* bar;
     int32_t* status;
+    long long spin_limit = kSpinLimit;
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
@@ -173,7 +174,7 @@ __device__ __forceinline__ bool team_barrier(Team& t, int* s_flag) {
                 aborted = 1;
                 break;
             }
-            if (++spins > kSpinLimit) {
+            if (++spins > t.spin_limit) {
                 set_status(t.status, FGL_ERR_TIMEOUT);
                 atomicExch(t.status + 1, 1);
                 aborted = 1;

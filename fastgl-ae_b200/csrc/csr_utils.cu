@@ -113,6 +113,21 @@ __global__ void __launch_bounds__(kStageThreads) stage_segments_kernel(const __g
     }
 }
 
+// Self-test of the bounded wait: every CTA arrives at a team barrier that expects one arrival more than the grid
+// has, so the wait runs out after spin_limit polls, records FGL_ERR_TIMEOUT, raises the abort flag and returns.
+__global__ void __launch_bounds__(32) barrier_timeout_kernel(unsigned long long* bar, int32_t* status, long long spin_limit,
+                                                             int32_t* passed) {
+    __shared__ int s_flag;
+    Team t;
+    t.rank = blockIdx.x;
+    t.size = gridDim.x + 1;
+    t.epoch = 0;
+    t.bar = bar;
+    t.status = status;
+    t.spin_limit = spin_limit;
+    if (team_barrier(t, &s_flag) && threadIdx.x == 0) atomicAdd(passed, 1);  // cannot happen: nobody sends the last arrival
+}
+
 }  // namespace fgl
 
 using namespace fgl;
@@ -154,6 +169,20 @@ int fgl_stage_segments(const fgl_segment* segs, int32_t n_segs, int32_t* words_d
     if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
     stage_segments_kernel<<<(unsigned)blocks, kStageThreads, 0, (cudaStream_t)stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_selftest_barrier_timeout(fgl_ws* ws, int32_t n_ctas, int64_t spin_limit, void* stream) {
+    if (!ws || n_ctas < 1 || n_ctas > 64 || spin_limit < 1 || spin_limit > kSpinLimit) return FGL_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(ws->mu);
+    DeviceGuard guard(ws->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = ws_ensure(ws, 0, 256);
+    if (rc != FGL_OK) return rc;
+    FGL_CUDA_OK(ws, cudaMemsetAsync(ws->scratch, 0, 256, st));
+    barrier_timeout_kernel<<<n_ctas, 32, 0, st>>>((unsigned long long*)ws->scratch, ws->status, (long long)spin_limit,
+                                                  (int32_t*)(ws->scratch + 128));
+    FGL_CUDA_OK(ws, cudaGetLastError());
+    return FGL_OK;
 }
 
 int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream) {

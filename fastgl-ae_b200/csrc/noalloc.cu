@@ -14,7 +14,9 @@
 // call should come before any stream capture.  All calls share the array, which keeps the previous call's
 // contents: each call clears the words that must start at zero, and two calls whose kernels overlap on the
 // GPU (different streams) would race.  If the scan's bounded barrier ever gives up, FGL_ERR_TIMEOUT is left
-// in the array's status word and the output is incomplete.
+// in the array's status word and the output is incomplete.  That word is not cleared by later scans: it keeps
+// the first failure until fgl_exclusive_sum_noalloc_status copies it to the caller's host memory and clears it
+// (again without allocating anything).
 #include <algorithm>
 
 #include "common.cuh"
@@ -129,11 +131,30 @@ int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* 
     int32_t* scratch = g_na_ptr[dev];
     const int64_t tiles = (n + kNaThreads * kNaItems - 1) / (kNaThreads * kNaItems);
     const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(g_na_max_grid[dev], tiles));
-    // the arrival counter and the status words must start at zero; the partials are rewritten by every CTA
-    if (cudaMemsetAsync(scratch, 0, 32 * sizeof(int32_t), st) != cudaSuccess) return FGL_ERR_CUDA;
+    // the arrival counter (words 0-1) and the abort flag (word 3) must start at zero; the status word (2) keeps the
+    // first failure until fgl_exclusive_sum_noalloc_status reads it; the partials are rewritten by every CTA
+    if (cudaMemsetAsync(scratch, 0, 2 * sizeof(int32_t), st) != cudaSuccess ||
+        cudaMemsetAsync(scratch + 3, 0, sizeof(int32_t), st) != cudaSuccess)
+        return FGL_ERR_CUDA;
     void* args[] = {(void*)&in, (void*)&n, (void*)&out, (void*)&scratch};
     if (cudaLaunchCooperativeKernel((const void*)exclusive_sum_noalloc_kernel, dim3(grid), dim3(kNaThreads), args, 0, st) !=
         cudaSuccess) {
+        cudaGetLastError();
+        return FGL_ERR_CUDA;
+    }
+    return FGL_OK;
+}
+
+int fgl_exclusive_sum_noalloc_status(int32_t* host_dst, void* stream) {
+    if (!host_dst) return FGL_ERR_INVALID;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FGL_ERR_CUDA;
+    int rc = noalloc_setup(dev);
+    if (rc != FGL_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t* status = g_na_ptr[dev] + 2;
+    if (cudaMemcpyAsync(host_dst, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaMemsetAsync(status, 0, sizeof(int32_t), st) != cudaSuccess) {
         cudaGetLastError();
         return FGL_ERR_CUDA;
     }

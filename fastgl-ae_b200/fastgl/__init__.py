@@ -33,8 +33,12 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
+
+# status codes of include/fastgl_b200.h that callers branch on
+ERR_CAPACITY, ERR_PROBE, ERR_BOUNDS, ERR_TIMEOUT = 4, 5, 6, 7
 
 _state_lock = threading.Lock()
 _workspaces: dict[int, ctypes.c_void_p] = {}
@@ -262,6 +266,21 @@ def exclusive_sum_noalloc(in_degs, out):
     return out
 
 
+def exclusive_sum_noalloc_status(device=None) -> int:
+    """Status of the ``exclusive_sum_noalloc`` calls on ``device`` since the last call of this function: 0, or the
+    code of the first failure (a scan whose bounded barrier gave up leaves its output incomplete).  Synchronises the
+    current stream; reads and clears the status word without allocating device memory."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if not hasattr(exclusive_sum_noalloc_status, "_pinned"):
+        exclusive_sum_noalloc_status._pinned = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host = exclusive_sum_noalloc_status._pinned
+    with _on_device(dev):
+        rc = lib().fgl_exclusive_sum_noalloc_status(ctypes.c_void_p(host.data_ptr()), _stream(dev))
+    _raise(rc, "exclusive_sum_noalloc_status")
+    torch.cuda.current_stream(dev).synchronize()
+    return int(host[0])
+
+
 # ------------------------------------------------------------------------------------------------
 # feature tables
 # ------------------------------------------------------------------------------------------------
@@ -291,24 +310,27 @@ class ShardedTable:
 
 
 def _table_args(input_feat):
-    """(x pointer, shards pointer, rows_per_shard, ld, dim, device) of a dense or sharded table."""
+    """(x pointer, shards pointer, rows_per_shard, n_rows, ld, dim, device) of a dense or sharded table."""
     if isinstance(input_feat, ShardedTable):
-        return ctypes.c_void_p(0), _ptr(input_feat.ptrs), input_feat.rows_per_shard, input_feat.ld, input_feat.dim, input_feat.device
+        return (ctypes.c_void_p(0), _ptr(input_feat.ptrs), input_feat.rows_per_shard, input_feat.n_rows, input_feat.ld,
+                input_feat.dim, input_feat.device)
     _check_rows_f32(input_feat, "input_feat")
-    return _ptr(input_feat), ctypes.c_void_p(0), 0, input_feat.stride(0), input_feat.size(1), input_feat.device
+    return (_ptr(input_feat), ctypes.c_void_p(0), 0, input_feat.size(0), input_feat.stride(0), input_feat.size(1),
+            input_feat.device)
 
 
 def gather_rows(table, ids, out=None):
     """``out[i] = table[ids[i]]`` for a dense CUDA matrix or a ``ShardedTable``; ``ids`` int32."""
     _check_i32(ids, "ids")
-    x, shards, rps, ld, dim, dev = _table_args(table)
+    x, shards, rps, n_rows, ld, dim, dev = _table_args(table)
     if out is None:
         out = torch.empty((ids.numel(), dim), dtype=torch.float32, device=dev)
     else:
         _check_rows_f32(out, "out")
     with _on_device(dev):
-        rc = lib().fgl_gather_rows(x, shards, ctypes.c_int64(rps), ctypes.c_int64(ld), ctypes.c_int32(dim), _ptr(ids),
-                                   ctypes.c_int64(ids.numel()), _ptr(out), ctypes.c_int64(out.stride(0)), _stream(dev))
+        rc = lib().fgl_gather_rows(_ws(dev), x, shards, ctypes.c_int64(rps), ctypes.c_int64(n_rows), ctypes.c_int64(ld),
+                                   ctypes.c_int32(dim), _ptr(ids), ctypes.c_int64(ids.numel()), _ptr(out),
+                                   ctypes.c_int64(out.stride(0)), _stream(dev))
     _raise(rc, "gather_rows")
     return out
 
@@ -334,7 +356,7 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     n_dst = int(dst_nodes)
     if edge_ptr.numel() < n_dst + 1:
         raise RuntimeError("edge_ptr is shorter than dst_nodes + 1")
-    x, shards, rps, ld, dim, dev = _table_args(input_feat)
+    x, shards, rps, n_rows, ld, dim, dev = _table_args(input_feat)
     if mode == AGG_SYMNORM:
         n_src = row_map.numel() if row_map is not None else (input_feat.size(0) if torch.is_tensor(input_feat) else None)
         if (src_norm_degs is None or dst_norm_degs is None or dst_norm_degs.numel() < n_dst
@@ -345,8 +367,10 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     else:
         _check_rows_f32(out, "out")
     with _on_device(dev):
-        rc = lib().fgl_agg_fwd_sharded(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
-                                       _ptr(dst_norm_degs), _ptr(row_map), x, shards, ctypes.c_int64(rps), ctypes.c_int64(ld),
+        rc = lib().fgl_agg_fwd_sharded(_ws(dev), ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+                                       _ptr(dst_norm_degs), _ptr(row_map),
+                                       ctypes.c_int64(row_map.numel() if row_map is not None else 0), x, shards,
+                                       ctypes.c_int64(rps), ctypes.c_int64(n_rows), ctypes.c_int64(ld),
                                        ctypes.c_int32(dim), ctypes.c_int32(n_dst),
                                        ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH if zero_deg_passthrough else 0), _ptr(out),
                                        ctypes.c_int64(out.stride(0)), _ptr(n_dst_dev), _stream(dev))
@@ -363,7 +387,7 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     list with the total appended).  With ``use_row_map`` the rows of ``input_feat`` are addressed through the
     window's global node ids (aggregation straight from the feature table); ``self_out`` also receives each
     destination's own input row."""
-    x, shards, rps, ld, dim, dev = _table_args(input_feat)
+    x, shards, rps, n_rows, ld, dim, dev = _table_args(input_feat)
     _check_rows_f32(out, "out")
     if self_out is not None:
         _check_rows_f32(self_out, "self_out")
@@ -380,9 +404,9 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
         return row_off
     with _on_device(dev):
         rc = lib().fgl_agg_fwd_window(
-            ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
+            _ws(dev), ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
             ctypes.c_int64(src.stride(0)), _ptr(fb.nodes if use_row_map else None), ctypes.c_int64(fb.nodes.stride(0)),
-            _ptr(off_dev), ctypes.c_int64(row_off[-1]), x, shards, ctypes.c_int64(rps),
+            _ptr(off_dev), ctypes.c_int64(row_off[-1]), x, shards, ctypes.c_int64(rps), ctypes.c_int64(n_rows),
             ctypes.c_int64(ld), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
             ctypes.c_int64(out.stride(0)), _ptr(self_out), ctypes.c_int64(self_out.stride(0) if self_out is not None else dim),
             _stream(dev))
@@ -418,7 +442,7 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
         d_x = out
     with _on_device(dev):
         if d_self is None:
-            rc = lib().fgl_agg_bwd(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+            rc = lib().fgl_agg_bwd(_ws(dev), ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
                                    _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), ctypes.c_int32(dim),
                                    ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
                                    ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
@@ -426,7 +450,7 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
             _check_rows_f32(d_self, "d_self")
             if d_self.size(0) != n_dst or d_self.size(1) != dim:
                 raise RuntimeError("d_self must be float32[n_dst, dim]")
-            rc = lib().fgl_agg_bwd_self(ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
+            rc = lib().fgl_agg_bwd_self(_ws(dev), ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
                                         _ptr(dst_norm_degs), _ptr(d_out), ctypes.c_int64(d_out.stride(0)), _ptr(d_self),
                                         ctypes.c_int64(d_self.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
                                         ctypes.c_int32(int(src_nodes)), _ptr(d_x), ctypes.c_int64(d_x.stride(0)),
@@ -596,8 +620,9 @@ def forward_gat(edge_ptr, edge_data, src_edges, input_feat, neighbor_num, dst_no
     dev = input_feat.device
     out = torch.empty((n_dst, dim), dtype=torch.float32, device=dev)
     with _on_device(dev):
-        rc = lib().fgl_agg_edge_fwd(_ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(input_feat),
-                                    ctypes.c_int64(input_feat.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
+        rc = lib().fgl_agg_edge_fwd(_ws(dev), _ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(input_feat),
+                                    ctypes.c_int32(input_feat.size(0)), ctypes.c_int64(input_feat.stride(0)),
+                                    ctypes.c_int32(dim), ctypes.c_int32(n_dst),
                                     ctypes.c_int32(FLAG_ZERO_DEG_PASSTHROUGH), _ptr(out), ctypes.c_int64(dim), _stream(dev))
     _raise(rc, "forward_gat")
     return [out]
@@ -618,7 +643,7 @@ def backward_gat(edge_ptr, edge_data, src_edges, d_input, src_nodes, num_heads):
     dev = d_input.device
     d_x = torch.empty((int(src_nodes), dim), dtype=torch.float32, device=dev)
     with _on_device(dev):
-        rc = lib().fgl_agg_edge_bwd(_ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(d_input),
+        rc = lib().fgl_agg_edge_bwd(_ws(dev), _ptr(edge_ptr), _ptr(src_edges), _ptr(edge_data), ctypes.c_int32(H), _ptr(d_input),
                                     ctypes.c_int64(d_input.stride(0)), ctypes.c_int32(dim), ctypes.c_int32(n_dst),
                                     ctypes.c_int32(int(src_nodes)), _ptr(d_x), ctypes.c_int64(dim), _stream(dev))
     _raise(rc, "backward_gat")
@@ -636,8 +661,8 @@ def edge_weight_grad(edge_ptr, src_edges, input_feat, d_out, num_heads):
     dev = d_out.device
     d_w = torch.empty((E, H), dtype=torch.float32, device=dev)
     with _on_device(dev):
-        rc = lib().fgl_agg_edge_wgrad(_ptr(edge_ptr), _ptr(src_edges), ctypes.c_int32(H), _ptr(input_feat),
-                                      ctypes.c_int64(input_feat.stride(0)), _ptr(d_out), ctypes.c_int64(d_out.stride(0)),
+        rc = lib().fgl_agg_edge_wgrad(_ws(dev), _ptr(edge_ptr), _ptr(src_edges), ctypes.c_int32(H), _ptr(input_feat),
+                                      ctypes.c_int32(input_feat.size(0)), ctypes.c_int64(input_feat.stride(0)), _ptr(d_out), ctypes.c_int64(d_out.stride(0)),
                                       ctypes.c_int32(dim), ctypes.c_int32(d_out.size(0)), ctypes.c_int64(E), _ptr(d_w),
                                       _stream(dev))
     _raise(rc, "edge_weight_grad")

@@ -438,15 +438,19 @@ class Trainer:
             nxt = None
             fb.counts_host()
             if fb.device_status != 0:
-                # The capped hashtable was too small for this window (or another device-side check fired): clear the
-                # status, drop the cap and sample the same window again -- same seeds, same Philox counters.
                 code = fb.device_status
+                if code not in (fastgl.ERR_PROBE, fastgl.ERR_CAPACITY) or self.table_slots == 0:
+                    # Not a table that was capped too small: a node id or a label out of range, a bounded wait that
+                    # gave up ... -- recorded by this window's sampler or by the training steps enqueued before it.
+                    # Clear the status and stop: the rows concerned contributed nothing.
+                    fastgl.check_status(self.dev)
+                    raise RuntimeError(f"device status: {fastgl.status_str(code)}")
+                # The capped hashtable was too small for this window: clear the status, drop the cap and sample the
+                # same window again -- same seeds, same Philox counters.
                 try:
                     fastgl.check_status(self.dev)
                 except RuntimeError:
                     pass
-                if self.table_slots == 0:
-                    raise RuntimeError(f"fused sampling failed: {fastgl.status_str(code)}")
                 self.table_slots, self._auto_table = 0, False
                 self.table_overflows += 1
                 self.sampler.batch_counter -= nb
@@ -473,14 +477,14 @@ class Trainer:
                     nxt = sample_next(done + nb)
                 loss = self.train_batch(fb, b, layer0=layer0)
                 if read_loss_each_step:
-                    slot = len(losses) & 1 if pending is None else 1 - pending[1]
-                    self._loss_host[slot: slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)
+                    loss_slot = len(losses) & 1 if pending is None else 1 - pending[1]
+                    self._loss_host[loss_slot: loss_slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record()
                     if pending is not None:
                         pending[0].synchronize()
                         losses.append(float(self._loss_host[pending[1]]))
-                    pending = (ev, slot)
+                    pending = (ev, loss_slot)
             done += nb
         if pending is not None:
             pending[0].synchronize()

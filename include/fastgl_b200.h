@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define FGL_ABI_VERSION 2
+#define FGL_ABI_VERSION 3
 
 /* status codes */
 #define FGL_OK 0
@@ -64,8 +64,10 @@ const char* fgl_status_str(int status);
 /* Workspace.  Replaces the per-call cudaMalloc / cudaFree of scratch in the reference
  * (sample.cu:118,151,157,161-162,197; id_map.cu:45-58; utilis.cu:33,38).  Buffers grow on demand
  * (never inside a stream capture: size the workspace with fgl_ws_reserve first) and are freed by
- * fgl_ws_destroy.  A workspace belongs to one device and may be used from any host thread, one call
- * at a time (calls lock it). */
+ * fgl_ws_destroy.  A workspace belongs to one device and may be used from any host thread: the lock a call
+ * takes only covers its enqueueing.  The kernels of one workspace share its table, scratch, barrier and
+ * status words, so calls on one workspace must be stream-ordered (one stream, or streams the caller orders
+ * with events); calls that may overlap on the GPU need a workspace each. */
 int fgl_ws_create(int device, fgl_ws** ws);
 int fgl_ws_destroy(fgl_ws* ws);
 int fgl_ws_reserve(fgl_ws* ws, int64_t table_slots, int64_t scratch_bytes);
@@ -77,6 +79,13 @@ int fgl_ws_check(fgl_ws* ws, void* stream);
  * synchronising and without clearing it: a caller that already waits for another read-back of the same stream
  * learns of device-side errors at that point for free.  After a non-zero value, fgl_ws_check clears the word. */
 int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream);
+
+/* Self-test of the library's bounded device-side wait (no counterpart in the reference, whose kernels never
+ * wait on one another): n_ctas (<= 64) CTAs arrive at a barrier that expects n_ctas + 1 arrivals, so every wait
+ * gives up after spin_limit polls, records FGL_ERR_TIMEOUT and raises the workspace's abort flag.  Nothing
+ * faults and nothing hangs; the next fgl_ws_check returns FGL_ERR_TIMEOUT and clears the flag, after which the
+ * workspace works as before. */
+int fgl_selftest_barrier_timeout(fgl_ws* ws, int32_t n_ctas, int64_t spin_limit, void* stream);
 
 /* Neighbour sampling; replaces sample_node_cuda (sample.cu:102-203; binding aggregate_acc.cpp:491-512).
  * indptr has n_nodes + 1 entries of int32 (indptr_is_64 = 0, as the reference) or int64.  For seed i
@@ -171,6 +180,11 @@ int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, vo
  * device. */
 #define FGL_NOALLOC_MAX_N (1LL << 27)
 int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* stream);
+/* How such a caller learns that a scan's bounded barrier gave up (its output is then incomplete): enqueues, on the
+ * stream, a copy of the array's status word to host_dst (one int32 of host memory; pinned if the copy is to stay
+ * asynchronous) followed by clearing the word -- FGL_OK, or FGL_ERR_TIMEOUT if any scan since the last such call
+ * timed out.  Allocates nothing either; read *host_dst after synchronising the stream. */
+int fgl_exclusive_sum_noalloc_status(int32_t* host_dst, void* stream);
 
 /* Aggregation forward; replaces the gather kernels K8 / K10 of the reference
  * (computation_aware_forward_gcn_cuda_kernel aggregate_acc_kernel.cu:271-331 and
@@ -178,22 +192,28 @@ int fgl_exclusive_sum_noalloc(const int32_t* in, int64_t n, int32_t* out, void* 
  * [indptr[d], indptr[d+1]) of w * x[row(src[e]), 0..dim), with w by mode and row(i) = row_map[i] if
  * row_map is not NULL (aggregation straight from a feature table by global id) else i.  src_deg /
  * dst_deg are only read in FGL_AGG_SYMNORM.
+ * Bounds: x has n_rows rows and row_map (if any) n_map entries.  The reference dereferences whatever id the
+ * block holds (:316-324); here an id outside [0, n_map) or a row outside [0, n_rows) is never dereferenced: the
+ * edge contributes nothing (a gathered row or a row's own copy becomes zeros) and FGL_ERR_BOUNDS is recorded in
+ * the status word of ws (fgl_ws_check).  ws may be NULL: bad ids are then skipped silently.  This holds for every
+ * aggregation entry point below.
  * n_dst_dev (may be NULL) points at the real row count in device memory; n_dst is then the padded count the
  * launch is sized for (rows beyond the real count are zero-filled), which lets a captured CUDA graph be
  * replayed on blocks of different sizes. */
-int fgl_agg_fwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
-                const int32_t* dst_deg, const int32_t* row_map, const float* x, int64_t ldx, int32_t dim,
-                int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream);
+int fgl_agg_fwd(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                const int32_t* dst_deg, const int32_t* row_map, int64_t n_map, const float* x, int64_t n_rows,
+                int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo,
+                const int32_t* n_dst_dev, void* stream);
 
 /* fgl_agg_fwd over a feature table that is row-sharded across GPUs: shards (device array of n pointers, each a
  * table of the same leading dimension, mapped into this GPU's address space -- its own HBM or a peer's over
  * NVLink) replaces x (x may then be NULL); global row r is shards[r / rows_per_shard][r % rows_per_shard].
  * Rows are fetched with plain 128-bit peer loads, each warp its own rows: no collective, no TMA multicast.
  * No counterpart in the reference, which keeps features on the host (train_fastgl.py:233). */
-int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
-                        const int32_t* dst_deg, const int32_t* row_map, const float* x, const float* const* shards,
-                        int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
-                        int64_t ldo, const int32_t* n_dst_dev, void* stream);
+int fgl_agg_fwd_sharded(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+                        const int32_t* dst_deg, const int32_t* row_map, int64_t n_map, const float* x,
+                        const float* const* shards, int64_t rows_per_shard, int64_t n_rows, int64_t ldx, int32_t dim,
+                        int32_t n_dst, int32_t flags, float* out, int64_t ldo, const int32_t* n_dst_dev, void* stream);
 
 /* Edge-weighted multi-head aggregation; replaces computation_aware_forward_gat_cuda /
  * computation_aware_backward_gat_cuda (aggregate_acc_kernel.cu:789-979; bindings aggregate_acc.cpp
@@ -202,23 +222,25 @@ int fgl_agg_fwd_sharded(int32_t mode, const int32_t* indptr, const int32_t* src,
  * Forward: out[d, f] = sum over row d's edges e of edge_w[e, head(f)] * x[src[e], f]; a row without in-edges
  * copies x[d] when FGL_AGG_ZERO_DEG_PASSTHROUGH is set (:870-872).  Backward: dx is zero-filled, then
  * dx[src[e], f] += edge_w[e, head(f)] * dy[d, f]; like the reference, no gradient flows to edge_w. */
-int fgl_agg_edge_fwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* x,
-                     int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out, int64_t ldo, void* stream);
-int fgl_agg_edge_bwd(const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads, const float* dy,
-                     int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, void* stream);
+int fgl_agg_edge_fwd(fgl_ws* ws, const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads,
+                     const float* x, int32_t n_src, int64_t ldx, int32_t dim, int32_t n_dst, int32_t flags, float* out,
+                     int64_t ldo, void* stream);
+int fgl_agg_edge_bwd(fgl_ws* ws, const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads,
+                     const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
+                     void* stream);
 
 /* Gradient of the attention coefficients, which the reference does not compute (MA_Function_GAT.backward returns
  * None for edge_data, GraphConv.py:227): dw[e, h] = sum over head h's columns f of dy[d, f] * x[src[e], f] for
  * every edge e of row d.  dw is float32 [n_edges][n_heads] and is zero-filled first. */
-int fgl_agg_edge_wgrad(const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x, int64_t ldx,
-                       const float* dy, int64_t ldy, int32_t dim, int32_t n_dst, int64_t n_edges, float* dw,
-                       void* stream);
+int fgl_agg_edge_wgrad(fgl_ws* ws, const int32_t* indptr, const int32_t* src, int32_t n_heads, const float* x,
+                       int32_t n_src, int64_t ldx, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst,
+                       int64_t n_edges, float* dw, void* stream);
 
 /* Row gather out[i, :] = table[ids[i], :] from a single table (shards = NULL) or a row-sharded one (table may
- * be NULL), as above.  Replaces the CPU index_select + host-to-device copy of load_subtensors
+ * be NULL) of n_rows rows, as above; an id outside [0, n_rows) gives a row of zeros and FGL_ERR_BOUNDS.  Replaces the CPU index_select + host-to-device copy of load_subtensors
  * (train_fastgl.py:161-184) and the MatchServer cache look-ups (MatchReorderServer.py:79-110). */
-int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows_per_shard, int64_t ld, int32_t dim,
-                    const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream);
+int fgl_gather_rows(fgl_ws* ws, const float* table, const float* const* shards, int64_t rows_per_shard, int64_t n_rows,
+                    int64_t ld, int32_t dim, const int32_t* ids, int64_t n_ids, float* out, int64_t ldo, void* stream);
 
 /* Forward aggregation (FGL_AGG_SUM or FGL_AGG_MEAN) of one layer for a whole window of mini-batches in one
  * launch, laid out as fgl_sample_map_fused leaves them: batch b's block is indptr + b * indptr_stride,
@@ -231,11 +253,11 @@ int fgl_gather_rows(const float* table, const float* const* shards, int64_t rows
  * not depend on the weights; the reference runs K10 once per mini-batch (GraphConv.py:109) after a CPU
  * gather of the input rows (train_fastgl.py:161-184).  x / shards / rows_per_shard as in
  * fgl_agg_fwd_sharded. */
-int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride,
+int fgl_agg_fwd_window(fgl_ws* ws, int32_t mode, int32_t n_batches, const int32_t* indptr, int64_t indptr_stride,
                        const int32_t* src, int64_t src_stride, const int32_t* row_map, int64_t row_map_stride,
                        const int64_t* out_row_off, int64_t total_rows, const float* x, const float* const* shards,
-                       int64_t rows_per_shard, int64_t ldx, int32_t dim, int32_t flags, float* out, int64_t ldo,
-                       float* self_out, int64_t ld_self, void* stream);
+                       int64_t rows_per_shard, int64_t n_rows, int64_t ldx, int32_t dim, int32_t flags, float* out,
+                       int64_t ldo, float* self_out, int64_t ld_self, void* stream);
 
 /* Aggregation backward; replaces the scatter kernels K9 / K11
  * (computation_aware_backward_gcn_cuda_kernel aggregate_acc_kernel.cu:468-517 and
@@ -243,16 +265,17 @@ int fgl_agg_fwd_window(int32_t mode, int32_t n_batches, const int32_t* indptr, i
  * dx[src[e], :] += w * dy[d, :] for every edge e of row d.  Rows without in-edges contribute nothing
  * (as the reference, :498-500, :580-582).  n_dst_dev as in fgl_agg_fwd (n_src is never read from the
  * device: dx is zero-filled over all n_src rows). */
-int fgl_agg_bwd(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+int fgl_agg_bwd(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                 const int32_t* dst_deg, const float* dy, int64_t ldy, int32_t dim, int32_t n_dst,
                 int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev, void* stream);
 
 /* fgl_agg_bwd for a layer that also feeds each destination's own row forward (GraphSAGE: [h_dst | aggregate]):
  * dx starts as dy_self in its first n_dst rows (the destinations are the first n_dst sources) and zero below,
  * then receives the scattered dy as above -- one pass instead of a zero-fill, a scatter, a padded copy and an
- * add.  dy_self is float32 [n_dst][dim] with leading dimension ld_self; n_dst <= n_src.  No counterpart in the
+ * add.  dy_self is float32 [n_dst][dim] with leading dimension ld_self; n_dst <= n_src.  With n_dst_dev the
+ * rows of dy_self at or beyond the real count are ignored (dx is zero there), whatever they hold.  No counterpart in the
  * reference, whose models have no self term (GraphConv.py:86-99). */
-int fgl_agg_bwd_self(int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
+int fgl_agg_bwd_self(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* src, const int32_t* src_deg,
                      const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
                      int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
                      void* stream);

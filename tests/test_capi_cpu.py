@@ -50,8 +50,10 @@ def test_invalid_arguments_return_status_without_touching_a_device():
     lib = _capi.lib()
     assert lib.fgl_sample(None, None, 0, None, ctypes.c_int64(0), None, 0, 0, 0, ctypes.c_uint64(0), ctypes.c_uint64(0),
                           None, None, None, None, None) == 1
-    assert lib.fgl_agg_fwd(9, None, None, None, None, None, None, ctypes.c_int64(4), 4, 1, 0, None, ctypes.c_int64(4),
-                           None, None) == 1
+    assert lib.fgl_agg_fwd(None, 9, None, None, None, None, None, ctypes.c_int64(0), None, ctypes.c_int64(1),
+                           ctypes.c_int64(4), 4, 1, 0, None, ctypes.c_int64(4), None, None) == 1
+    assert lib.fgl_exclusive_sum_noalloc_status(None, None) == 1
+    assert lib.fgl_selftest_barrier_timeout(None, 1, ctypes.c_int64(10), None) == 1
     assert lib.fgl_ws_destroy(None) == 0
 
 

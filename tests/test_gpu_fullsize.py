@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def products_like():
-    from fastgl_b200.checks import EdgeKeys
+    from checks import EdgeKeys
     from fastgl_b200.graphgen import rmat_graph
     dev = torch.device("cuda", 0)
     indptr, indices = rmat_graph(2_450_000, 50.6, seed=12345, device=dev)
@@ -24,7 +24,7 @@ def products_like():
 @pytest.mark.parametrize("replace", [False, True])
 def test_products_sized_window_passes_every_gate(products_like, replace):
     import fastgl
-    from fastgl_b200.checks import check_window, check_window_aggregation
+    from checks import check_window, check_window_aggregation
     indptr, indices, keys, feat = products_like
     dev = feat.device
     gen = torch.Generator(device=dev)
@@ -65,7 +65,7 @@ def test_sampling_is_reproducible_and_counter_dependent_at_full_size(products_li
 def test_dense_graph_wide_fanout_window_passes_every_gate():
     """The shapes of the 2-layer GCN workload: average degree ~490, fanouts [25, 10]."""
     import fastgl
-    from fastgl_b200.checks import EdgeKeys, check_window
+    from checks import EdgeKeys, check_window
     from fastgl_b200.graphgen import rmat_graph
     dev = torch.device("cuda", 0)
     indptr, indices = rmat_graph(233_000, 490.0, seed=12345, device=dev)

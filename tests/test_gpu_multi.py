@@ -1,6 +1,11 @@
 """Two-GPU tests.  (1) The row-sharded feature table: every rank keeps half of the rows, opens the other half
 through CUDA IPC, and gathers / aggregates rows that live on both GPUs with peer loads.  (2) Data-parallel
-training over NCCL with the step replayed from CUDA graphs.  Skipped on boxes with one GPU.  Ranks are child processes; a rank only leaves between steps (after the final barrier)."""
+training over NCCL with the step replayed from CUDA graphs.  Skipped on boxes with one GPU.  Ranks are child
+processes.  A rank leaves only through ``_leave_together``: whether its checks passed or raised, it first drains
+its own GPU work, waits on a host-side (gloo) barrier until every rank has done the same, drops its mappings of
+the peers' memory, waits again, and only then tears down -- so no rank unmaps memory a peer's kernel may still
+read, on the failure path as on the success path."""
+import datetime
 import os
 import socket
 
@@ -19,6 +24,23 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _leave_together(exc, host_group, release=None):
+    """Common exit of a rank (see the module docstring); re-raises ``exc`` at the end."""
+    try:
+        torch.cuda.synchronize()
+    finally:
+        try:
+            dist.barrier(group=host_group)          # every rank's kernels have finished
+            if release is not None:
+                release()                            # drop this rank's mappings of the peers' memory
+            torch.cuda.ipc_collect()
+            dist.barrier(group=host_group)          # nobody maps anybody's memory any more
+        finally:
+            dist.destroy_process_group()
+    if exc is not None:
+        raise exc
+
+
 def _worker(rank, world, port):
     import fastgl
     from fastgl_b200.sharding import rows_per_shard, share_feature_shards
@@ -29,7 +51,8 @@ def _worker(rank, world, port):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=180))
+    held, err = {}, None
     try:
         n, dim = 50_001, 256
         rng = np.random.default_rng(77)                       # the same table on every rank (host side, for checking)
@@ -38,7 +61,7 @@ def _worker(rank, world, port):
         mine = torch.zeros((rps, dim), dtype=torch.float32, device=dev)
         part = table[rank * rps:(rank + 1) * rps]
         mine[: part.shape[0]] = torch.from_numpy(part).to(dev)
-        st = share_feature_shards(mine, n)
+        st = held["table"] = share_feature_shards(mine, n)
         ids = np.random.default_rng(100 + rank).integers(0, n, size=20_000).astype(np.int32)
         got = fastgl.gather_rows(st, torch.from_numpy(ids).to(dev))
         assert np.array_equal(got.cpu().numpy(), table[ids])
@@ -51,10 +74,15 @@ def _worker(rank, world, port):
         ref = oc.aggregate_fwd(oc.MODE_MEAN, indptr, src, table, n_dst, zero_deg_passthrough=False)
         err = float(np.abs(out.cpu().numpy() - ref).max() / np.abs(ref).max())
         assert err <= 1e-5, err
-        torch.cuda.synchronize()
-        dist.barrier()                                        # nobody unmaps a shard while a peer still reads it
-    finally:
-        dist.destroy_process_group()
+        # an id beyond the table is reported, not dereferenced (its row comes back as zeros)
+        bad = fastgl.gather_rows(st, torch.tensor([0, n, -1, n - 1], dtype=torch.int32, device=dev))
+        with pytest.raises(RuntimeError, match="out of range"):
+            fastgl.check_status(dev)
+        assert np.array_equal(bad.cpu().numpy()[[0, 3]], table[[0, n - 1]]) and not bad[1:3].any()
+    except BaseException as e:                                # noqa: BLE001 -- re-raised by _leave_together
+        err = e
+    st = None
+    _leave_together(err, dist.group.WORLD, release=held.clear)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -75,7 +103,9 @@ def _train_worker(rank, world, port):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=180))
+    host_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=400))
+    err = None
     try:
         n = 6000
         indptr, indices = make_graph(n, 14, seed=9, hub=400)
@@ -101,10 +131,9 @@ def _train_worker(rank, world, port):
         both = [torch.empty_like(flat) for _ in range(world)]
         dist.all_gather(both, flat)
         assert torch.equal(both[0], both[1])                  # the replicas stay bit-identical
-        torch.cuda.synchronize()
-        dist.barrier()
-    finally:
-        dist.destroy_process_group()
+    except BaseException as e:                                # noqa: BLE001 -- re-raised by _leave_together
+        err = e
+    _leave_together(err, host_group)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

@@ -347,6 +347,84 @@ def test_aggregate_forward_backward(fastgl, mode, dim):
     assert rel_err(dx.cpu().numpy(), refb) <= AGG_RTOL
 
 
+@pytest.mark.parametrize("mode", [0, 2])
+@pytest.mark.parametrize("with_map", [False, True])
+def test_aggregate_reports_an_out_of_range_id_and_matches_the_oracle_without_it(fastgl, mode, with_map):
+    """One edge carries a source id beyond the input rows (and one a negative id): the ids are never dereferenced,
+    the status word reports them, and the result equals the oracle's on the block with those two edges removed."""
+    rng = np.random.default_rng(99 + mode)
+    n_dst, n_src, n_table, dim = 300, 900, 5000, 100
+    indptr, src = random_block(rng, n_dst, n_src, 40, zero_frac=0.0)
+    row_map = rng.permutation(n_table)[:n_src].astype(np.int32) if with_map else None
+    table = rng.standard_normal((n_table if with_map else n_src, dim)).astype(np.float32)
+    sdeg = np.maximum(oc.cal_deg(src, n_src), 1)
+    ddeg = np.maximum(np.diff(indptr), 1).astype(np.int32)
+    bad = src.copy()
+    e_hi, e_lo = int(indptr[17]), int(indptr[170])              # the first edges of rows 17 and 170
+    bad[e_hi] = n_src + 12345
+    bad[e_lo] = -3
+    if with_map:
+        row_map_bad = row_map.copy()
+        victim = int(bad[int(indptr[5])])                      # a third edge whose *mapped* row is beyond the table
+        row_map_bad[victim] = n_table + 7
+    out = fastgl.aggregate(mode, to_dev(indptr), to_dev(bad), to_dev(table), n_dst, to_dev(sdeg), to_dev(ddeg),
+                           row_map=to_dev(row_map_bad) if with_map else None)
+    with pytest.raises(RuntimeError, match="out of range"):
+        fastgl.check_status(dev())
+    fastgl.check_status(dev())                                  # cleared: the next check passes
+    # the oracle on the same block without the bad edges, weights of the remaining edges unchanged
+    x = table[row_map] if with_map else table
+    w = np.ones(len(src), dtype=np.float64)
+    if mode == 2:
+        dst_of = np.repeat(np.arange(n_dst), np.diff(indptr))
+        w = (1.0 / np.sqrt(ddeg[dst_of].astype(np.float32))).astype(np.float64) * (1.0 / np.sqrt(sdeg[src].astype(np.float32))).astype(np.float64)
+    keep = np.ones(len(src), dtype=bool)
+    keep[[e_hi, e_lo]] = False
+    if with_map:
+        keep &= src != victim
+    ref = np.zeros((n_dst, dim), dtype=np.float64)
+    dst_of = np.repeat(np.arange(n_dst), np.diff(indptr))
+    np.add.at(ref, dst_of[keep], x[src[keep]].astype(np.float64) * w[keep, None])
+    assert rel_err(out.cpu().numpy(), ref) <= AGG_RTOL
+    # backward: the bad edges scatter nothing and are reported
+    dy = rng.standard_normal((n_dst, dim)).astype(np.float32)
+    dx = fastgl.aggregate_backward(mode, to_dev(indptr), to_dev(bad), to_dev(dy), n_src, to_dev(sdeg), to_dev(ddeg))
+    with pytest.raises(RuntimeError, match="out of range"):
+        fastgl.check_status(dev())
+    refb = np.zeros((n_src, dim), dtype=np.float64)
+    keep_b = np.ones(len(src), dtype=bool)
+    keep_b[[e_hi, e_lo]] = False
+    np.add.at(refb, src[keep_b], dy[dst_of[keep_b]].astype(np.float64) * w[keep_b, None])
+    assert rel_err(dx.cpu().numpy(), refb) <= AGG_RTOL
+
+
+def test_gather_rows_reports_an_out_of_range_id(fastgl):
+    table = torch.randn((1000, 100), device=dev())
+    ids = torch.tensor([5, 1000, 999, -1, 0], dtype=torch.int32, device=dev())
+    got = fastgl.gather_rows(table, ids)
+    with pytest.raises(RuntimeError, match="out of range"):
+        fastgl.check_status(dev())
+    assert torch.equal(got[[0, 2, 4]], table[[5, 999, 0]]) and not got[[1, 3]].any()
+
+
+def test_bounded_barrier_wait_runs_out_and_the_workspace_recovers(fastgl):
+    """A team barrier that one arrival never reaches gives up after its spin limit, reports FGL_ERR_TIMEOUT through
+    the status word (no fault, no hang), and the same workspace then runs the next barrier-using call correctly."""
+    import ctypes
+    from fastgl import _capi
+    d = dev()
+    ws = fastgl._ws(d)
+    rc = _capi.lib().fgl_selftest_barrier_timeout(ws, 4, ctypes.c_int64(1000), ctypes.c_void_p(torch.cuda.current_stream(d).cuda_stream))
+    assert rc == 0
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        fastgl.check_status(d)
+    fastgl.check_status(d)
+    degs = torch.randint(0, 9, (1_000_003,), dtype=torch.int32, device=d)
+    out = fastgl.exclusive_sum(degs)                            # two-level scan: uses the same barrier
+    fastgl.check_status(d)
+    assert torch.equal(out[1:].long(), torch.cumsum(degs.long(), 0))
+
+
 @pytest.mark.parametrize("dim", [100, 128, 256])
 def test_aggregate_sampled_block_shapes_with_row_map(fastgl, dim):
     # in-degrees 0..15 (the sampled-block case) plus a few long rows, both zero-degree conventions

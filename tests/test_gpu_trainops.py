@@ -183,3 +183,19 @@ def test_aggregate_backward_starting_from_the_self_gradient(fastgl):
     plain[:n_dst] += d2[:, :47]
     got = fastgl.aggregate_backward(fastgl.AGG_SUM, indptr, src, d2[:, 47:], n_src, d_self=d2[:, :47])
     assert float((got - plain).abs().max()) <= 1e-5 * float(plain.abs().max())
+
+
+def test_self_gradient_rows_beyond_the_device_side_row_count_are_ignored(fastgl):
+    """Padded launch (real row count on the device): whatever the padded rows of dy_self hold, dx is zero there."""
+    rng = np.random.default_rng(6)
+    n_real, n_pad, n_src, deg, dim = 500, 768, 2048, 7, 128
+    indptr = torch.zeros(n_pad + 1, dtype=torch.int32, device=DEV)
+    indptr[: n_real + 1] = torch.arange(0, (n_real + 1) * deg, deg, dtype=torch.int32, device=DEV)
+    src = torch.from_numpy(rng.integers(0, n_src, n_pad * deg).astype(np.int32)).to(DEV)
+    dcat = torch.randn((n_pad, 2 * dim), device=DEV)            # the padded rows hold non-zero garbage
+    n_dev = torch.tensor([n_real], dtype=torch.int32, device=DEV)
+    got = fastgl.aggregate_backward(fastgl.AGG_MEAN, indptr, src, dcat[:, dim:], n_src, n_dst_dev=n_dev, d_self=dcat[:, :dim])
+    want = fastgl.aggregate_backward(fastgl.AGG_MEAN, indptr[: n_real + 1].contiguous(), src[: n_real * deg].contiguous(),
+                                     dcat[:n_real, dim:].contiguous(), n_src)
+    want[:n_real] += dcat[:n_real, :dim]
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
