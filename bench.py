@@ -14,7 +14,9 @@ itself has no CPU code path and is CUDA-only for sm_80) on the host cores.
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -110,10 +112,39 @@ class ClockSampler:
         return out
 
 
+def load_ncu_traffic(config: str, window: int):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the two window-level kernels, from the
+    tracked summary of an ncu capture of this workload: (aggregation, sampler, note).  The summary names the kernel
+    sources it was captured with; if those have changed since, the figures are withheld."""
+    path = os.path.join(ROOT, "profiles", f"dram_traffic_{config}.json")
+    if not os.path.exists(path):
+        return None, None, None
+    with open(path) as f:
+        prof = json.load(f)
+    entry = prof.get("window", {}).get(str(window))
+    if entry is None:
+        return None, None, None
+    csrc = os.path.join(ROOT, "fastgl-ae_b200", "csrc")
+    stale = []
+    for name, sha in prof.get("sources_sha16", {}).items():
+        with open(os.path.join(csrc, name), "rb") as f:
+            if hashlib.sha256(f.read()).hexdigest()[:16] != sha:
+                stale.append(name)
+    agg = None if "aggregate.cu" in stale else entry.get("agg_fwd_window")
+    smp = None if "sample_map.cu" in stale else entry.get("sample_map")
+    note = f"profile predates the current {', '.join(stale)}: figure withheld" if stale else None
+    return agg, smp, note
+
+
 def build_inputs(cfg, device, rank=0, world=1):
     from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
     a, b, c = cfg.get("rmat", (0.57, 0.19, 0.19))
     indptr, indices = rmat_graph(cfg["n_nodes"], cfg["avg_degree"], seed=12345, device=device, a=a, b=b, c=c)
+    if cfg.get("layout") == "degree":
+        # the same graph with its nodes renumbered by descending degree; features, labels and training seeds are drawn
+        # afterwards, in the new numbering (they are i.i.d. per node, so the workload is the same in distribution)
+        from fastgl_b200.graphgen import relabel_by_degree
+        indptr, indices, _, _ = relabel_by_degree(indptr, indices)
     if cfg.get("sharded") and world > 1:
         # every rank fills only its own row block; the blocks are then opened by all ranks over CUDA IPC
         from fastgl_b200.sharding import rows_per_shard, share_feature_shards
@@ -233,6 +264,89 @@ def run_gates(cfg, args, indptr, indices, feat, train, device):
     return out
 
 
+def run_sharded_leg(cfg, args, tr, indptr, rank, world, device, barrier, max_over_ranks):
+    """The feature-sharded configuration's data path on the graph at hand: 1024-d fp32 rows block-partitioned over
+    the ranks' HBM (CUDA IPC, plain 128-bit peer loads over NVLink, no collective), one window's first-layer mean
+    aggregation straight through the sharded table.  Gate: the result equals, bit for bit, the same launch on a dense
+    local copy of the table (itself assembled with the sharded row gather)."""
+    import fastgl
+    from fastgl_b200.sharding import rows_per_shard, share_feature_shards
+    D = 1024
+    n = indptr.numel() - 1
+    if n * D * 4 > 24e9:
+        return {"status": "skipped", "reason": f"a dense local copy of {n} x {D} floats (the gate) does not fit the leg's budget"}
+    out = {"status": "failed"}
+    st = full = fb = got = want = None
+    failure = None
+    try:   # set-up: a rank that cannot allocate or map says so; the ranks then skip the measurement together
+        rps = rows_per_shard(n, world)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(777 + 31 * rank)
+        shard = torch.randn((rps, D), generator=gen, device=device, dtype=torch.float32)
+    except RuntimeError as e:
+        failure = str(e).splitlines()[0][:200]
+        shard = torch.zeros((1, D), device=device)
+    if max_over_ranks(0.0 if failure is None else 1.0) > 0:
+        return {"status": "failed", "reason": failure or "another rank could not allocate its shard"}
+    st = share_feature_shards(shard, n)
+    try:
+        full = fastgl.gather_rows(st, torch.arange(n, dtype=torch.int32, device=device))
+        nb, batch = args.window, cfg["batch"]
+        seeds = tr.my_seeds[: nb * batch]
+        if seeds.numel() < nb * batch:
+            seeds = tr.my_seeds.repeat(-(-nb * batch // tr.my_seeds.numel()))[: nb * batch]
+        counts = torch.full((nb,), batch, dtype=torch.int32, device=device)
+        fb = tr.sampler.sample_window(seeds.view(nb, batch).contiguous(), counts, reuse=False)
+        hop = len(cfg["fanouts"]) - 1
+        ch = fb.counts_host()
+        total = int(ch[:, hop].sum())
+        got = torch.empty((total, D), dtype=torch.float32, device=device)
+        want = torch.empty((total, D), dtype=torch.float32, device=device)
+        fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, st, got)
+        torch.cuda.synchronize()
+    except RuntimeError as e:
+        failure = str(e).splitlines()[0][:200]
+    if max_over_ranks(0.0 if failure is None else 1.0) > 0:
+        out = {"status": "failed", "reason": failure or "another rank failed during set-up"}
+    else:
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record()
+            fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, st, got)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, full, want)
+        fastgl.check_status(device)
+        equal = bool(torch.equal(got, want))
+        remote_edges = edges = 0
+        for b in range(nb):
+            n_e = int(ch[b, 8 + hop])
+            rows = fb.nodes[b].long()[fb.block_src[hop][b, :n_e].long()]
+            remote_edges += int(((rows // rps) != rank).sum())
+            edges += n_e
+        ms = max_over_ranks(statistics.median(times))
+        all_equal = max_over_ranks(0.0 if equal else 1.0) == 0.0
+        remote_gbs = remote_edges * D * 4 / (ms * 1e-3) / 1e9
+        out = {"status": "ok" if all_equal else "mismatch", "table": f"{n} rows x {D} fp32, {world} shards of {rps} rows",
+               "window_rows": total, "window_edges": edges, "launch_ms": ms, "remote_edge_fraction": remote_edges / max(1, edges),
+               "remote_gb_per_s_per_gpu": remote_gbs, "nvlink_peak_gb_per_s": 900.0, "frac_of_nvlink": remote_gbs / 900.0,
+               "equal_to_local_copy": all_equal,
+               "note": "rank 0's remote bytes over the slowest rank's median launch time; rows a window re-reads are "
+                       "served by this GPU's L2, so the figure can exceed the link rate"}
+    got = want = fb = None
+    # nobody unmaps a shard while a peer may still read it
+    torch.cuda.synchronize()
+    barrier()
+    st = full = None
+    torch.cuda.ipc_collect()
+    torch.cuda.empty_cache()
+    barrier()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -252,10 +366,17 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=150, help="mini-batches of the CPU baseline sample (about 10 s of CPU work)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gates", action="store_true", help="skip the untimed correctness gates (profiler runs)")
+    ap.add_argument("--layout", default="generated", choices=["generated", "degree"],
+                    help="node numbering of the synthetic graph: as generated, or renumbered by descending degree (the "
+                         "reference's sort_degree ranking used as a table layout)")
+    ap.add_argument("--repeats", type=int, default=7, help="how often the --steps region is timed (the median is reported)")
+    ap.add_argument("--no-sharded-leg", action="store_true", help="N > 1: skip the row-sharded feature table leg")
+    ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "oneshot"],
+                    help="N > 1: gradient all-reduce by NCCL, or by this library's one-launch peer-store kernel")
     ap.add_argument("--kernels", action="store_true",
                     help="print a per-kernel table (time, algorithmic bytes, fraction of the HBM peak) instead of training")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config], layout=args.layout)
     args.warmup = max(args.warmup, 3) if args.impl == "fastgl" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -268,7 +389,7 @@ def main():
                                f"(symmetrised), {cfg['feat_dim']}-d fp32 features resident in HBM, {cfg['n_classes']} classes, "
                                f"{len(cfg['fanouts'])}-layer {model_name} hidden {cfg['hidden']}, fanout {cfg['fanouts']}, "
                                f"batch {cfg['batch']} per GPU",
-                   "window": args.window, "parallelism": f"dp{world}", "global_batch": cfg["batch"] * world,
+                   "layout": args.layout, "window": args.window, "parallelism": f"dp{world}", "global_batch": cfg["batch"] * world,
                    "l2": f"inputs larger than L2: {table_mb:.0f} MB feature table + {adj_mb:.0f} MB adjacency are gathered at "
                          "random each step"}
 
@@ -322,7 +443,7 @@ def main():
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
                  reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph,
-                 table_slots=None if args.table_slots < 0 else args.table_slots)
+                 table_slots=None if args.table_slots < 0 else args.table_slots, grad_sync=args.grad_sync)
 
     def barrier():
         if world > 1:
@@ -347,36 +468,55 @@ def main():
     #     the sampled blocks and, for the SAGE first layer, the window aggregation against float64 torch algebra
     gates = None if args.no_gates else run_gates(cfg, args, indptr, indices, feat, train, device)
 
-    # --- set-up (tables, workspace, graph capture), warm-up, then the device-resident timed region ------------
+    # --- set-up (tables, workspace, graph capture), then a settle phase of at least two full windows whatever
+    #     --warmup says (the sampler's tables, the allocator and NCCL reach their steady state), then the warm-up
     tr.prime()
+    tr.run_steps(2 * args.window)
     tr.run_steps(args.warmup)
     fastgl.check_status(device)
     barrier()
     clocks = ClockSampler(local_rank)
     if rank == 0:
         clocks.start()
-    tr.sampled_edges = 0
     tr.time_layer0 = True
     tr.layer0_events.clear()
     tr.sample_events.clear()
-    counter_at_start = tr.sampler.batch_counter
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    tr.run_steps(args.steps)
-    ev1.record()
-    barrier()
-    ms = max_over_ranks(ev0.elapsed_time(ev1))
-    edges_all = sum_over_ranks(float(tr.sampled_edges))
+
+    def timed_region(**kw):
+        """EXACTLY --steps steps between two device events, a barrier and a synchronize on both sides; returns
+        (milliseconds: max over ranks, sampled edges: sum over ranks, losses)."""
+        tr.sampled_edges = 0
+        barrier()
+        ev0.record()
+        losses = tr.run_steps(args.steps, **kw)
+        ev1.record()
+        barrier()
+        return max_over_ranks(ev0.elapsed_time(ev1)), sum_over_ranks(float(tr.sampled_edges)), losses
+
+    def repeats_for(first_ms: float) -> int:
+        """The --steps region is repeated at least seven times, and often enough for the clock sampler to see it."""
+        r = max(args.repeats, math.ceil(300.0 / max(first_ms, 1e-3)))
+        r = int(max_over_ranks(float(min(r, 101))))
+        return r if r % 2 == 1 else r + 1
+
+    # --- device-resident regions: value = median over the repeats ---------------------------------------------
+    regions = [timed_region()]
+    for _ in range(repeats_for(regions[0][0]) - 1):
+        regions.append(timed_region())
+        if len(tr.layer0_events) > 256:
+            del tr.layer0_events[:-128], tr.sample_events[:-128]
     tr.time_layer0 = False
-    value = edges_all / (ms * 1e-3)
     fastgl.check_status(device)
+    by_ms = sorted(regions, key=lambda r: r[0])
+    ms, edges_all, _ = by_ms[len(by_ms) // 2]
+    value = edges_all / (ms * 1e-3)
 
     # --- roofline of the dominant kernel: the window-level first-layer aggregation (mean of neighbours + self
     #     rows, straight from the feature table), one launch per window, timed by events on the launching stream
     D = cfg["feat_dim"]
     peak, peak_kind = load_peaks()
-    full = [(s.elapsed_time(e), fb) for s, e, fb in tr.layer0_events if fb.n_batches == args.window]
+    full = [(s_.elapsed_time(e_), fb) for s_, e_, fb in tr.layer0_events if fb.n_batches == args.window]
     agg_ms = [t for t, _ in full]
     roofline = {"kernel": "agg_fwd_kernel<4, MEAN, row_map> over a window (layer 0)", "bound": "hbm", "achieved": None,
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": None, "traffic": None}
@@ -391,6 +531,8 @@ def main():
         for b in range(fb.n_batches):
             n_dst, n_edges = int(counts_h[b, hop]), int(counts_h[b, 8 + hop])
             touched = torch.cat([fb.block_src[hop][b, :n_edges], torch.arange(n_dst, dtype=torch.int32, device=device)])
+            # distinct rows are counted per mini-batch and summed over the window: a row that two mini-batches of
+            # the window share is credited twice, although the second read may be served by L2
             r_all = int(torch.unique(touched).numel())
             # reads: every distinct feature row once + its id; edge ids and offsets; writes: self and mean rows
             alg += 4 * D * r_all + 4 * r_all + 4 * n_edges + 4 * (n_dst + 1) + 2 * 4 * D * n_dst
@@ -400,44 +542,43 @@ def main():
                 dg = deg_all[nodes[:S]]
                 k = torch.clamp(dg, max=fan_s[h])
                 sm_bytes += S * 40 + int(torch.minimum(32 * ((4 * dg + 31) // 32), 32 * k).sum()) + 4 * E + 4 * U
-        mean_ms = statistics.mean(agg_ms)
-        achieved = alg / (mean_ms * 1e-3) / 1e9
+        med_ms = statistics.median(agg_ms)
+        achieved = alg / (med_ms * 1e-3) / 1e9
         roofline.update({"achieved": achieved, "frac": achieved / peak, "algorithmic_bytes_per_launch": alg,
-                         "launch_ms": mean_ms, "launches_timed": len(agg_ms)})
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the two window-level kernels on this workload,
-        # taken from ncu captures (ncu --set full) of the same command at these window sizes (profiles/)
-        ncu_traffic = {8: (744.6e6, 338.7e6), 16: (1467.5e6, 1011.0e6)}
-        default_run = args.config == "products-like" and args.teams == 0 and args.table_slots < 0
-        if default_run and args.window in ncu_traffic:
-            roofline["traffic"] = ncu_traffic[args.window][0]
-        smp = [s.elapsed_time(e) for s, e, nb in tr.sample_events if nb == args.window]
+                         "launch_ms": med_ms, "launch_ms_min": min(agg_ms), "launch_ms_max": max(agg_ms),
+                         "launches_timed": len(agg_ms)})
+        default_run = args.teams == 0 and args.table_slots < 0 and not args.reorder and args.layout == "generated"
+        agg_traffic, smp_traffic, traffic_note = load_ncu_traffic(args.config, args.window) if default_run else (None, None, None)
+        roofline["traffic"] = agg_traffic
+        if traffic_note:
+            roofline["traffic_note"] = traffic_note
+        smp = [s_.elapsed_time(e_) for s_, e_, nb in tr.sample_events if nb == args.window]
         if smp:
-            smp_ms = statistics.mean(smp)
+            smp_ms = statistics.median(smp)
             sample_roofline = {"kernel": "sample_map_kernel (3 hops x window)", "bound": "hbm",
                                "achieved": sm_bytes / (smp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                                "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
-                               "launch_ms": smp_ms, "launches_timed": len(smp),
-                               "traffic": ncu_traffic[args.window][1] if (default_run and args.window in ncu_traffic) else None,
+                               "launch_ms": smp_ms, "launch_ms_min": min(smp), "launch_ms_max": max(smp),
+                               "launches_timed": len(smp), "traffic": smp_traffic,
                                "note": "event-timed on the launching stream; includes the host gap before the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
     host_rows, host_counts = [], []
     for _ in range(args.steps):
-        s, c = tr._next_window_seeds(1)
-        host_rows.append(s.cpu())
-        host_counts.append(c)
+        s_, c_ = tr._next_window_seeds(1)
+        host_rows.append(s_.cpu())
+        host_counts.append(c_)
     seeds_h = torch.cat(host_rows).pin_memory()
     counts_h = torch.cat(host_counts).pin_memory()
-    tr.sampled_edges = 0
-    barrier()
-    ev0.record()
-    losses = tr.run_steps(args.steps, host_seeds=(seeds_h, counts_h), read_loss_each_step=True)
-    ev1.record()
-    barrier()
-    ms_e2e = max_over_ranks(ev0.elapsed_time(ev1))
-    e2e_edges = sum_over_ranks(float(tr.sampled_edges))
+    e2e_regions = [timed_region(host_seeds=(seeds_h, counts_h), read_loss_each_step=True) for _ in range(len(regions))]
+    e2e_by_ms = sorted(e2e_regions, key=lambda r: r[0])
+    ms_e2e, e2e_edges, losses = e2e_by_ms[len(e2e_by_ms) // 2]
     clock_info = clocks.stop() if rank == 0 else None
     fastgl.check_status(device)
+
+    sharded_leg = None
+    if world > 1 and not args.no_sharded_leg:
+        sharded_leg = run_sharded_leg(cfg, args, tr, indptr, rank, world, device, barrier, max_over_ranks)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and cfg.get("model") != "gcn" and cfg["n_nodes"] <= 10_000_000:
@@ -459,22 +600,36 @@ def main():
         n_layers = len(cfg["fanouts"])
         per_step = (5 * n_layers - 1) if tr.graphed is not None else 2 * (n_layers - 1)
         launches = args.steps * per_step + 2 * n_windows
+        epoch_s = steps_per_epoch * ms / args.steps * 1e-3
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32" if args.matmul == "fp32" else "tf32", "data": "synthetic", "config": config_json,
-                "per_gpu_value": value / world, "epoch_time_s": steps_per_epoch * ms / args.steps * 1e-3,
+                "repeats": len(regions), "ms_per_step_min": by_ms[0][0] / args.steps, "ms_per_step_max": by_ms[-1][0] / args.steps,
+                "settle_steps": 2 * args.window,
+                "per_gpu_value": value / world, "epoch_time_s": epoch_s,
+                "epoch_time_kind": "measured" if args.steps >= steps_per_epoch else f"extrapolated from {args.steps} steps",
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
                 "dense_matmul": args.matmul, "cuda_graph": not args.no_graph, "graph_fallback_steps": tr.graph_fallbacks,
+                "gradient_sync": tr.grad_sync_kind(),
                 "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
+                        "ms_per_step_min": e2e_by_ms[0][0] / args.steps, "ms_per_step_max": e2e_by_ms[-1][0] / args.steps,
+                        "repeats": len(e2e_regions),
                         "h2d_bytes_per_step": cfg["batch"] * 4 + 4, "d2h_bytes_per_step": 4 + 64},
                 "gpu_launches": launches * world, "roofline": roofline, "roofline_sample_map": sample_roofline,
                 "gates": gates, "clocks": clock_info}
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
+        if sharded_leg is not None:
+            line["sharded"] = sharded_leg
         print(json.dumps(line))
     if world > 1:
-        # drop peers' mappings before any rank tears its allocations down
+        # every rank's GPU work has drained; only then drop the mappings of the peers' memory, and only after every
+        # rank has dropped them tear the allocations down
+        torch.cuda.synchronize()
+        dist.barrier()
+        tr.release_peers()
         del tr, feat
+        torch.cuda.ipc_collect()
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()

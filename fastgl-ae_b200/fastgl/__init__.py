@@ -33,7 +33,7 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
-    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -602,6 +602,61 @@ def adam_step_(param, grad, exp_avg, exp_avg_sq, step_dev, lr=1e-3, betas=(0.9, 
                                  ctypes.c_float(lr), ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps),
                                  ctypes.c_float(weight_decay), _ptr(step_dev), _stream(dev))
     _raise(rc, "adam_step_")
+
+
+class PeerSync:
+    """The peer-mapped buffers ``allreduce_adam_`` exchanges gradients through (struct fgl_peer_sync).
+
+    ``recv[q]`` / ``flags[q]``: rank q's receive buffer (float32[2 * world * n_pad]) and flag array
+    (int32[2 * world * n_chunks]) as CUDA tensors mapped into this process -- this rank's own allocations at index
+    ``rank``, the peers' opened over CUDA IPC (``fastgl_b200.sharding.open_peer_tensors``).  All zero before the first
+    step."""
+
+    def __init__(self, rank: int, world: int, recv, flags, n: int):
+        if world > _capi.MAX_PEERS:
+            raise RuntimeError(f"at most {_capi.MAX_PEERS} ranks")
+        self.rank, self.world, self.n = int(rank), int(world), int(n)
+        self.n_chunks = int(lib().fgl_peer_sync_chunks(ctypes.c_int64(n)))
+        self.n_pad = self.n_chunks * 2048
+        self.keep = (list(recv), list(flags))
+        for t in recv:
+            if t.dtype != torch.float32 or t.numel() < 2 * world * self.n_pad:
+                raise RuntimeError("receive buffers must be float32[2 * world * n_pad]")
+        for t in flags:
+            if t.dtype != torch.int32 or t.numel() < 2 * world * self.n_chunks:
+                raise RuntimeError("flag arrays must be int32[2 * world * n_chunks]")
+        self.c = _capi.PeerSync()
+        self.c.rank, self.c.world, self.c.n_pad, self.c.n_chunks = self.rank, self.world, self.n_pad, self.n_chunks
+        for q in range(world):
+            self.c.recv[q] = recv[q].data_ptr()
+            self.c.flags[q] = flags[q].data_ptr()
+
+    @staticmethod
+    def sizes(n: int, world: int):
+        """(floats of a receive buffer, int32 words of a flag array) for a flat gradient of ``n`` elements."""
+        chunks = int(lib().fgl_peer_sync_chunks(ctypes.c_int64(n)))
+        return 2 * world * chunks * 2048, 2 * world * chunks
+
+
+def allreduce_adam_(peers: PeerSync, param, grad, exp_avg, exp_avg_sq, step_dev, lr=1e-3, betas=(0.9, 0.999), eps=1e-8,
+                    weight_decay=0.0, spin_limit=4_000_000):
+    """Average ``grad`` over the ranks of ``peers`` and apply one Adam step, in one launch (see fgl_allreduce_adam).
+    ``step_dev``: int32[3] CUDA tensor, zero before the first step.  The flat buffers hold a multiple of 4 floats."""
+    for t, n in ((param, "param"), (grad, "grad"), (exp_avg, "exp_avg"), (exp_avg_sq, "exp_avg_sq")):
+        _check_f32(t, n)
+        if t.numel() != param.numel():
+            raise RuntimeError("param, grad and the two moment buffers must have the same length")
+    _check_i32(step_dev, "step_dev")
+    if step_dev.numel() < 3 or param.numel() != peers.n:
+        raise RuntimeError("step_dev must hold three int32 words and the buffers peers.n floats")
+    dev = param.device
+    ws = _ws(dev)
+    with _on_device(dev):
+        rc = lib().fgl_allreduce_adam(ws, ctypes.byref(peers.c), _ptr(param), _ptr(grad), _ptr(exp_avg), _ptr(exp_avg_sq),
+                                      ctypes.c_int64(param.numel()), ctypes.c_float(lr), ctypes.c_float(betas[0]),
+                                      ctypes.c_float(betas[1]), ctypes.c_float(eps), ctypes.c_float(weight_decay),
+                                      _ptr(step_dev), ctypes.c_int64(spin_limit), _stream(dev))
+    _raise(rc, "allreduce_adam_", ws)
 
 
 def forward_gat(edge_ptr, edge_data, src_edges, input_feat, neighbor_num, dst_nodes, num_heads):

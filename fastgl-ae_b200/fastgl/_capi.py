@@ -25,6 +25,7 @@ EXPORTS = (
     "fgl_ws_check", "fgl_ws_status_peek", "fgl_selftest_barrier_timeout", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
     "fgl_stage_segments", "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_exclusive_sum_noalloc_status", "fgl_agg_fwd", "fgl_agg_fwd_sharded", "fgl_gather_rows", "fgl_agg_edge_fwd", "fgl_agg_edge_bwd", "fgl_agg_edge_wgrad", "fgl_agg_fwd_window", "fgl_agg_bwd",
     "fgl_agg_bwd_self", "fgl_bias_relu_dropout", "fgl_relu_dropout_bwd", "fgl_softmax_xent", "fgl_linear_softmax_xent", "fgl_adam_step",
+    "fgl_sizeof_peer_sync", "fgl_peer_sync_chunks", "fgl_allreduce_adam",
 )
 
 
@@ -54,6 +55,15 @@ class FusedArgs(ctypes.Structure):
         ("block_src", ctypes.c_void_p * MAX_HOPS),
         ("block_src_stride", ctypes.c_int64 * MAX_HOPS),
     ]
+
+
+MAX_PEERS = 8
+
+
+class PeerSync(ctypes.Structure):
+    """struct fgl_peer_sync"""
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("recv", ctypes.c_void_p * MAX_PEERS),
+                ("flags", ctypes.c_void_p * MAX_PEERS), ("n_pad", ctypes.c_int64), ("n_chunks", ctypes.c_int32)]
 
 
 class Segment(ctypes.Structure):
@@ -89,6 +99,10 @@ def lib() -> ctypes.CDLL:
         for name in EXPORTS:
             if name not in ("fgl_status_str", "fgl_last_error"):
                 getattr(handle, name).restype = ctypes.c_int
+        handle.fgl_peer_sync_chunks.restype = ctypes.c_int64
+        handle.fgl_peer_sync_chunks.argtypes = [ctypes.c_int64]
+        if handle.fgl_sizeof_peer_sync() != ctypes.sizeof(PeerSync):
+            raise ImportError("struct fgl_peer_sync layout differs between the library and this binding")
         _lib = handle
     return _lib
 

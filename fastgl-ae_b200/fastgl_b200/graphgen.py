@@ -90,6 +90,42 @@ def rmat_graph(n_nodes: int, avg_degree: float, seed: int = 12345, device="cpu",
     return indptr, indices
 
 
+def relabel_by_degree(indptr: torch.Tensor, indices: torch.Tensor, chunk_edges: int = 1 << 27):
+    """Renumber the nodes by descending in-degree (ties by old id): new node ``i`` is old node ``order[i]``.
+
+    The reference ranks nodes by degree to choose what its GPU feature cache holds (``sort_degree``, utilis.py:86-89;
+    ``pre_sample`` :64-74 ranks by sampling frequency for the same purpose).  With the whole table resident in HBM
+    the same ranking becomes a layout: the rows that most sampled edges request are packed at the front of the table
+    (a few megabytes that stay in L2 and in a handful of TLB entries), and so are their adjacency lists.
+    Returns ``(indptr, indices, order, new_of_old)``; per-node arrays move with ``x[order]``, node ids with
+    ``new_of_old[ids]``.  Adjacency lists keep their order."""
+    n = indptr.numel() - 1
+    dev = indptr.device
+    deg = indptr[1:] - indptr[:-1]
+    order = torch.argsort(deg, descending=True, stable=True)
+    new_of_old = torch.empty(n, dtype=torch.int64, device=dev)
+    new_of_old[order] = torch.arange(n, device=dev)
+    new_deg = deg[order]
+    new_indptr = torch.zeros(n + 1, dtype=indptr.dtype, device=dev)
+    torch.cumsum(new_deg, 0, out=new_indptr[1:])
+    old_start = indptr[:-1][order]
+    new_indices = torch.empty_like(indices)
+    map32 = new_of_old.to(indices.dtype)
+    lo = 0
+    bounds = new_indptr.cpu()
+    while lo < n:   # node ranges of at most chunk_edges edges (a single node with more edges forms its own range)
+        hi = int(torch.searchsorted(bounds, bounds[lo] + chunk_edges, right=True)) - 1
+        hi = min(n, max(hi, lo + 1))
+        e0, e1 = int(bounds[lo]), int(bounds[hi])
+        if e1 > e0:
+            shift = torch.repeat_interleave(old_start[lo:hi] - new_indptr[lo:hi], new_deg[lo:hi], output_size=e1 - e0)
+            pos = torch.arange(e0, e1, device=dev) + shift
+            new_indices[e0:e1] = map32[indices[pos].long()]
+            del shift, pos
+        lo = hi
+    return new_indptr, new_indices, order, new_of_old
+
+
 def synthetic_node_data(n_nodes: int, feat_dim: int, n_classes: int, train_frac: float, seed: int = 12345,
                         device="cpu"):
     """fp32 N(0,1) features, uniform labels and a random training subset (sorted ids, int32)."""

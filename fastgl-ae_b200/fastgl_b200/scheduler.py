@@ -29,6 +29,26 @@ def overlap_matrix(node_lists, n_nodes: int, chunk: int = 1 << 22) -> torch.Tens
     return out
 
 
+def overlap_matrix_padded(nodes: torch.Tensor, counts: torch.Tensor, n_nodes: int, chunk: int = 1 << 22) -> torch.Tensor:
+    """``overlap_matrix`` for the node lists as the fused sampler leaves them on the device: ``nodes`` int32[W, stride]
+    of which only the first ``counts[b]`` entries of row ``b`` are ids (the rest is stale), ``counts`` an integer CUDA
+    tensor.  Nothing is read back, so this can be enqueued right behind the sampler."""
+    W, stride = nodes.shape
+    dev = nodes.device
+    valid = torch.arange(stride, device=dev)[None, :] < counts.to(torch.int64)[:, None]
+    ids = torch.where(valid, nodes, torch.zeros_like(nodes)).long()
+    rows = torch.arange(W, device=dev)[:, None].expand(W, stride)
+    out = torch.zeros((W, W), dtype=torch.float32, device=dev)
+    for lo in range(0, n_nodes, chunk):
+        hi = min(n_nodes, lo + chunk)
+        inside = valid & (ids >= lo) & (ids < hi)
+        mask = torch.zeros((W, hi - lo), dtype=torch.float32, device=dev)
+        # ids are distinct within a row, so every cell receives at most one 1 (entries outside add 0 to column 0)
+        mask.index_put_((rows, torch.where(inside, ids - lo, torch.zeros_like(ids))), inside.to(torch.float32), accumulate=True)
+        out += mask @ mask.t()
+    return out
+
+
 def greedy_order(overlap: torch.Tensor, sizes: torch.Tensor) -> list[int]:
     """Greedy chain over the match degrees (utilis.py:41-60)."""
     W = overlap.size(0)
@@ -61,3 +81,23 @@ class MatchReorder:
             return list(range(len(node_lists)))
         sizes = torch.tensor([n.numel() for n in node_lists])
         return greedy_order(overlap_matrix(node_lists, self.num_nodes), sizes)
+
+    def enqueue(self, nodes: torch.Tensor, counts: torch.Tensor, key=0) -> None:
+        """Enqueue the overlap computation of a freshly sampled window on the current stream and copy the result to
+        pinned host memory, without waiting: whoever later waits for a read-back enqueued after this call (the
+        window's counts) finds the matrix there.  ``key`` tells windows in flight apart."""
+        if not hasattr(self, "_pinned"):
+            self._pinned = {}
+        W = nodes.size(0)
+        buf = self._pinned.get((key, W))
+        if buf is None:
+            buf = self._pinned[(key, W)] = torch.zeros((W, W), dtype=torch.float32).pin_memory()
+        buf.copy_(overlap_matrix_padded(nodes, counts, self.num_nodes), non_blocking=True)
+
+    def order(self, sizes, key=0) -> list[int]:
+        """The greedy chain for the window whose overlap ``enqueue(..., key)`` produced (its copy must have
+        completed: wait for a later read-back of the same stream first).  ``sizes``: the node-list lengths."""
+        W = len(sizes)
+        if W <= 2:
+            return list(range(W))
+        return greedy_order(self._pinned[(key, W)], torch.as_tensor(sizes))

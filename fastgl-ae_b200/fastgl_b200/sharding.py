@@ -20,6 +20,30 @@ def rows_per_shard(n_rows: int, world: int) -> int:
     return (n_rows + world - 1) // world
 
 
+def open_peer_tensors(local: torch.Tensor, group=None) -> list[torch.Tensor]:
+    """Collective over ``group``: every rank exports ``local`` (a contiguous CUDA tensor, the same shape on every rank)
+    with CUDA IPC and opens the others'; returns one tensor per rank, ``local`` itself at this rank's index.  The
+    returned peer tensors are mappings of the peers' memory: drop them (and call ``torch.cuda.ipc_collect()``) before
+    the owning processes free it."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if not local.is_cuda or not local.is_contiguous():
+        raise RuntimeError("open_peer_tensors needs a contiguous CUDA tensor")
+    rebuild, args = reduce_tensor(local)               # CUDA IPC handle of the allocation
+    exported = [None] * world
+    dist.all_gather_object(exported, (rebuild, args), group=group)
+    out = []
+    for r, (fn, a) in enumerate(exported):
+        if r == rank:
+            out.append(local)
+        else:
+            a = list(a)
+            a[6] = local.device.index                   # open the peer's allocation on this rank's device
+            out.append(fn(*a))
+    dist.barrier(group)
+    return out
+
+
 def share_feature_shards(local_shard: torch.Tensor, n_rows: int, group=None) -> fastgl.ShardedTable:
     """``local_shard``: this rank's float32 [rows_per_shard, dim] block (the last rank may use fewer rows of it).
     Collective over ``group``: returns the table of all ranks' shards as seen from this rank."""
@@ -30,16 +54,5 @@ def share_feature_shards(local_shard: torch.Tensor, n_rows: int, group=None) -> 
     rps = rows_per_shard(n_rows, world)
     if local_shard.size(0) < min(rps, max(0, n_rows - rank * rps)):
         raise RuntimeError("local_shard has fewer rows than this rank's share")
-    rebuild, args = reduce_tensor(local_shard)          # CUDA IPC handle of the shard's allocation
-    exported = [None] * world
-    dist.all_gather_object(exported, (rebuild, args), group=group)
-    shards = []
-    for r, (fn, a) in enumerate(exported):
-        if r == rank:
-            shards.append(local_shard)
-        else:
-            a = list(a)
-            a[6] = local_shard.device.index             # open the peer's allocation on this rank's device
-            shards.append(fn(*a))
-    dist.barrier(group)
+    shards = open_peer_tensors(local_shard, group)
     return fastgl.ShardedTable(shards, rps, local_shard.size(1), n_rows, local_shard.device, ld=local_shard.stride(0))

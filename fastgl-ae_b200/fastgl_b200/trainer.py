@@ -43,6 +43,7 @@ class FlatGrads:
     def __init__(self, params):
         self.params = [p for p in params if p.requires_grad]
         total = sum(p.numel() for p in self.params)
+        total = (total + 3) // 4 * 4      # whole 128-bit vectors: the padding stays zero
         self.buffer = torch.zeros(total, dtype=self.params[0].dtype, device=self.params[0].device)
         off = 0
         for p in self.params:
@@ -65,12 +66,14 @@ class FlatAdam:
     """Adam (torch.optim.Adam's arithmetic, L2 weight decay) as one launch over all parameters: the parameters are
     moved into one flat buffer (each ``p.data`` becomes a view of it, in the order of ``FlatGrads``) next to flat
     first- and second-moment buffers.  The step count lives on the device and the launch advances it, so the launch
-    can be captured in a CUDA graph."""
+    can be captured in a CUDA graph.  With ``peers`` (a ``fastgl.PeerSync``) the same launch first averages the
+    gradient over the data-parallel ranks through peer-mapped buffers: no separate collective."""
 
-    def __init__(self, grads: FlatGrads, lr, weight_decay, betas=(0.9, 0.999), eps=1e-8):
+    def __init__(self, grads: FlatGrads, lr, weight_decay, betas=(0.9, 0.999), eps=1e-8, peers=None):
         self.grads = grads
+        self.peers = peers
         self.lr, self.weight_decay, self.betas, self.eps = lr, weight_decay, betas, eps
-        self.flat = torch.empty_like(grads.buffer)
+        self.flat = torch.zeros_like(grads.buffer)
         off = 0
         with torch.no_grad():
             for p in grads.params:
@@ -80,16 +83,20 @@ class FlatAdam:
                 off += p.numel()
         self.exp_avg = torch.zeros_like(self.flat)
         self.exp_avg_sq = torch.zeros_like(self.flat)
-        self.step_dev = torch.zeros(2, dtype=torch.int32, device=self.flat.device)
+        self.step_dev = torch.zeros(3, dtype=torch.int32, device=self.flat.device)
 
     def step(self):
-        fastgl.adam_step_(self.flat, self.grads.buffer, self.exp_avg, self.exp_avg_sq, self.step_dev, lr=self.lr,
-                          betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)
+        if self.peers is not None:
+            fastgl.allreduce_adam_(self.peers, self.flat, self.grads.buffer, self.exp_avg, self.exp_avg_sq, self.step_dev,
+                                   lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)
+        else:
+            fastgl.adam_step_(self.flat, self.grads.buffer, self.exp_avg, self.exp_avg_sq, self.step_dev, lr=self.lr,
+                              betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)
 
     def zero_state(self):
         self.exp_avg.zero_()
         self.exp_avg_sq.zero_()
-        self.step_dev.zero_()
+        self.step_dev[:2].zero_()     # the exchange counter [2] keeps counting: the peers' flags are monotonic
 
 
 class GraphedStep:
@@ -120,9 +127,11 @@ class GraphedStep:
             self.blocks.append(Block(ptr, src, self.pad_dst[i - 1], self.pad_dst[i], n_dst_dev=self.sizes[i: i + 1]))
         self.graph = None
         self.loss = None
-        # Data-parallel runs keep the gradient all-reduce between two graphs (forward/backward, optimizer step):
-        # every rank then issues the collective the same way whether or not its batch fitted the padded shapes.
-        self.step_in_graph = tr.world == 1
+        # With the library collective, data-parallel runs keep the gradient all-reduce between two graphs
+        # (forward/backward, optimizer step): every rank then issues the collective the same way whether or not its
+        # batch fitted the padded shapes.  With the one-launch exchange the optimizer launch averages the gradients
+        # itself, so the whole step is one graph.
+        self.step_in_graph = tr.world == 1 or tr.oneshot
         self.opt_graph = None
         self.program = SageStepProgram(tr.model, tr.grads, tr.labels, self.x0, self.seeds, self.sizes, self.blocks,
                                        self.pad_dst, self.sizes[L: L + 1], rng_seed=tr.sampler.rng_seed)
@@ -189,7 +198,7 @@ class GraphedStep:
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
                  lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
-                 window_layer0=True, cuda_graph=False, table_direct=True, table_slots=None):
+                 window_layer0=True, cuda_graph=False, table_direct=True, table_slots=None, grad_sync="auto"):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -213,6 +222,16 @@ class Trainer:
         self.use_graph = bool(cuda_graph) and self.sage
         self.graphed = None
         self.graph_fallbacks = 0
+        # gradient averaging across ranks: "nccl" = one all-reduce call per step between forward/backward and the
+        # optimizer; "oneshot" = the optimizer launch exchanges the gradients itself through peer-mapped buffers
+        # (GraphSAGE's flat optimizer on CUDA ranks of one box); "auto" picks the latter where it applies
+        if grad_sync not in ("auto", "nccl", "oneshot"):
+            raise ValueError("grad_sync must be auto, nccl or oneshot")
+        can_oneshot = world > 1 and self.sage and self.dev.type == "cuda" and world <= 8
+        if grad_sync == "oneshot" and not can_oneshot:
+            raise ValueError("grad_sync='oneshot' needs 2..8 CUDA ranks and the GraphSAGE model")
+        self.oneshot = can_oneshot and grad_sync != "nccl"
+        self._peers = None
         self.reset_optimizer()
         self.train_nids = train_nids
         self._train_nids_host = train_nids.cpu()
@@ -222,6 +241,7 @@ class Trainer:
         self._set_epoch_seeds()
         self.sampled_edges = 0
         self.last_loss = None
+        self.last_order = None    # order in which the last window's mini-batches were trained
         self.layer0_events = []   # (start, end, block | window) of the first-layer aggregation, when timed
         self._loss_host = None
         self.sample_events = []   # (start, end, n_batches) of the fused sampling launches, when timed
@@ -231,9 +251,38 @@ class Trainer:
         self.window_layer0 = bool(window_layer0) and self.sage
         self._layer0_buf = None
 
+    def grad_sync_kind(self) -> str:
+        if self.world == 1:
+            return "none (one rank)"
+        return "one-launch peer-store exchange fused with Adam" if self.oneshot else "NCCL all-reduce between two graphs"
+
+    def _peer_sync(self):
+        """Collective over the default group: allocate this rank's receive buffer and flags, map the peers'."""
+        if self._peers is None:
+            from .sharding import open_peer_tensors
+            n = self.grads.buffer.numel()
+            n_recv, n_flags = fastgl.PeerSync.sizes(n, self.world)
+            recv = torch.zeros(n_recv, dtype=torch.float32, device=self.dev)
+            flags = torch.zeros(n_flags, dtype=torch.int32, device=self.dev)
+            torch.cuda.synchronize(self.dev)
+            self._peers = fastgl.PeerSync(self.rank, self.world, open_peer_tensors(recv), open_peer_tensors(flags), n)
+        return self._peers
+
+    def release_peers(self):
+        """Drop the mappings of the peers' buffers (before any rank frees its own)."""
+        if isinstance(getattr(self, "opt", None), FlatAdam):
+            self.opt.peers = None
+        self._peers = None
+        self.graphed = None
+
+    def _sync_and_step(self):
+        if not self.oneshot:
+            self.grads.all_reduce(self.world)
+        self.opt.step()
+
     def reset_optimizer(self):
         if self.sage:
-            self.opt = FlatAdam(self.grads, self.lr, self.weight_decay)
+            self.opt = FlatAdam(self.grads, self.lr, self.weight_decay, peers=self._peer_sync() if self.oneshot else None)
         else:
             self.opt = torch.optim.Adam(self.model.parameters(), lr=self.lr, weight_decay=self.weight_decay, fused=True)
 
@@ -385,8 +434,7 @@ class Trainer:
         loss = F.cross_entropy(logits, y)
         self.grads.zero()
         loss.backward()
-        self.grads.all_reduce(self.world)
-        self.opt.step()
+        self._sync_and_step()
         self.sampled_edges += sum(blk.num_edges() for blk in blocks)
         self.last_loss = loss
         return loss
@@ -415,6 +463,10 @@ class Trainer:
             if self.time_layer0:
                 end.record()
                 self.sample_events.append((start, end, nb))
+            if self.matcher is not None:
+                # Match-Reorder's overlap matrix is computed on the device right behind the sampler and rides along
+                # with the counts read-back, so ordering the window costs the host no extra synchronisation
+                self.matcher.enqueue(fb.nodes, fb.counts[:, len(self.fanouts)], key=slot)
             fb.start_readback()
             return fb
 
@@ -471,7 +523,8 @@ class Trainer:
             layer0 = self.aggregate_window_layer0(fb) if self.window_layer0 else None
             order = list(range(nb))
             if self.matcher is not None:
-                order = self.matcher.reorder([fb.input_nodes(b) for b in range(nb)])
+                order = self.matcher.order(fb.counts_host()[:, len(self.fanouts)].tolist(), key=slot)
+            self.last_order = order
             for i, b in enumerate(order):
                 if i == max(0, nb - 2) and done + nb < n_steps:
                     nxt = sample_next(done + nb)

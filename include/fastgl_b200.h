@@ -331,6 +331,38 @@ int fgl_linear_softmax_xent(fgl_ws* ws, const float* x, int64_t ldx, int32_t k, 
 int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, float lr, float beta1,
                   float beta2, float eps, float weight_decay, int32_t* step_dev, void* stream);
 
+/* ---- Data-parallel gradient exchange -----------------------------------------------------------------------
+ * The reference trains its replicas without synchronising gradients at all (train_fastgl.py:204-212,404-405);
+ * a data-parallel run that is to converge like a single-GPU run needs the average of the ranks' gradients before
+ * the optimizer step.  fgl_allreduce_adam does both in ONE launch per step, without a library collective: every
+ * rank pushes its flat gradient into the receive buffers of the other ranks with plain peer stores over
+ * NVLink, raises a flag per 8 KB chunk, waits (bounded) for the other ranks' flags, adds the contributions in rank
+ * order (identical on every rank, so the replicas stay bit-identical), scales by 1 / world, writes the average
+ * back to grad and applies fgl_adam_step's arithmetic to param / exp_avg / exp_avg_sq.
+ *
+ * peers describes the buffers as they are mapped into THIS process (CUDA IPC or any other peer mapping):
+ * recv[q] is rank q's receive buffer, float[2][world][n_pad], and flags[q] rank q's flag array,
+ * uint32[2][world][n_chunks], both zero before the first call; n_chunks = fgl_peer_sync_chunks(n) and
+ * n_pad >= n_chunks * 2048.  step_dev is three int32 words, zero before the first step: [0] completed optimizer
+ * steps, [1] scratch, [2] completed exchanges; the launch advances them itself, so it can be captured in a CUDA
+ * graph and replayed.  Every rank must issue the same sequence of calls.  With world = 1 nothing is exchanged.
+ * A wait gives up after spin_limit polls (about a microsecond each): the chunk's parameters are then left as they
+ * were and FGL_ERR_TIMEOUT is recorded in the workspace's status word.  n is a multiple of 4, buffers 16-byte
+ * aligned. */
+#define FGL_MAX_PEERS 8
+typedef struct fgl_peer_sync {
+    int32_t rank, world;
+    float* recv[FGL_MAX_PEERS];
+    uint32_t* flags[FGL_MAX_PEERS];
+    int64_t n_pad;
+    int32_t n_chunks;
+} fgl_peer_sync;
+int fgl_sizeof_peer_sync(void);
+int64_t fgl_peer_sync_chunks(int64_t n);
+int fgl_allreduce_adam(fgl_ws* ws, const fgl_peer_sync* peers, float* param, float* grad, float* exp_avg,
+                       float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                       int32_t* step_dev, int64_t spin_limit, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -91,9 +91,10 @@ def test_sharded_feature_table_over_two_gpus():
 
 
 def _train_worker(rank, world, port):
-    """Two data-parallel ranks over NCCL: the step replayed from CUDA graphs (forward/backward, then the all-reduce,
-    then the optimizer step) must train like the op-by-op step, across an epoch boundary with its short last
-    batch, and keep the replicas identical."""
+    """Two data-parallel ranks.  The step replayed from CUDA graphs must train like the op-by-op step, across an epoch
+    boundary with its short last batch, and keep the replicas identical -- with the NCCL all-reduce between two
+    graphs, and with the one-launch exchange (peer stores + flags, fused with Adam) that makes the step one graph.
+    With two ranks both average a + b the same way, so the two kinds of exchange must agree bit for bit."""
     from conftest import make_graph
     from fastgl_b200.layers import GraphSAGE
     from fastgl_b200.trainer import Trainer
@@ -106,34 +107,53 @@ def _train_worker(rank, world, port):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=180))
     host_group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=400))
     err = None
+    held = {}
+
+    def release():
+        for tr in held.values():
+            tr.release_peers()
+        held.clear()
+
     try:
+        import fastgl
         n = 6000
         indptr, indices = make_graph(n, 14, seed=9, hub=400)
         rng = np.random.default_rng(9)
         feat = torch.from_numpy(rng.standard_normal((n, 100)).astype(np.float32)).to(dev)
         labels = torch.from_numpy(rng.integers(0, 7, n)).to(dev)
         train = torch.from_numpy(np.sort(rng.choice(n, size=n // 2, replace=False)).astype(np.int32)).to(dev)
-        runs = []
-        for graph in (False, True):
+        runs = {}
+        for name, graph, sync in (("eager-nccl", False, "nccl"), ("graph-nccl", True, "nccl"), ("eager-oneshot", False, "oneshot"),
+                                  ("graph-oneshot", True, "oneshot")):
             torch.manual_seed(3)
             model = GraphSAGE(100, 32, 7, 3, dropout=0.0).to(dev)
-            tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), feat, labels, train, model,
-                         [15, 10, 5], batch_size=256, window=4, cuda_graph=graph, rank=rank, world=world)
+            tr = held[name] = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), feat, labels, train,
+                                      model, [15, 10, 5], batch_size=256, window=4, cuda_graph=graph, rank=rank, world=world,
+                                      grad_sync=sync)
             assert tr.steps_per_epoch() == 6                  # 1500 seeds per rank: five full batches and one of 220
+            assert tr.oneshot == (sync == "oneshot")
             losses = tr.run_steps(14, read_loss_each_step=True)
-            runs.append((losses, [p.detach().clone() for p in model.parameters()], tr))
-        (le, pe, _), (lg, pg, tg) = runs
-        assert tg.graphed is not None and tg.graphed.opt_graph is not None and tg.graph_fallbacks <= 2
-        assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
-        for a, b in zip(pe, pg):
-            assert torch.allclose(a, b, rtol=1e-3, atol=1e-4)
-        flat = torch.cat([p.flatten() for p in pg])
-        both = [torch.empty_like(flat) for _ in range(world)]
-        dist.all_gather(both, flat)
-        assert torch.equal(both[0], both[1])                  # the replicas stay bit-identical
+            fastgl.check_status(dev)
+            runs[name] = (losses, [p.detach().clone() for p in model.parameters()], tr)
+        le, pe, _ = runs["eager-nccl"]
+        for name in ("graph-nccl", "eager-oneshot", "graph-oneshot"):
+            lg, pg, tg = runs[name]
+            if name.startswith("graph"):
+                assert tg.graphed is not None and tg.graph_fallbacks <= 2
+                assert (tg.graphed.opt_graph is None) == name.endswith("oneshot")   # one graph per step with the exchange inside
+            assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (name, le, lg)
+            for a, b in zip(pe, pg):
+                assert torch.allclose(a, b, rtol=1e-3, atol=1e-4), name
+            flat = torch.cat([p.flatten() for p in pg])
+            both = [torch.empty_like(flat) for _ in range(world)]
+            dist.all_gather(both, flat)
+            assert torch.equal(both[0], both[1]), name        # the replicas stay bit-identical
+        # same arithmetic, same order: the exchange kernel and NCCL's average agree exactly on two ranks
+        for a, b in zip(runs["eager-nccl"][1], runs["eager-oneshot"][1]):
+            assert torch.equal(a, b)
     except BaseException as e:                                # noqa: BLE001 -- re-raised by _leave_together
         err = e
-    _leave_together(err, host_group)
+    _leave_together(err, host_group, release=release)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

@@ -259,3 +259,159 @@ def test_gat_layer_matches_a_dense_torch_restatement():
     assert torch.allclose(out.double().cpu(), ref.detach(), rtol=1e-4, atol=1e-5)
     for got, want in ((layer.fc.weight.grad, W.grad), (layer.attn_l.grad, al.grad), (layer.attn_r.grad, ar.grad)):
         assert torch.allclose(got.double().cpu(), want, rtol=1e-3, atol=1e-4)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the reference's own model stacks (GCN, GIN) through the trainer, against float64 models on oracle-sampled blocks
+# ----------------------------------------------------------------------------------------------------------------
+def _oracle_epoch_losses(problem, fanouts, batch, n_steps, params, forward):
+    """Losses of ``n_steps`` Adam steps of a float64 CPU model on the blocks the oracle samples for the trainer's own
+    seed order and Philox counters.  ``forward(blocks, inputs, f64_features, params)`` returns the logits."""
+    from fastgl_b200.trainer import shard_seeds
+    indptr, indices, feat, labels, train = problem
+    opt = torch.optim.Adam(params, lr=0.01, weight_decay=5e-4)
+    seeds_all = shard_seeds(torch.from_numpy(train), 0, 1, 12345).numpy()
+    f64 = torch.from_numpy(feat).double()
+    losses = []
+    for step in range(n_steps):
+        seeds = seeds_all[step * batch:(step + 1) * batch]
+        inputs, _, blocks = oc.sample_blocks(indptr, indices, seeds, list(fanouts), False, rng_seed=12345, rng_ctr=8 * step)
+        logits = forward(blocks, inputs, f64, params)
+        loss = torch.nn.functional.cross_entropy(logits, torch.from_numpy(labels[seeds.astype(np.int64)]))
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    return losses
+
+
+def _f64_block_sum(blk, h, weights=None):
+    """sum over in-edges of (weights *) h[src]; rows without in-edges copy their own row (aggregate_acc_kernel.cu:307,405)."""
+    deg = np.diff(blk["indptr"])
+    dst = torch.from_numpy(np.repeat(np.arange(blk["n_dst"]), deg))
+    src = torch.from_numpy(blk["src_local"].astype(np.int64))
+    rows = h[src] if weights is None else h[src] * weights[:, None]
+    out = torch.zeros((blk["n_dst"], h.shape[1]), dtype=torch.float64).index_add_(0, dst, rows)
+    lonely = torch.from_numpy(deg == 0)
+    return torch.where(lonely[:, None], h[: blk["n_dst"]], out)
+
+
+def _gcn_forward(blocks, inputs, f64, params):
+    h = f64[torch.from_numpy(inputs.astype(np.int64))]
+    for blk, w in zip(blocks, params):
+        deg = np.diff(blk["indptr"])
+        ddeg = np.maximum(deg, 1).astype(np.float64)                                         # GraphConv.py:97
+        sdeg = np.maximum(np.bincount(blk["src_local"], minlength=blk["n_src"]), 1).astype(np.float64)   # GraphConv.py:96
+        dst = np.repeat(np.arange(blk["n_dst"]), deg)
+        wgt = torch.from_numpy(1.0 / (np.sqrt(ddeg[dst]) * np.sqrt(sdeg[blk["src_local"]])))
+        h = _f64_block_sum(blk, h @ w, wgt)                                                  # update, then aggregate
+    return h
+
+
+def _gin_forward(blocks, inputs, f64, params):
+    h = f64[torch.from_numpy(inputs.astype(np.int64))]
+    for blk, w in zip(blocks, params):
+        h = _f64_block_sum(blk, h) @ w                                                       # aggregate, then update
+    return h
+
+
+@pytest.mark.parametrize("kind", ["gcn", "gcn-gathered", "gin"])
+def test_gcn_and_gin_stacks_through_the_trainer_track_the_float64_model(kind):
+    """The dense-graph configuration scaled down: 602-d rows, fanout [25, 10], two layers, batch 256.  The GCN first
+    layer reads the feature table in place (``gcn``) or the gathered rows as the reference does (``gcn-gathered``)."""
+    from fastgl_b200.layers import GCN, GIN
+    from fastgl_b200.trainer import Trainer
+    problem = setup_problem(n=5000, feat_dim=602, classes=7, seed=23)
+    indptr, indices, feat, labels, train = problem
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    model = (GIN if kind == "gin" else GCN)(602, 48, 7, 2, dropout=0.0).to(dev)
+    tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), torch.from_numpy(feat).to(dev),
+                 torch.from_numpy(labels).to(dev), torch.from_numpy(train).to(dev), model, [25, 10], batch_size=256, window=4,
+                 table_direct=(kind == "gcn"))
+    params = [p.detach().double().cpu().clone().requires_grad_(True) for p in model.parameters()]
+    gpu = tr.run_steps(6, read_loss_each_step=True)
+    import fastgl
+    fastgl.check_status(dev)
+    cpu = _oracle_epoch_losses(problem, (25, 10), 256, 6, params, _gin_forward if kind == "gin" else _gcn_forward)
+    assert np.allclose(gpu, cpu, rtol=2e-3, atol=2e-3), (gpu, cpu)
+    assert gpu[-1] < gpu[0]
+
+
+def test_one_epoch_of_the_cpu_runnable_configuration_tracks_the_float64_model():
+    """The smallest benchmark configuration at full size: seeded R-MAT graph, 100 k nodes of average degree 20, 128-d
+    N(0,1) rows, 10 classes, 10 % training seeds, 3-layer GraphSAGE-mean (hidden 256), fanout [15, 10, 5], batch 1024:
+    the ten mini-batches of one epoch (the last one short), through the windowed, graph-replayed trainer, against a
+    float64 CPU model stepping on the blocks the oracle samples."""
+    from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+    dev = torch.device("cuda", 0)
+    indptr, indices = rmat_graph(100_000, 20.0, seed=12345, device=dev)
+    feat, labels, train = synthetic_node_data(100_000, 128, 10, 0.10, seed=12345, device=dev)
+    torch.manual_seed(12345)
+    model = GraphSAGE(128, 256, 10, 3, dropout=0.0).to(dev)
+    tr = Trainer(indptr, indices, feat, labels, train, model, [15, 10, 5], batch_size=1024, window=8, cuda_graph=True)
+    assert tr.steps_per_epoch() == 10
+    params = [p.detach().double().cpu().clone().requires_grad_(True) for p in model.parameters()]
+    tr.prime()
+    gpu = tr.run_steps(10, read_loss_each_step=True)
+    import fastgl
+    fastgl.check_status(dev)
+    assert tr.epoch == 0 and tr.graph_fallbacks <= 1
+    problem = (indptr.cpu().numpy(), indices.cpu().numpy(), feat.cpu().numpy(), labels.cpu().numpy(), train.cpu().numpy())
+
+    def sage_forward(blocks, inputs, f64, ps):
+        h = f64[torch.from_numpy(inputs.astype(np.int64))]
+        for i, blk in enumerate(blocks):
+            w, bias = ps[2 * i], ps[2 * i + 1]
+            deg = np.diff(blk["indptr"])
+            dst = torch.from_numpy(np.repeat(np.arange(blk["n_dst"]), deg))
+            agg = torch.zeros((blk["n_dst"], h.shape[1]), dtype=torch.float64)
+            agg.index_add_(0, dst, h[torch.from_numpy(blk["src_local"].astype(np.int64))])
+            agg = agg / torch.from_numpy(np.maximum(deg, 1)).double().unsqueeze(1)
+            h = torch.cat([h[: blk["n_dst"]], agg], 1) @ w + bias
+            if i != len(blocks) - 1:
+                h = torch.relu(h)
+        return h
+
+    cpu = _oracle_epoch_losses(problem, (15, 10, 5), 1024, 10, params, sage_forward)
+    assert np.allclose(gpu, cpu, rtol=2e-3, atol=2e-3), (gpu, cpu)
+    assert gpu[-1] < gpu[0]
+
+
+def test_a_label_out_of_range_stops_the_run_instead_of_being_resampled_away():
+    """A bad label is recorded by the loss kernel (FGL_ERR_BOUNDS).  The trainer sees the status word with the next
+    window's read-back; it must raise, not treat the code as a hashtable overflow, drop the cap and carry on."""
+    import fastgl
+    problem = setup_problem(seed=31)
+    indptr, indices, feat, labels, train = problem
+    labels = labels.copy()
+    labels[train] = 7000                                  # every training label is out of range (7 classes)
+    tr = make_trainer((indptr, indices, feat, labels, train), cuda_graph=True)
+    with pytest.raises(RuntimeError, match="out of range"):
+        tr.run_steps(12, read_loss_each_step=False)        # three windows of four: the second read-back sees the word
+        fastgl.check_status(torch.device("cuda", 0))
+    assert tr.table_overflows == 0
+
+
+def test_match_reorder_trains_the_same_batches_in_another_order():
+    """Match-Reorder (utilis.py:31-62) only permutes the mini-batches of a window: over whole windows the sampled
+    edges are those of the plain order, and training still converges."""
+    problem = setup_problem(seed=33)
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+    indptr, indices, feat, labels, train = problem
+    dev = torch.device("cuda", 0)
+    runs = []
+    for reorder in (False, True):
+        torch.manual_seed(3)
+        model = GraphSAGE(feat.shape[1], 32, 7, 3, dropout=0.0).to(dev)
+        tr = Trainer(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), torch.from_numpy(feat).to(dev),
+                     torch.from_numpy(labels).to(dev), torch.from_numpy(train).to(dev), model, [15, 10, 5], batch_size=256,
+                     window=4, cuda_graph=True, reorder=reorder)
+        losses = tr.run_steps(8, read_loss_each_step=True)
+        runs.append((losses, tr.sampled_edges, tr))
+    assert runs[0][1] == runs[1][1]
+    assert sorted(runs[1][2].last_order) == [0, 1, 2, 3]
+    assert all(np.isfinite(runs[1][0])) and runs[1][0][-1] < runs[1][0][0] + 0.1

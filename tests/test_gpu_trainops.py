@@ -199,3 +199,64 @@ def test_self_gradient_rows_beyond_the_device_side_row_count_are_ignored(fastgl)
                                      dcat[:n_real, dim:].contiguous(), n_src)
     want[:n_real] += dcat[:n_real, :dim]
     assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+
+
+def _flat_problem(n, seed):
+    g = torch.Generator(device=DEV)
+    g.manual_seed(seed)
+    p = torch.randn(n, device=DEV, generator=g)
+    return p, torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+
+
+def test_allreduce_adam_with_one_rank_is_the_plain_adam_step(fastgl):
+    n = 10_240 + 4
+    p1, m1, v1 = _flat_problem(n, 1)
+    p2, m2, v2 = p1.clone(), m1.clone(), v1.clone()
+    s1, s2 = torch.zeros(2, dtype=torch.int32, device=DEV), torch.zeros(3, dtype=torch.int32, device=DEV)
+    n_recv, n_flags = fastgl.PeerSync.sizes(n, 1)
+    peers = fastgl.PeerSync(0, 1, [torch.zeros(n_recv, device=DEV)], [torch.zeros(n_flags, dtype=torch.int32, device=DEV)], n)
+    for step in range(3):
+        g = torch.randn(n, device=DEV)
+        g2 = g.clone()
+        fastgl.adam_step_(p1, g, m1, v1, s1, lr=0.01, weight_decay=5e-4)
+        fastgl.allreduce_adam_(peers, p2, g2, m2, v2, s2, lr=0.01, weight_decay=5e-4)
+        assert torch.equal(g2, g)                                   # the average over one rank
+    assert torch.equal(p1, p2) and torch.equal(m1, m2) and torch.equal(v1, v2)
+    assert s2.tolist() == [3, 0, 3]
+
+
+def test_allreduce_adam_reduces_a_delivered_contribution_and_times_out_on_a_missing_one(fastgl):
+    """Rank 0 of two, on one GPU: the second rank's contribution is placed in rank 0's receive buffer by hand and its
+    flags are raised before the launch (no kernel waits for another kernel here), for two steps in a row (both
+    halves of the double buffer).  Then a step whose flags nobody raises: the bounded wait gives up, the status word
+    says so, and the parameters stay as they were."""
+    n = 3 * 2048 + 8
+    p, m, v = _flat_problem(n, 2)
+    ref_p, ref_m, ref_v = p.clone(), m.clone(), v.clone()
+    step, ref_step = torch.zeros(3, dtype=torch.int32, device=DEV), torch.zeros(2, dtype=torch.int32, device=DEV)
+    n_recv, n_flags = fastgl.PeerSync.sizes(n, 2)
+    mine_recv, mine_flags = torch.zeros(n_recv, device=DEV), torch.zeros(n_flags, dtype=torch.int32, device=DEV)
+    peer_recv, peer_flags = torch.zeros(n_recv, device=DEV), torch.zeros(n_flags, dtype=torch.int32, device=DEV)
+    peers = fastgl.PeerSync(0, 2, [mine_recv, peer_recv], [mine_flags, peer_flags], n)
+    n_pad, n_chunks = peers.n_pad, peers.n_chunks
+    for e in (1, 2):
+        g0, g1 = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+        parity = e & 1
+        mine_recv.view(2, 2, n_pad)[parity, 1, :n] = g1             # what rank 1's launch would have pushed
+        mine_flags.view(2, 2, n_chunks)[parity, 1, :] = e
+        avg = (g0 + g1) * 0.5
+        g = g0.clone()
+        fastgl.allreduce_adam_(peers, p, g, m, v, step, lr=0.01, weight_decay=5e-4)
+        fastgl.adam_step_(ref_p, avg.clone(), ref_m, ref_v, ref_step, lr=0.01, weight_decay=5e-4)
+        fastgl.check_status(DEV)
+        assert torch.equal(g, avg) and torch.equal(p, ref_p) and torch.equal(m, ref_m)
+        # this rank's own push: its gradient and its flags arrived in the "peer's" buffers
+        assert torch.equal(peer_recv.view(2, 2, n_pad)[parity, 0, :n], g0)
+        assert bool((peer_flags.view(2, 2, n_chunks)[parity, 0] == e).all())
+    before = p.clone()
+    g = torch.randn(n, device=DEV)
+    fastgl.allreduce_adam_(peers, p, g, m, v, step, lr=0.01, weight_decay=5e-4, spin_limit=2000)
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        fastgl.check_status(DEV)
+    assert torch.equal(p, before)
+    fastgl.check_status(DEV)

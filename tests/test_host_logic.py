@@ -40,6 +40,19 @@ def test_build_csr_keeps_edge_order_within_a_destination():
     assert indptr.tolist() == [0, 2, 3, 5] and indices.tolist() == [1, 2, 9, 5, 7]
 
 
+def test_relabel_by_degree_is_an_isomorphism_with_hubs_first():
+    from fastgl_b200.graphgen import relabel_by_degree, rmat_graph
+    indptr, indices = rmat_graph(3000, 9.0, seed=3, device="cpu")
+    p2, i2, order, new_of_old = relabel_by_degree(indptr, indices, chunk_edges=1000)
+    deg2 = p2[1:] - p2[:-1]
+    assert bool((deg2[:-1] >= deg2[1:]).all()) and int(p2[-1]) == int(indptr[-1])
+    assert torch.equal(new_of_old[order], torch.arange(3000))
+    for v in (0, 1, 17, 1500, 2999):                      # the same neighbours, renamed, in the same order
+        old = order[v]
+        want = new_of_old[indices[indptr[old]: indptr[old + 1]].long()]
+        assert torch.equal(i2[p2[v]: p2[v + 1]].long(), want)
+
+
 def test_synthetic_node_data_shapes():
     feat, labels, train = synthetic_node_data(1000, 16, 7, 0.1, seed=1)
     assert feat.shape == (1000, 16) and feat.dtype == torch.float32
@@ -68,6 +81,25 @@ def test_overlap_matrix_and_greedy_order():
     # batches without any overlap are still all scheduled exactly once
     disjoint = [torch.tensor([i]) for i in range(5)]
     assert sorted(MatchReorder(8).reorder(disjoint)) == [0, 1, 2, 3, 4]
+
+
+def test_overlap_of_padded_device_style_node_lists_equals_the_list_version():
+    from fastgl_b200.scheduler import MatchReorder, overlap_matrix, overlap_matrix_padded
+    rng = np.random.default_rng(8)
+    n, W, stride = 5000, 6, 900
+    counts = rng.integers(100, stride, size=W)
+    nodes = rng.integers(0, n, size=(W, stride)).astype(np.int32)         # stale entries everywhere ...
+    lists = []
+    for b in range(W):
+        ids = rng.choice(n, size=counts[b], replace=False).astype(np.int32)
+        nodes[b, : counts[b]] = ids                                          # ... except the first counts[b]
+        lists.append(torch.from_numpy(ids))
+    want = overlap_matrix(lists, n, chunk=1024)
+    got = overlap_matrix_padded(torch.from_numpy(nodes), torch.from_numpy(counts), n, chunk=1500)
+    assert torch.equal(got, want)
+    m = MatchReorder(n)
+    m._pinned = {(0, W): got}
+    assert m.order(counts.tolist()) == m.reorder(lists)
 
 
 def test_block_edges_view_matches_the_csr():
