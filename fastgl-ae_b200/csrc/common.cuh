@@ -140,6 +140,31 @@ __device__ __forceinline__ int block_sum(int v, int* smem) {
     return res;
 }
 
+// One Adam update with L2 weight decay (torch.optim.Adam's arithmetic), spelled with explicit roundings so that
+// every kernel that applies it -- the plain optimizer launch and the one fused with the gradient exchange -- rounds
+// the same way, whatever the compiler would contract around it.
+struct AdamCoef {
+    float b1, b2, eps, wd, step_size, c2;
+};
+
+__device__ __forceinline__ AdamCoef adam_coef(float lr, float b1, float b2, float eps, float wd, int t) {
+    AdamCoef c;
+    c.b1 = b1;
+    c.b2 = b2;
+    c.eps = eps;
+    c.wd = wd;
+    c.step_size = __fdiv_rn(lr, __fsub_rn(1.f, powf(b1, (float)t)));
+    c.c2 = __fsqrt_rn(__fsub_rn(1.f, powf(b2, (float)t)));
+    return c;
+}
+
+__device__ __forceinline__ void adam_update(const AdamCoef& c, float& p, float g, float& m, float& v) {
+    const float grad = __fmaf_rn(c.wd, p, g);
+    m = __fmaf_rn(c.b1, m, __fmul_rn(__fsub_rn(1.f, c.b1), grad));
+    v = __fmaf_rn(c.b2, v, __fmul_rn(__fmul_rn(__fsub_rn(1.f, c.b2), grad), grad));
+    p = __fsub_rn(p, __fdiv_rn(__fmul_rn(c.step_size, m), __fadd_rn(__fdiv_rn(__fsqrt_rn(v), c.c2), c.eps)));
+}
+
 constexpr long long kSpinLimit = 20LL * 1000 * 1000;  // x ~50 ns: a second or so, then give up
 
 // ----------------------------------------------------------------------------------------------

@@ -76,8 +76,8 @@ __global__ void __launch_bounds__(kSyncThreads) allreduce_adam_kernel(const __gr
     }
 
     // (2) + (3) per chunk: wait for the peers' contributions, reduce in rank order, Adam
-    const float c1 = 1.f - powf(p.b1, (float)t), c2 = sqrtf(1.f - powf(p.b2, (float)t));
-    const float step_size = p.lr / c1, inv_world = 1.f / (float)p.world;
+    const AdamCoef coef = adam_coef(p.lr, p.b1, p.b2, p.eps, p.wd, t);
+    const float inv_world = 1.f / (float)p.world;
     const float* mine = p.recv[p.rank];
     for (int c = blockIdx.x; c < p.n_chunks; c += gridDim.x) {
         if (threadIdx.x == 0) s_fail = 0;
@@ -119,16 +119,10 @@ __global__ void __launch_bounds__(kSyncThreads) allreduce_adam_kernel(const __gr
             *reinterpret_cast<float4*>(p.grad + i) = g;
             float4 pp = *reinterpret_cast<float4*>(p.param + i);
             float4 mm = *reinterpret_cast<float4*>(p.m + i), vv = *reinterpret_cast<float4*>(p.v + i);
-#define FGL_ADAM1(P, G, M, V)                                 \
-    {                                                         \
-        const float grad = G + p.wd * P;                      \
-        M = p.b1 * M + (1.f - p.b1) * grad;                   \
-        V = p.b2 * V + (1.f - p.b2) * grad * grad;            \
-        P -= step_size * M / (sqrtf(V) / c2 + p.eps);         \
-    }
-            FGL_ADAM1(pp.x, g.x, mm.x, vv.x) FGL_ADAM1(pp.y, g.y, mm.y, vv.y)
-            FGL_ADAM1(pp.z, g.z, mm.z, vv.z) FGL_ADAM1(pp.w, g.w, mm.w, vv.w)
-#undef FGL_ADAM1
+            adam_update(coef, pp.x, g.x, mm.x, vv.x);
+            adam_update(coef, pp.y, g.y, mm.y, vv.y);
+            adam_update(coef, pp.z, g.z, mm.z, vv.z);
+            adam_update(coef, pp.w, g.w, mm.w, vv.w);
             *reinterpret_cast<float4*>(p.param + i) = pp;
             *reinterpret_cast<float4*>(p.m + i) = mm;
             *reinterpret_cast<float4*>(p.v + i) = vv;

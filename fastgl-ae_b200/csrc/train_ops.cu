@@ -308,32 +308,25 @@ __global__ void __launch_bounds__(kEwThreads)
 adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, int64_t n,
             float lr, float b1, float b2, float eps, float wd, int32_t* __restrict__ step, unsigned int* __restrict__ ticket) {
     const int t = *(volatile int32_t*)step + 1;
-    const float c1 = 1.f - powf(b1, (float)t), c2 = sqrtf(1.f - powf(b2, (float)t));
-    const float step_size = lr / c1;
+    const AdamCoef c = adam_coef(lr, b1, b2, eps, wd, t);
     for (int64_t i = ((int64_t)blockIdx.x * kEwThreads + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * kEwThreads * 4) {
         if (i + 4 <= n) {
             float4 pp = *reinterpret_cast<float4*>(p + i), gg = *reinterpret_cast<const float4*>(g + i);
             float4 mm = *reinterpret_cast<float4*>(m + i), vv = *reinterpret_cast<float4*>(v + i);
-#define FGL_ADAM1(P, G, M, V)                                   \
-    {                                                           \
-        const float grad = G + wd * P;                          \
-        M = b1 * M + (1.f - b1) * grad;                         \
-        V = b2 * V + (1.f - b2) * grad * grad;                  \
-        P -= step_size * M / (sqrtf(V) / c2 + eps);             \
-    }
-            FGL_ADAM1(pp.x, gg.x, mm.x, vv.x) FGL_ADAM1(pp.y, gg.y, mm.y, vv.y)
-            FGL_ADAM1(pp.z, gg.z, mm.z, vv.z) FGL_ADAM1(pp.w, gg.w, mm.w, vv.w)
+            adam_update(c, pp.x, gg.x, mm.x, vv.x);
+            adam_update(c, pp.y, gg.y, mm.y, vv.y);
+            adam_update(c, pp.z, gg.z, mm.z, vv.z);
+            adam_update(c, pp.w, gg.w, mm.w, vv.w);
             *reinterpret_cast<float4*>(p + i) = pp;
             *reinterpret_cast<float4*>(m + i) = mm;
             *reinterpret_cast<float4*>(v + i) = vv;
         } else {
             for (int64_t j = i; j < n; ++j) {
                 float pj = p[j], mj = m[j], vj = v[j];
-                FGL_ADAM1(pj, g[j], mj, vj)
+                adam_update(c, pj, g[j], mj, vj);
                 p[j] = pj; m[j] = mj; v[j] = vj;
             }
         }
-#undef FGL_ADAM1
     }
     __syncthreads();
     if (threadIdx.x == 0) {
