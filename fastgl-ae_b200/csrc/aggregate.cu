@@ -21,13 +21,16 @@
 
 namespace fgl {
 
-constexpr int kAggThreads = 256;
+#ifndef FGL_AGG_THREADS
+#define FGL_AGG_THREADS 256
+#endif
+constexpr int kAggThreads = FGL_AGG_THREADS;
 constexpr int kAggWarps = kAggThreads / 32;
 #ifndef FGL_AGG_UNR1
 #define FGL_AGG_UNR1 8  // neighbour rows in flight per lane for rows of up to 32 vectors
 #endif
 #ifndef FGL_AGG_MIN_CTAS
-#define FGL_AGG_MIN_CTAS 3
+#define FGL_AGG_MIN_CTAS 2
 #endif
 
 template <int VEC>
@@ -131,89 +134,177 @@ __device__ __forceinline__ const float* x_row(const AggParams& p, int64_t r) {
 // flight before their FMAs.  In window mode (out_row_off != NULL) the rows of all mini-batches form one
 // sequence in batch-major order and the grid sweeps it front to back, so that at any moment the CTAs work
 // on one or two mini-batches and the rows those batches re-read stay in L2.
+//
+// A warp issues its instructions in order, so a value that was just requested from memory stalls the warp at its
+// first use.  The ids of a row form a dependent chain -- indptr[d] -> src[a + lane] -> row_map[s] -> the feature
+// rows -- and walked one row at a time that chain is four round trips per destination row, more than the row data
+// itself costs.  The chain is therefore software-pipelined over the warp's rows: while row i is summed, the map
+// entries of row i+1, the source ids of row i+2 and the offsets of row i+3 are in flight, and every loaded value is
+// first touched one iteration after it was requested.  The row's own input row (the "self" copy) is requested
+// together with the first batch of neighbour rows, not before it.
+constexpr int kAggMaxWindow = 512;  // mini-batches per window launch (their row offsets are staged in shared memory)
+
 template <int VEC, int MODE, bool HAS_MAP, int NACC, int UNR>
 __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(const AggParams p) {
     using V = Vec<VEC>;
     using T = typename V::T;
+    __shared__ long long s_off[kAggMaxWindow + 1];
     const int lane = threadIdx.x & 31;
     const int warp_global = blockIdx.x * kAggWarps + (threadIdx.x >> 5);
     const int n_warps = gridDim.x * kAggWarps;
     const int chunks = p.dim / VEC;  // dim % VEC == 0 by dispatch
     const bool window = p.out_row_off != nullptr;
-    const int64_t padded = window ? __ldg(p.out_row_off + p.n_batches) : (int64_t)p.n_dst;
+    if (window) {
+        for (int i = threadIdx.x; i <= p.n_batches; i += blockDim.x) s_off[i] = __ldg(p.out_row_off + i);
+        __syncthreads();
+    }
+    const int64_t padded = window ? s_off[p.n_batches] : (int64_t)p.n_dst;
     const int64_t total = p.n_dst_dev ? min((int64_t)max(__ldg(p.n_dst_dev), 0), padded) : padded;
     // padding rows of a launch sized for more rows than the block has: zero them
     for (int64_t g = total + warp_global; g < padded; g += n_warps) {
         T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
         for (int c = lane; c < chunks; c += 32) orow[c] = V::zero();
     }
+    const bool want_self = p.self_out != nullptr || p.passthrough != 0;
 
-    // State of the row after the current one.  Its ids are fetched one row ahead so that the dependent chain
-    // indptr -> src -> row_map is off the critical path.
-    int b_n = 0, d_n = 0, a_n = 0, e_n = 0;
-    int64_t lo_n = 0, hi_n = window ? __ldg(p.out_row_off + 1) : total;
-    int64_t row_n = 0, self_n = 0;
-    float w_n = 1.0f;
-    unsigned bad_n = 0;  // neighbours (of the first 32) whose id is out of range: loaded from row 0, never added
-    auto prefetch = [&](int64_t g) {
-        a_n = 0;
-        e_n = 0;
-        row_n = 0;
-        w_n = 1.0f;
-        bad_n = 0;
+    // ---- pipeline state: stage A (offsets), B (source ids), C (map entries / degrees) ------------------------------
+    int bA = 0, dA = 0, aA = 0, eA = 0;              // row i+3 after its stage A: batch, local row, edge range
+    int bB = 0, dB = 0, aB = 0, eB = 0, sB = -1;      // row i+2 after stage B: + this lane's source id
+    int selfB = -1;                                   //                         + the row's own input row (raw)
+    int ddegB = 1;
+    int bC = 0, dC = 0, aC = 0, eC = 0, sC = -1;      // row i+1 after stage C: + raw map entry / degree of the lane's source
+    int rowC = 0, selfC = -1;
+    int sdegC = 1, ddegC = 1;
+    int batch_ptr = 0;                                // window mode: batch of the row stage A looks at (monotonic)
+
+    auto stage_a = [&](int64_t g) {  // offsets of row g
+        aA = 0;
+        eA = 0;
         if (g >= total) return;
-        while (g >= hi_n) {  // window mode only: step to the mini-batch that holds row g
-            ++b_n;
-            lo_n = hi_n;
-            hi_n = __ldg(p.out_row_off + b_n + 1);
+        if (window) {
+            while (g >= s_off[batch_ptr + 1]) ++batch_ptr;
+            bA = batch_ptr;
+            dA = (int)(g - s_off[batch_ptr]);
+        } else {
+            bA = 0;
+            dA = (int)g;
         }
-        d_n = (int)(g - lo_n);
-        const int32_t* indptr = p.indptr + (int64_t)b_n * p.indptr_stride;
-        const int32_t* src = p.src + (int64_t)b_n * p.src_stride;
-        const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b_n * p.row_map_stride : nullptr;
-        a_n = __ldg(indptr + d_n);
-        e_n = __ldg(indptr + d_n + 1);
-        bool bad = false;
-        if (lane < e_n - a_n) {
-            const int s = __ldg(src + a_n + lane);
-            row_n = checked_row<HAS_MAP>(p, row_map, s);
-            bad = row_n < 0;
-            if (bad) row_n = 0;
-            if (MODE == FGL_AGG_SYMNORM && !bad) w_n = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
-        }
-        bad_n = __ballot_sync(0xffffffffu, bad);
-        // the row's own input row, only validated where it is used (self copy, zero-degree pass-through)
-        self_n = HAS_MAP ? ((int64_t)d_n < p.n_map ? (int64_t)__ldg(row_map + d_n) : -1) : (int64_t)d_n;
+        const int32_t* indptr = p.indptr + (int64_t)bA * p.indptr_stride;
+        aA = __ldg(indptr + dA);
+        eA = __ldg(indptr + dA + 1);
     };
-    prefetch(warp_global);
+    auto stage_b = [&]() {  // source ids of the row stage A saw one iteration ago (its offsets have arrived)
+        bB = bA;
+        dB = dA;
+        aB = aA;
+        eB = eA;
+        sB = -1;
+        selfB = -1;
+        if (lane < eB - aB) sB = __ldg(p.src + (int64_t)bB * p.src_stride + aB + lane);
+        if (want_self) {
+            if (HAS_MAP)
+                selfB = (int64_t)dB < p.n_map ? __ldg(p.row_map + (int64_t)bB * p.row_map_stride + dB) : -1;
+            else
+                selfB = dB;
+        }
+        if (MODE == FGL_AGG_SYMNORM && eB > aB) ddegB = __ldg(p.dst_deg + dB);
+    };
+    auto stage_c = [&]() {  // map entry and degree of this lane's source (the id has arrived)
+        bC = bB;
+        dC = dB;
+        aC = aB;
+        eC = eB;
+        sC = sB;
+        selfC = selfB;
+        ddegC = ddegB;
+        rowC = sB;
+        sdegC = 1;
+        const bool id_ok = sB >= 0 && (HAS_MAP ? (int64_t)sB < p.n_map : (int64_t)sB < p.n_rows);
+        if (id_ok) {
+            if (HAS_MAP) rowC = __ldg(p.row_map + (int64_t)bC * p.row_map_stride + sB);
+            if (MODE == FGL_AGG_SYMNORM) sdegC = __ldg(p.src_deg + sB);
+        } else {
+            rowC = -1;  // no such edge in this lane, or an id out of range (told apart when the row is summed)
+        }
+    };
+
+    // prologue: fill the pipeline (each stage waits for the one before it, once)
+    stage_a(warp_global);
+    stage_b();
+    stage_c();
+    stage_a(warp_global + (int64_t)n_warps);
+    stage_b();
+    stage_a(warp_global + 2 * (int64_t)n_warps);
 
     for (int64_t g = warp_global; g < total; g += n_warps) {
-        const int b = b_n, d = d_n, a = a_n, e_end = e_n;
-        const int64_t first_row = row_n;  // neighbours a .. a+31
-        int64_t self_row = self_n;        // the row's own source row
-        const float first_w = w_n;
-        const unsigned first_bad = bad_n;
-        if ((p.self_out || (a >= e_end && p.passthrough)) && (self_row < 0 || self_row >= p.n_rows)) {
+        // ---- the current row: everything below was requested at least one iteration ago ----------------------------
+        const int b = bC, a = aC, e_end = eC;
+        const int cnt_first = min(32, e_end - a);
+        const bool has_edge = lane < cnt_first;
+        bool bad = has_edge && (rowC < 0 || (int64_t)rowC >= p.n_rows);
+        if (bad) agg_bad_id(p);
+        const int first_row = (has_edge && !bad) ? rowC : 0;
+        const unsigned first_bad = __ballot_sync(0xffffffffu, bad);
+        float first_w = 1.0f;
+        if (MODE == FGL_AGG_SYMNORM && has_edge && !bad) first_w = 1.0f / sqrtf((float)sdegC);
+        int self_row = selfC;
+        const int ddeg = ddegC;
+        const bool need_self = p.self_out != nullptr || (a >= e_end && p.passthrough);
+        if (need_self && (self_row < 0 || (int64_t)self_row >= p.n_rows)) {
             agg_bad_id(p);
             self_row = -1;
         }
-        prefetch(g + n_warps);
         const int32_t* src = p.src + (int64_t)b * p.src_stride;
         const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b * p.row_map_stride : nullptr;
         T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
+
+        // ---- requests of this iteration, all issued before anything is consumed ------------------------------------
+        // (1) the row's own input row (narrow rows: one vector per lane, kept in a register until it is stored)
+        T self_v = V::zero();
+        const bool self_in_reg = NACC == 1 && need_self && self_row >= 0;
+        if (self_in_reg && lane < chunks) self_v = __ldg(reinterpret_cast<const T*>(x_row(p, self_row)) + lane);
+        // (2) the first batch of neighbour rows, first pass over the columns
+        T v0[UNR][NACC];
+        if (a < e_end) {
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                const int j = min(u, cnt_first - 1);  // past the end: reload the last row, skip its FMA
+                const int r = __shfl_sync(0xffffffffu, first_row, j);
+                const T* xr = reinterpret_cast<const T*>(x_row(p, r));
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) {
+                    const int c = k * 32 + lane;
+                    v0[u][k] = (c < chunks) ? __ldg(xr + c) : V::zero();
+                }
+            }
+        }
+        // (3) the pipeline stages of the warp's next rows
+        stage_c();
+        stage_b();
+        stage_a(g + 3 * (int64_t)n_warps);
+
+        // ---- consume ------------------------------------------------------------------------------------------------
         if (p.self_out) {
-            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
             T* srow = reinterpret_cast<T*>(p.self_out + g * p.ld_self);
-            for (int c = lane; c < chunks; c += 32) srow[c] = self_row < 0 ? V::zero() : __ldg(xr + c);
+            if (NACC == 1) {
+                if (lane < chunks) srow[lane] = self_v;
+            } else {
+                const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
+                for (int c = lane; c < chunks; c += 32) srow[c] = self_row < 0 ? V::zero() : __ldg(xr + c);
+            }
         }
         if (a >= e_end) {  // aggregate_acc_kernel.cu:307-308, :405-406
-            const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
-            for (int c = lane; c < chunks; c += 32) orow[c] = (p.passthrough && self_row >= 0) ? __ldg(xr + c) : V::zero();
+            if (NACC == 1) {
+                if (lane < chunks) orow[lane] = p.passthrough ? self_v : V::zero();
+            } else {
+                const T* xr = reinterpret_cast<const T*>(x_row(p, self_row < 0 ? 0 : self_row));
+                for (int c = lane; c < chunks; c += 32) orow[c] = (p.passthrough && self_row >= 0) ? __ldg(xr + c) : V::zero();
+            }
             continue;
         }
         float scale = 1.0f;
         if (MODE == FGL_AGG_MEAN) scale = 1.0f / (float)(e_end - a);
-        if (MODE == FGL_AGG_SYMNORM) scale = 1.0f / sqrtf((float)__ldg(p.dst_deg + d));
+        if (MODE == FGL_AGG_SYMNORM) scale = 1.0f / sqrtf((float)ddeg);
 
         for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
             T acc[NACC];
@@ -225,29 +316,44 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
             }
             for (int e0 = a; e0 < e_end; e0 += 32) {
                 const int cnt = min(32, e_end - e0);
-                int64_t my_row = first_row;
+                int my_row = first_row;
                 float my_w = first_w;
                 unsigned bad_mask = first_bad;
-                if (e0 != a) {
+                if (e0 != a) {  // rows with more than 32 in-edges: their further ids are fetched in line
                     my_row = 0;
                     my_w = 1.0f;
-                    bool bad = false;
+                    bool bad2 = false;
                     if (lane < cnt) {
                         const int s = __ldg(src + e0 + lane);
-                        my_row = checked_row<HAS_MAP>(p, row_map, s);
-                        bad = my_row < 0;
-                        if (bad) my_row = 0;
-                        if (MODE == FGL_AGG_SYMNORM && !bad) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+                        my_row = (int)checked_row<HAS_MAP>(p, row_map, s);
+                        bad2 = my_row < 0;
+                        if (bad2) my_row = 0;
+                        if (MODE == FGL_AGG_SYMNORM && !bad2) my_w = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
                     }
-                    bad_mask = __ballot_sync(0xffffffffu, bad);
+                    bad_mask = __ballot_sync(0xffffffffu, bad2);
                 }
-                for (int j0 = 0; j0 < cnt; j0 += UNR) {
+                int j0 = 0;
+                if (c0 == 0 && e0 == a) {  // warp-uniform: the batch requested before the pipeline stages
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+                        const float wu = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, min(u, cnt - 1)) : 1.0f;
+                        if (u < cnt && !((bad_mask >> u) & 1u)) {
+#pragma unroll
+                            for (int k = 0; k < NACC; ++k) {
+                                const float wk = (MODE == FGL_AGG_EDGE) ? __ldg(p.edge_w + (int64_t)(e0 + u) * p.n_heads + head[k]) : wu;
+                                V::fma(acc[k], wk, v0[u][k]);
+                            }
+                        }
+                    }
+                    j0 = UNR;
+                }
+                for (; j0 < cnt; j0 += UNR) {
                     T v[UNR][NACC];
                     float w[UNR];
 #pragma unroll
                     for (int u = 0; u < UNR; ++u) {
                         const int j = min(j0 + u, cnt - 1);  // past the end: reload the last row, skip its FMA
-                        const int64_t r = __shfl_sync(0xffffffffu, my_row, j);
+                        const int r = __shfl_sync(0xffffffffu, my_row, j);
                         w[u] = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, j) : 1.0f;
                         const T* xr = reinterpret_cast<const T*>(x_row(p, r));
 #pragma unroll
@@ -276,6 +382,229 @@ __global__ void __launch_bounds__(kAggThreads, FGL_AGG_MIN_CTAS) agg_fwd_kernel(
                 if (c < chunks) orow[c] = (MODE == FGL_AGG_SUM || MODE == FGL_AGG_EDGE) ? acc[k] : V::scale(acc[k], scale);
             }
         }
+    }
+}
+
+// The same forward aggregation for the shapes a sampled mini-batch has on its widest hop -- rows of at most 32
+// 128-bit vectors (D <= 128 floats), a single dense table, sum / mean / sym-norm -- with the rows staged through
+// shared memory by asynchronous copies (cp.async, 16 bytes per lane, L2 only) instead of through registers.
+//
+// Why: a warp of agg_fwd_kernel holds every byte it has in flight in registers; at 120 registers a thread an SM keeps
+// 16 warps x 8 rows = 50 KB in flight, and on 400-byte rows fetched at random from HBM that -- not bandwidth -- bounds
+// the kernel (measured: 2.6 TB/s of DRAM traffic, 40 % of the copy peak).  Here every warp owns kAggSlots row slots of
+// shared memory and needs few registers, so an SM runs 24 warps with 16 rows each in flight (150 KB; measured best).  Per
+// destination row a warp requests its own input row (slot 0, the self copy) and up to 15 neighbour rows (a row sampled
+// with fanout 15 is exactly one pass), moves the id pipeline (indptr -> src -> row_map, three rows ahead, as in
+// agg_fwd_kernel) while the copies fly, waits for its copies, and adds the rows out of shared memory.  Per neighbour
+// row that is one shuffle, one multiply-add and one cp.async, later one 128-bit shared-memory load and four adds.  Rows
+// with more than 15 in-edges take further passes whose ids are fetched in line.
+constexpr int kAggSlots = 16;
+#ifndef FGL_AGG_STAGED_WARPS
+#define FGL_AGG_STAGED_WARPS 24
+#endif
+constexpr int kAggStagedMaxWarps = FGL_AGG_STAGED_WARPS;  // per CTA (one CTA per SM); fewer when the rows are wider
+
+__device__ __forceinline__ void cp_async16(unsigned smem_dst, const void* gmem_src) {  // smem_dst: shared-space address
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ float4 lds128(unsigned smem_src) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_src));
+    return v;
+}
+
+template <int MODE, bool HAS_MAP>
+__global__ void __launch_bounds__(kAggStagedMaxWarps * 32, 1) agg_fwd_staged_kernel(const AggParams p) {
+    using V = Vec<4>;
+    using T = float4;
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
+    __shared__ long long s_off[kAggMaxWindow + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cta_warps = blockDim.x >> 5;
+    const int warp_global = blockIdx.x * cta_warps + warp;
+    const int n_warps = gridDim.x * cta_warps;
+    const int chunks = p.dim / 4;  // <= 32
+    const unsigned slot_bytes = (unsigned)chunks * 16u;
+    const bool window = p.out_row_off != nullptr;
+    if (window) {
+        for (int i = threadIdx.x; i <= p.n_batches; i += blockDim.x) s_off[i] = __ldg(p.out_row_off + i);
+        __syncthreads();
+    }
+    const int64_t padded = window ? s_off[p.n_batches] : (int64_t)p.n_dst;
+    const int64_t total = p.n_dst_dev ? min((int64_t)max(__ldg(p.n_dst_dev), 0), padded) : padded;
+    const bool lane_on = lane < chunks;
+    for (int64_t g = total + warp_global; g < padded; g += n_warps)
+        if (lane_on) reinterpret_cast<T*>(p.out + g * p.ldo)[lane] = V::zero();
+    const bool want_self = p.self_out != nullptr || p.passthrough != 0;
+    // Lanes beyond the row's last vector repeat that vector (same source, same destination: a duplicate request inside
+    // one instruction), so that no copy, load or add in the loops below needs a per-lane predicate.
+    const int lane_c = min(lane, chunks - 1);
+    const char* lane_base = reinterpret_cast<const char*>(p.x) + lane_c * 16;
+    const unsigned ld_bytes = (unsigned)(p.ldx * 4);
+    auto row_ptr = [&](int r) { return lane_base + (uint64_t)(unsigned)r * ld_bytes; };  // one 32 x 32 + 64 multiply-add
+    const unsigned slots = (unsigned)__cvta_generic_to_shared(dyn_smem) + (unsigned)warp * kAggSlots * slot_bytes + lane_c * 16;
+
+    // ---- id pipeline, three destination rows ahead (see agg_fwd_kernel) ------------------------------------------------
+    int bA = 0, dA = 0, aA = 0, eA = 0;
+    int bB = 0, dB = 0, aB = 0, eB = 0, sB = -1, selfB = -1, ddegB = 1;
+    int bC = 0, aC = 0, eC = 0, rowC = 0, selfC = -1, sdegC = 1, ddegC = 1;
+    int batch_ptr = 0;
+    auto stage_a = [&](int64_t g) {
+        aA = 0;
+        eA = 0;
+        if (g >= total) return;
+        if (window) {
+            while (g >= s_off[batch_ptr + 1]) ++batch_ptr;
+            bA = batch_ptr;
+            dA = (int)(g - s_off[batch_ptr]);
+        } else {
+            bA = 0;
+            dA = (int)g;
+        }
+        const int32_t* indptr = p.indptr + (int64_t)bA * p.indptr_stride;
+        aA = __ldg(indptr + dA);
+        eA = __ldg(indptr + dA + 1);
+    };
+    auto stage_b = [&]() {
+        bB = bA;
+        dB = dA;
+        aB = aA;
+        eB = eA;
+        sB = -1;
+        selfB = -1;
+        if (lane < min(eB - aB, kAggSlots - 1)) sB = __ldg(p.src + (int64_t)bB * p.src_stride + aB + lane);
+        if (want_self) {
+            if (HAS_MAP)
+                selfB = (int64_t)dB < p.n_map ? __ldg(p.row_map + (int64_t)bB * p.row_map_stride + dB) : -1;
+            else
+                selfB = dB;
+        }
+        if (MODE == FGL_AGG_SYMNORM && eB > aB) ddegB = __ldg(p.dst_deg + dB);
+    };
+    auto stage_c = [&]() {
+        bC = bB;
+        aC = aB;
+        eC = eB;
+        selfC = selfB;
+        ddegC = ddegB;
+        rowC = sB;
+        sdegC = 1;
+        const bool id_ok = sB >= 0 && (HAS_MAP ? (int64_t)sB < p.n_map : (int64_t)sB < p.n_rows);
+        if (id_ok) {
+            if (HAS_MAP) rowC = __ldg(p.row_map + (int64_t)bC * p.row_map_stride + sB);
+            if (MODE == FGL_AGG_SYMNORM) sdegC = __ldg(p.src_deg + sB);
+        } else {
+            rowC = -1;
+        }
+    };
+    stage_a(warp_global);
+    stage_b();
+    stage_c();
+    stage_a(warp_global + (int64_t)n_warps);
+    stage_b();
+    stage_a(warp_global + 2 * (int64_t)n_warps);
+
+    // Copy `cnt` rows (lane u holds row u) into slots 1 .. cnt; add them out of shared memory.
+    auto request = [&](int my_row, int cnt) {
+        unsigned dst = slots;
+        if (cnt == kAggSlots - 1) {  // the common case: a row sampled with the full fanout
+#pragma unroll
+            for (int u = 0; u < kAggSlots - 1; ++u) {
+                dst += slot_bytes;
+                cp_async16(dst, row_ptr(__shfl_sync(0xffffffffu, my_row, u)));
+            }
+        } else {
+            for (int u = 0; u < cnt; ++u) {
+                dst += slot_bytes;
+                cp_async16(dst, row_ptr(__shfl_sync(0xffffffffu, my_row, u)));
+            }
+        }
+    };
+    auto add_up = [&](T& acc, int cnt, unsigned bad_mask, float my_w) {
+        unsigned from = slots;
+        if (cnt == kAggSlots - 1 && bad_mask == 0u) {
+#pragma unroll
+            for (int u = 0; u < kAggSlots - 1; ++u) {
+                from += slot_bytes;
+                V::fma(acc, (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, u) : 1.0f, lds128(from));
+            }
+        } else {
+            for (int u = 0; u < cnt; ++u) {
+                from += slot_bytes;
+                const float wu = (MODE == FGL_AGG_SYMNORM) ? __shfl_sync(0xffffffffu, my_w, u) : 1.0f;
+                if (!((bad_mask >> u) & 1u)) V::fma(acc, wu, lds128(from));
+            }
+        }
+    };
+
+    for (int64_t g = warp_global; g < total; g += n_warps) {
+        // the current row: its ids were requested at least one iteration ago
+        const int b = bC, a = aC, e_end = eC, ddeg = ddegC;
+        const int cnt = min(kAggSlots - 1, e_end - a);
+        const bool has_edge = lane < cnt;
+        const bool bad = has_edge && (rowC < 0 || (int64_t)rowC >= p.n_rows);
+        if (bad) agg_bad_id(p);
+        const int my_row = (has_edge && !bad) ? rowC : 0;
+        const unsigned bad_mask = __ballot_sync(0xffffffffu, bad);
+        float my_w = 1.0f;
+        if (MODE == FGL_AGG_SYMNORM && has_edge && !bad) my_w = 1.0f / sqrtf((float)sdegC);
+        int self_row = selfC;
+        const bool need_self = p.self_out != nullptr || (a >= e_end && p.passthrough);
+        if (need_self && (self_row < 0 || (int64_t)self_row >= p.n_rows)) {
+            agg_bad_id(p);
+            self_row = -1;
+        }
+        // requests: the row's own input row, its first 15 neighbours, the next rows' ids
+        if (need_self && self_row >= 0) cp_async16(slots, row_ptr(self_row));
+        request(my_row, cnt);
+        stage_c();
+        stage_b();
+        stage_a(g + 3 * (int64_t)n_warps);
+        cp_async_wait_all();
+        __syncwarp();
+        // consume
+        T self_v = V::zero();
+        if (need_self && self_row >= 0) self_v = lds128(slots);
+        if (p.self_out && lane_on) reinterpret_cast<T*>(p.self_out + g * p.ld_self)[lane] = self_v;
+        T* orow = reinterpret_cast<T*>(p.out + g * p.ldo);
+        if (a >= e_end) {  // aggregate_acc_kernel.cu:307-308, :405-406
+            if (lane_on) orow[lane] = p.passthrough ? self_v : V::zero();
+            __syncwarp();
+            continue;
+        }
+        T acc = V::zero();
+        add_up(acc, cnt, bad_mask, my_w);
+        __syncwarp();  // every lane is done with the slots before the next copies overwrite them
+        if (e_end - a > kAggSlots - 1) {  // further passes of a long row: ids in line, same slots
+            const int32_t* src = p.src + (int64_t)b * p.src_stride;
+            const int32_t* row_map = HAS_MAP ? p.row_map + (int64_t)b * p.row_map_stride : nullptr;
+            for (int e0 = a + kAggSlots - 1; e0 < e_end; e0 += kAggSlots - 1) {
+                const int n = min(kAggSlots - 1, e_end - e0);
+                int row2 = 0;
+                float w2 = 1.0f;
+                bool bad2 = false;
+                if (lane < n) {
+                    const int s = __ldg(src + e0 + lane);
+                    row2 = (int)checked_row<HAS_MAP>(p, row_map, s);
+                    bad2 = row2 < 0;
+                    if (bad2) row2 = 0;
+                    if (MODE == FGL_AGG_SYMNORM && !bad2) w2 = 1.0f / sqrtf((float)__ldg(p.src_deg + s));
+                }
+                const unsigned bad2_mask = __ballot_sync(0xffffffffu, bad2);
+                request(row2, n);
+                cp_async_wait_all();
+                __syncwarp();
+                add_up(acc, n, bad2_mask, w2);
+                __syncwarp();
+            }
+        }
+        float scale = 1.0f;
+        if (MODE == FGL_AGG_MEAN) scale = 1.0f / (float)(e_end - a);
+        if (MODE == FGL_AGG_SYMNORM) scale = 1.0f / sqrtf((float)ddeg);
+        if (lane_on) orow[lane] = (MODE == FGL_AGG_SUM) ? acc : V::scale(acc, scale);
     }
 }
 
@@ -450,10 +779,41 @@ static void launch_fwd(const AggParams& p, dim3 grid, cudaStream_t st) {
         agg_fwd_kernel<VEC, MODE, false, NACC, UNR><<<grid, kAggThreads, 0, st>>>(p);
 }
 
+// Whether agg_fwd_staged_kernel applies: 128-bit rows of at most 32 vectors in a single dense table.
+static bool staged_applies(const AggParams& p, int vec) {
+    return vec == 4 && p.shards == nullptr && p.dim / 4 <= 32 && p.ldx * 4 <= 0xffffffffLL;
+}
+
+template <int MODE>
+static void launch_fwd_staged(const AggParams& p, cudaStream_t st) {
+    static int sms = 0, smem_optin = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    // as many warps per SM as their row slots fit beside the kernel's static shared memory
+    const int64_t per_warp = (int64_t)kAggSlots * (p.dim / 4) * 16;
+    const int warps = (int)std::max<int64_t>(1, std::min<int64_t>(kAggStagedMaxWarps, ((int64_t)smem_optin - 8 * 1024) / per_warp));
+    const size_t dyn = (size_t)warps * per_warp;
+    const int64_t rows = p.out_row_off ? 0x7fffffff : p.n_dst;  // window launches fill the GPU
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(sms, (rows + warps - 1) / warps));
+    if (p.row_map) {
+        cudaFuncSetAttribute(agg_fwd_staged_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        agg_fwd_staged_kernel<MODE, true><<<grid, warps * 32, dyn, st>>>(p);
+    } else {
+        cudaFuncSetAttribute(agg_fwd_staged_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+        agg_fwd_staged_kernel<MODE, false><<<grid, warps * 32, dyn, st>>>(p);
+    }
+}
+
 template <int VEC, int MODE>
 static void launch_fwd_nacc(const AggParams& p, dim3 grid, cudaStream_t st) {
     const int chunks = p.dim / VEC;
-    if (chunks <= 32)
+    if (MODE != FGL_AGG_EDGE && staged_applies(p, VEC)) {
+        launch_fwd_staged<MODE == FGL_AGG_EDGE ? FGL_AGG_SUM : MODE>(p, st);
+    } else if (chunks <= 32)
         launch_fwd<VEC, MODE, 1, FGL_AGG_UNR1>(p, grid, st);
     else if (chunks <= 64)
         launch_fwd<VEC, MODE, 2, 4>(p, grid, st);
@@ -573,7 +933,8 @@ int fgl_agg_fwd_window(fgl_ws* ws, int32_t mode, int32_t n_batches, const int32_
                        const int64_t* out_row_off, int64_t total_rows, const float* x, const float* const* shards,
                        int64_t rows_per_shard, int64_t n_rows, int64_t ldx, int32_t dim, int32_t flags, float* out,
                        int64_t ldo, float* self_out, int64_t ld_self, void* stream) {
-    if ((mode != FGL_AGG_SUM && mode != FGL_AGG_MEAN) || n_batches < 0 || total_rows < 0 || total_rows > 0x7fffffffLL ||
+    if ((mode != FGL_AGG_SUM && mode != FGL_AGG_MEAN) || n_batches < 0 || n_batches > kAggMaxWindow || total_rows < 0 ||
+        total_rows > 0x7fffffffLL ||
         dim < 1 || ldx < dim || ldo < dim || (self_out && ld_self < dim) || n_rows < 0)
         return FGL_ERR_INVALID;
     if (n_batches == 0 || total_rows == 0) return FGL_OK;
