@@ -5,17 +5,21 @@
 // small enough to stay in the 126 MB L2, and synchronises with a team-local barrier, so that several
 // mini-batches are in flight and one team's barrier latency is covered by the others' memory traffic.
 //
-// Per hop, for the current node list (the seeds of the hop):
-//   A  count     k_s = min(deg, fanout) per seed, one partial sum per CTA
-//   B  sample    block-CSR offsets by a two-level scan; each seed is served by a group of 8/16/32 lanes
-//                that choose the picks (Philox4x32-10; Floyd's algorithm for a k-subset), read the picked
-//                sources and insert them into the open-addressing table (64-bit slots {key, value},
-//                atomicCAS to claim, atomicMin of the edge number to find the first occurrence)
-//   C  count     first occurrences per CTA            (first-occurrence order only)
-//   D  rank      scan -> local id, publish it in the slot, append the node to the unique list
-//   E  relabel   replace the slot position kept in the edge array by the local id
-// With FGL_MAP_ARRIVAL_ORDER the claiming thread takes the next id from a warp-aggregated counter in
-// phase B and phases C and D are skipped.
+// Per hop, for the current node list (the seeds of the hop), in the fused kernel:
+//   A  count     k_s = min(deg, fanout) per seed from the degrees cached when the node joined the list (coalesced),
+//                one partial sum per CTA
+//   B  sample    block-CSR offsets by a two-level scan; each seed is served by a group of 8/16/32 lanes that choose
+//                the picks (Philox4x32-10; Floyd's algorithm for a k-subset, run by the group in registers), read the
+//                picked sources and insert them into the open-addressing table (64-bit slots {key, value}, atomicCAS
+//                to claim, atomicMin of the edge number to find the first occurrence).  A thread that claims a slot or
+//                lowers its edge number marks its edge "possibly first" and moves one unit of the per-CTA count of
+//                first occurrences from the displaced edge's CTA to its own, so no counting pass is needed
+//   D  rank      scan over the possibly-first edges that still hold their slot -> local id, publish it in the slot,
+//                append the node (and its adjacency offset and degree, for the next hop) to the list
+//   E  relabel   replace the slot position kept in the remaining edge entries by the local id
+// With FGL_MAP_ARRIVAL_ORDER the claiming thread takes the next id from a warp-aggregated counter in phase B and
+// phase D is skipped.  The drop-in kernels (fgl_sample: phases A + B without a table; fgl_map: explicit edges) keep
+// a counting pass (C) between B and D.
 //
 // Replaces sample_node_cuda (sample.cu:102-203), transfer_edge_id_cuda (id_map.cu:386-493) and the
 // hashtable of id_map.cu:26-255 / cuda_hashtable.cuh.
@@ -69,12 +73,12 @@ struct KParams {
     int64_t table_slots;  // per team, power of two
     int32_t table_shift;  // 32 - log2(table_slots)
     unsigned long long* barriers;  // one per team, 16 words apart
-    int32_t* team_sums;            // [n_teams][team_size]
-    int32_t* node_pos;             // [n_teams][nodes_stride]: slot of every node, for the clean-up walk
+    int32_t* team_sums;            // [n_teams][team_size]: per-CTA edge counts of the hop
+    int32_t* team_cnt;             // [n_teams][team_size]: per-CTA counts of first occurrences (fused kernel)
+    long long* node_start;         // [n_teams][deg_stride]: adjacency offset of every node that can still be a seed
+    int32_t* node_deg;             // [n_teams][deg_stride]: and its degree
+    int64_t deg_stride;
     int32_t* status;               // [0] first error, [1] abort flag
-#ifdef FGL_PHASE_TIMING
-    unsigned long long* dbg;       // phase timestamps of team 0 / rank 0 (instrumented builds only)
-#endif
 };
 
 // ----------------------------------------------------------------------------------------------
@@ -162,6 +166,43 @@ __device__ __forceinline__ int table_insert(const Table& t, uint32_t key, uint32
     return table_insert_from<ARRIVAL>(t, key, edge, hash_pos(t, key), status, created);
 }
 
+// Lowers the edge number kept in a pending slot to `edge` if that is smaller.  Returns the edge number that lost
+// its place as the key's first occurrence, or -1 if nothing changed.
+__device__ __forceinline__ int table_lower_edge(const Table& t, uint32_t pos, uint32_t key, uint32_t edge) {
+    const unsigned long long mine = ((unsigned long long)key << 32) | (kPending | edge);
+    const unsigned long long old = atomicMin(t.slots + pos, mine);
+    const uint32_t old_lo = (uint32_t)old;
+    return ((old_lo & kPending) && old_lo > (kPending | edge)) ? (int)(old_lo & ~kPending) : -1;
+}
+
+// table_insert_from for the fused kernel's first-occurrence order: also reports the edge this insert displaced as the
+// key's first occurrence (-1: none).  created or displaced >= 0 means "edge may be the key's first occurrence".
+__device__ __forceinline__ int table_insert_track(const Table& t, uint32_t key, uint32_t edge, uint32_t pos,
+                                                  int32_t* status, bool& created, int& displaced) {
+    created = false;
+    displaced = -1;
+    const unsigned long long mine = ((unsigned long long)key << 32) | (kPending | edge);
+    for (uint32_t probe = 0; probe <= probe_limit(t); ++probe) {
+        unsigned long long cur = ld_slot(t.slots + pos);
+        if (cur == kEmpty) {
+            cur = atomicCAS(t.slots + pos, kEmpty, mine);
+            if (cur == kEmpty) {
+                created = true;
+                return ~(int)pos;
+            }
+        }
+        if ((uint32_t)(cur >> 32) == key) {
+            const uint32_t lo = (uint32_t)cur;
+            if (!(lo & kPending)) return (int)lo;
+            if (lo > (kPending | edge)) displaced = table_lower_edge(t, pos, key, edge);
+            return ~(int)pos;
+        }
+        pos = (pos + 1) & t.mask;
+    }
+    probe_failed(status);
+    return 0;
+}
+
 // Value of a key that must be present (a seed); missing keys report FGL_ERR_BOUNDS and map to 0.
 __device__ __forceinline__ int table_lookup(const Table& t, uint32_t key, int32_t* status) {
     uint32_t pos = hash_pos(t, key);
@@ -183,12 +224,17 @@ struct Hop {
     int64_t nodes_cap;
     int32_t* counts;       // this mini-batch's counts row
     int32_t* blk_indptr;   // may be NULL (MODE_SAMPLE without CSR output)
-    int32_t* blk_src;      // edge array: global ids (MODE_SAMPLE) or local ids / ~pos
+    int32_t* blk_src;      // edge array: global ids (MODE_SAMPLE) or local ids / pending entries
     int32_t* out_dst;      // MODE_SAMPLE only
-    int32_t* node_pos;     // slot position of every node of the list (fused mode), else NULL
+    long long* node_start; // fused: adjacency offset and degree of the nodes that can still become seeds
+    int32_t* node_deg;
+    int64_t deg_cap;
     int hop, fanout, n_seeds;
+    bool last_hop;
     uint64_t ctr;
 };
+
+constexpr int kMaxTeam = 512;  // CTAs per team (a cooperative grid of 512-thread CTAs has at most a few hundred)
 
 struct Smem {
     int scan[40];
@@ -197,7 +243,13 @@ struct Smem {
     long long start[kThreads];
     int deg[kThreads];
     int off[kThreads];
+    int prefix[kMaxTeam + 1];  // fused: first edge of every CTA of the team (the owner of an edge number)
 };
+
+// Fused kernel, first-occurrence order: an edge entry is a local id (>= 0) or, while the id is pending,
+// ~(slot | kTentative if the edge may be the first occurrence of its key).  Slots are below 2^29.
+constexpr int kTentative = 1 << 29;
+constexpr int kSlotMask = kTentative - 1;
 
 __device__ __forceinline__ void chunk_of(int n, int rank, int size, int& lo, int& hi) {
     const int per = (n + size - 1) / size;
@@ -220,13 +272,47 @@ __device__ __forceinline__ void load_adj(const KParams& p, int v, long long& sta
     deg = d < 0 ? 0 : (d > 0x7fffffffLL ? 0x7fffffff : (int)d);
 }
 
-template <bool ARRIVAL>
-__device__ __forceinline__ void finish_edge(const KParams& p, const Hop& h, const Table& tab, int g, int e, int r,
-                                            bool created);
+// The CTA of the team whose edge range holds edge number e (sm.prefix is the exclusive scan of the CTAs' edge counts).
+__device__ __forceinline__ int edge_owner(const Smem& sm, int team_size, int e) {
+    int lo = 0, hi = team_size;  // invariant: prefix[lo] <= e < prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sm.prefix[mid] <= e) lo = mid; else hi = mid;
+    }
+    return lo;
+}
 
-// One sampled edge: picked source `g` of seed `v`, edge number e within the hop.
-template <int MODE, bool ARRIVAL>
-__device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const Table& tab, int v, int g, int e) {
+// Second half of an insert in arrival-order mode: the claiming thread takes the next local id and publishes it.
+template <typename PtrT>
+__device__ __forceinline__ int arrival_assign(const KParams& p, const Hop& h, const Table& tab, int g, int r) {
+    cg::coalesced_group grp = cg::coalesced_threads();  // one atomicAdd per group of claiming lanes
+    int base = 0;
+    if (grp.thread_rank() == 0) base = atomicAdd(h.counts + h.hop + 1, (int)grp.size());
+    base = grp.shfl(base, 0);
+    const int local = base + (int)grp.thread_rank();
+    const uint32_t pos = (uint32_t)~r;
+    if ((int64_t)local < h.nodes_cap) {
+        h.nodes[local] = g;
+        if (h.node_deg && !h.last_hop && (int64_t)local < h.deg_cap) {
+            long long start;
+            int deg;
+            load_adj<PtrT>(p, g, start, deg);
+            __stcg(h.node_start + local, start);
+            __stcg(h.node_deg + local, deg);
+        }
+        atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32) | (uint32_t)local);
+        return local;
+    }
+    set_status(p.status, FGL_ERR_CAPACITY);
+    atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32));
+    return 0;
+}
+
+// One sampled edge of the wide-fanout path: picked source `g` of seed `v`, edge number e within the hop.
+// first_cnt counts the edges of this thread that may be first occurrences (fused, first-occurrence order).
+template <typename PtrT, int MODE, bool ARRIVAL>
+__device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const Table& tab, const Smem& sm, int team_size,
+                                          int32_t* team_cnt, int v, int g, int e, int& first_cnt) {
     if (MODE == MODE_SAMPLE) {
         h.blk_src[e] = g;
         if (h.out_dst) h.out_dst[e] = v;
@@ -237,107 +323,90 @@ __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const 
         h.blk_src[e] = 0;
         return;
     }
-    bool created;
-    int r = table_insert<ARRIVAL>(tab, (uint32_t)g, (uint32_t)e, p.status, created);
-    finish_edge<ARRIVAL>(p, h, tab, g, e, r, created);
-}
-
-// Second half of an insert: in arrival-order mode the claiming thread takes the next local id and publishes
-// it; then the edge's entry (local id, or ~slot while the id is pending) is stored.
-template <bool ARRIVAL>
-__device__ __forceinline__ void finish_edge(const KParams& p, const Hop& h, const Table& tab, int g, int e, int r,
-                                            bool created) {
-    if (ARRIVAL && created) {
-        // one atomicAdd per group of claiming lanes
-        cg::coalesced_group grp = cg::coalesced_threads();
-        int base = 0;
-        if (grp.thread_rank() == 0) base = atomicAdd(h.counts + h.hop + 1, (int)grp.size());
-        base = grp.shfl(base, 0);
-        const int local = base + (int)grp.thread_rank();
-        const uint32_t pos = (uint32_t)~r;
-        if ((int64_t)local < h.nodes_cap) {
-            h.nodes[local] = g;
-            if (h.node_pos) h.node_pos[local] = (int)pos;
-            atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32) | (uint32_t)local);
-            r = local;
-        } else {
-            set_status(p.status, FGL_ERR_CAPACITY);
-            atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32));
-            r = 0;
+    if (ARRIVAL) {
+        bool created;
+        int r = table_insert<true>(tab, (uint32_t)g, (uint32_t)e, p.status, created);
+        if (created) r = arrival_assign<PtrT>(p, h, tab, g, r);
+        h.blk_src[e] = r;
+    } else {
+        bool created;
+        int displaced;
+        int r = table_insert_track(tab, (uint32_t)g, (uint32_t)e, hash_pos(tab, (uint32_t)g), p.status, created, displaced);
+        if (r < 0 && (created || displaced >= 0)) {
+            r = ~((~r) | kTentative);
+            ++first_cnt;
+            if (displaced >= 0) atomicAdd(team_cnt + edge_owner(sm, team_size, displaced), -1);
         }
+        h.blk_src[e] = r;
     }
-    h.blk_src[e] = r;
 }
 
-// Fanouts up to 32, in two steps per tile of kThreads seeds.
-// Step 1, one thread per seed: the thread chooses its seed's picks alone (Floyd's algorithm needs only the
-// earlier picks of the same seed, kept in the thread's row of shared memory; one Philox block yields four
-// picks) -- a small fraction of the instructions a lane-per-pick scheme spends on shuffles and ballots.
-// Step 2, a group of G lanes per seed, one lane per pick: a group works on kSeedsPerIter seeds at a time and
-// issues their dependent loads stage by stage -- picked sources, first table probes, claims -- so that four
-// independent round trips are in flight per lane instead of one chain after the other.
+// Fanouts up to 32: a group of G lanes per seed, one lane per pick; a group works on kSeedsPerIter seeds at a time.
+// Stage 0, picks: every lane draws its own Philox word; for a k-subset (Floyd's algorithm: slot i draws t in
+// [0, deg-k+i] and takes deg-k+i instead if an earlier slot already holds t) the group walks the slots in order, lane i
+// settling slot i after a ballot over the earlier lanes -- the picks never leave the registers.  Stages 1-4 issue the
+// dependent loads of the group's seeds stage by stage -- picked sources, first table probes, claims -- so that
+// kSeedsPerIter independent round trips are in flight per lane instead of one chain after the other.
 constexpr int kSeedsPerIter = 4;
 constexpr int kGroupPathMaxFanout = 32;
 
-__device__ __forceinline__ int picks_stride(int fanout) { return fanout | 1; }  // odd: conflict-free rows
-
-template <int MODE, bool ARRIVAL, int G>
-__device__ __forceinline__ void sample_tile_groups(const KParams& p, const Hop& h, const Table& tab, Smem& sm,
-                                                   uint32_t* picks, int tile0, int tile_n) {
+template <typename PtrT, int MODE, bool ARRIVAL, int G>
+__device__ __forceinline__ void sample_tile_groups(const KParams& p, const Hop& h, const Table& tab, Smem& sm, int team_size,
+                                                   int32_t* team_cnt, int tile0, int tile_n, int& first_cnt) {
     const bool replace = (p.flags & FGL_SAMPLE_REPLACE) != 0;
     const int fanout = h.fanout;
-    const int stride = picks_stride(fanout);
-    {
-        const int t = threadIdx.x;
-        const int deg = t < tile_n ? sm.deg[t] : 0;
-        if (deg > fanout) {
-            uint32_t* mine = picks + (size_t)t * stride;
-            uint4 blk = make_uint4(0, 0, 0, 0);
-            for (int i = 0; i < fanout; ++i) {
-                if ((i & 3) == 0) blk = philox_block(p.rng_seed, h.ctr, (uint32_t)(tile0 + t), (uint32_t)(i >> 2));
-                const uint32_t r = philox_word(blk, i & 3);
-                uint32_t pk;
-                if (replace) {
-                    pk = __umulhi(r, (uint32_t)deg);
-                } else {
-                    // Floyd: slot i draws tt in [0, deg-k+i]; a repeat is replaced by deg-k+i itself
-                    const uint32_t jj = (uint32_t)(deg - fanout + i);
-                    const uint32_t tt = __umulhi(r, jj + 1u);
-                    bool hit = false;
-                    for (int q = 0; q < i; ++q) hit |= (mine[q] == tt);
-                    pk = hit ? jj : tt;
-                }
-                mine[i] = pk;
-            }
-        }
-    }
-    __syncthreads();
-
     constexpr int kGroups = kThreads / G;
     constexpr int KS = kSeedsPerIter;
     const int gid = threadIdx.x / G, gl = threadIdx.x % G;
+    const int gbase = (threadIdx.x & 31) & ~(G - 1);  // first lane of the group within its warp
+    const unsigned gmask = G == 32 ? 0xffffffffu : ((1u << G) - 1u);
     for (int it = 0; it * kGroups * KS < tile_n; ++it) {
-        int v[KS], off[KS], g[KS];
-        bool has[KS];
-        // stage 1: the picked sources
+        int v[KS], off[KS], g[KS], deg[KS];
+        long long start[KS];
+        bool has[KS], hub[KS];
+        uint32_t pk[KS], draw[KS];
+        // stage 0: the picks
+        bool any_hub = false;
 #pragma unroll
         for (int q = 0; q < KS; ++q) {
             const int j = (it * KS + q) * kGroups + gid;
             v[q] = 0;
             off[q] = 0;
             g[q] = 0;
-            has[q] = false;
+            deg[q] = 0;
+            start[q] = 0;
             if (j < tile_n) {
-                const int deg = sm.deg[j];
-                has[q] = gl < min(deg, fanout);
-                if (has[q]) {
-                    v[q] = sm.v[j];
-                    off[q] = sm.off[j];
-                    const uint32_t pk = deg > fanout ? picks[(size_t)j * stride + gl] : (uint32_t)gl;
-                    g[q] = __ldg(p.indices + sm.start[j] + (long long)pk);
+                deg[q] = sm.deg[j];
+                v[q] = sm.v[j];
+                off[q] = sm.off[j];
+                start[q] = sm.start[j];
+            }
+            has[q] = gl < min(deg[q], fanout);
+            hub[q] = deg[q] > fanout;
+            pk[q] = (uint32_t)gl;
+            draw[q] = 0;
+            if (hub[q] && gl < fanout) {
+                draw[q] = philox_draw(p.rng_seed, h.ctr, (uint32_t)(tile0 + (it * KS + q) * kGroups + gid), (uint32_t)gl);
+                if (replace) pk[q] = __umulhi(draw[q], (uint32_t)deg[q]);
+            }
+            any_hub |= hub[q];
+        }
+        if (!replace && __any_sync(0xffffffffu, any_hub)) {  // warp-uniform
+            for (int i = 0; i < fanout; ++i) {
+#pragma unroll
+                for (int q = 0; q < KS; ++q) {
+                    const uint32_t ri = __shfl_sync(0xffffffffu, draw[q], gbase + i);
+                    const uint32_t jj = (uint32_t)(deg[q] - fanout + i);
+                    const uint32_t tt = __umulhi(ri, jj + 1u);
+                    const unsigned same = __ballot_sync(0xffffffffu, hub[q] && gl < i && pk[q] == tt);
+                    if (hub[q] && gl == i) pk[q] = ((same >> gbase) & gmask) ? jj : tt;
                 }
             }
         }
+        // stage 1: the picked sources
+#pragma unroll
+        for (int q = 0; q < KS; ++q)
+            if (has[q]) g[q] = __ldg(p.indices + start[q] + (long long)pk[q]);
         if (MODE == MODE_SAMPLE) {
 #pragma unroll
             for (int q = 0; q < KS; ++q) {
@@ -347,62 +416,71 @@ __device__ __forceinline__ void sample_tile_groups(const KParams& p, const Hop& 
                 }
             }
         } else {
-            // stage 2: first probe of every source
-            uint32_t pos[KS];
-            unsigned long long cur[KS], seen[KS];
+        // stage 2: first probe of every source
+        uint32_t pos[KS];
+        unsigned long long cur[KS], seen[KS];
 #pragma unroll
-            for (int q = 0; q < KS; ++q) {
-                if (has[q] && (g[q] < 0 || (int64_t)g[q] >= p.n_nodes)) {
-                    set_status(p.status, FGL_ERR_BOUNDS);
-                    h.blk_src[off[q] + gl] = 0;
-                    has[q] = false;
-                }
-                pos[q] = hash_pos(tab, (uint32_t)g[q]);
-                cur[q] = has[q] ? ld_slot(tab.slots + pos[q]) : 0ULL;
+        for (int q = 0; q < KS; ++q) {
+            if (has[q] && (g[q] < 0 || (int64_t)g[q] >= p.n_nodes)) {
+                set_status(p.status, FGL_ERR_BOUNDS);
+                h.blk_src[off[q] + gl] = 0;
+                has[q] = false;
             }
-            // stage 3: claim the slots that looked empty
+            pos[q] = hash_pos(tab, (uint32_t)g[q]);
+            cur[q] = has[q] ? ld_slot(tab.slots + pos[q]) : 0ULL;
+        }
+        // stage 3: claim the slots that looked empty
 #pragma unroll
-            for (int q = 0; q < KS; ++q) {
-                seen[q] = cur[q];
-                if (has[q] && cur[q] == kEmpty) {
-                    const uint32_t e = (uint32_t)(off[q] + gl);
-                    seen[q] = atomicCAS(tab.slots + pos[q], kEmpty,
-                                        ((unsigned long long)(uint32_t)g[q] << 32) | (ARRIVAL ? kPending : (kPending | e)));
-                }
-            }
-            // stage 4: settle every edge; collisions continue probing one by one
-#pragma unroll
-            for (int q = 0; q < KS; ++q) {
-                if (!has[q]) continue;
-                const uint32_t key = (uint32_t)g[q];
-                const int e = off[q] + gl;
-                bool created = false;
-                int r;
-                if (cur[q] == kEmpty && seen[q] == kEmpty) {
-                    created = true;
-                    r = ~(int)pos[q];
-                } else if ((uint32_t)(seen[q] >> 32) == key) {
-                    const uint32_t lo = (uint32_t)seen[q];
-                    if (!(lo & kPending)) {
-                        r = (int)lo;
-                    } else {
-                        if (!ARRIVAL && lo > (kPending | (uint32_t)e))
-                            atomicMin(tab.slots + pos[q], ((unsigned long long)key << 32) | (kPending | (uint32_t)e));
-                        r = ~(int)pos[q];
-                    }
-                } else {
-                    r = table_insert_from<ARRIVAL>(tab, key, (uint32_t)e, (pos[q] + 1) & tab.mask, p.status, created);
-                }
-                finish_edge<ARRIVAL>(p, h, tab, g[q], e, r, created);
+        for (int q = 0; q < KS; ++q) {
+            seen[q] = cur[q];
+            if (has[q] && cur[q] == kEmpty) {
+                const uint32_t e = (uint32_t)(off[q] + gl);
+                seen[q] = atomicCAS(tab.slots + pos[q], kEmpty,
+                                    ((unsigned long long)(uint32_t)g[q] << 32) | (ARRIVAL ? kPending : (kPending | e)));
             }
         }
+        // stage 4: settle every edge; collisions continue probing one by one
+#pragma unroll
+        for (int q = 0; q < KS; ++q) {
+            if (!has[q]) continue;
+            const uint32_t key = (uint32_t)g[q];
+            const int e = off[q] + gl;
+            bool created = false;
+            int displaced = -1;
+            int r;
+            if (cur[q] == kEmpty && seen[q] == kEmpty) {
+                created = true;
+                r = ~(int)pos[q];
+            } else if ((uint32_t)(seen[q] >> 32) == key) {
+                const uint32_t lo = (uint32_t)seen[q];
+                if (!(lo & kPending)) {
+                    r = (int)lo;
+                } else {
+                    if (!ARRIVAL && lo > (kPending | (uint32_t)e)) displaced = table_lower_edge(tab, pos[q], key, (uint32_t)e);
+                    r = ~(int)pos[q];
+                }
+            } else if (ARRIVAL) {
+                r = table_insert_from<true>(tab, key, (uint32_t)e, (pos[q] + 1) & tab.mask, p.status, created);
+            } else {
+                r = table_insert_track(tab, key, (uint32_t)e, (pos[q] + 1) & tab.mask, p.status, created, displaced);
+            }
+            if (ARRIVAL) {
+                if (created) r = arrival_assign<PtrT>(p, h, tab, g[q], r);
+            } else if (r < 0 && (created || displaced >= 0)) {
+                r = ~((~r) | kTentative);
+                ++first_cnt;
+                if (displaced >= 0) atomicAdd(team_cnt + edge_owner(sm, team_size, displaced), -1);
+            }
+            h.blk_src[e] = r;
+        }
+        }  // MODE != MODE_SAMPLE
     }
 }
 
 // Any fanout up to FGL_MAX_FANOUT: one warp per seed, picks in shared memory.
-template <int MODE, bool ARRIVAL>
-__device__ __forceinline__ void sample_tile_wide(const KParams& p, const Hop& h, const Table& tab, Smem& sm,
-                                                 uint32_t* picks_all, int tile0, int tile_n) {
+template <typename PtrT, int MODE, bool ARRIVAL>
+__device__ __forceinline__ void sample_tile_wide(const KParams& p, const Hop& h, const Table& tab, Smem& sm, int team_size,
+                                                 int32_t* team_cnt, uint32_t* picks_all, int tile0, int tile_n, int& first_cnt) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool replace = (p.flags & FGL_SAMPLE_REPLACE) != 0;
     const int fanout = h.fanout;
@@ -412,11 +490,12 @@ __device__ __forceinline__ void sample_tile_wide(const KParams& p, const Hop& h,
         const long long start = sm.start[j];
         if (deg <= fanout) {
             for (int i = lane; i < deg; i += 32)
-                emit_edge<MODE, ARRIVAL>(p, h, tab, v, p.indices[start + i], off + i);
+                emit_edge<PtrT, MODE, ARRIVAL>(p, h, tab, sm, team_size, team_cnt, v, p.indices[start + i], off + i, first_cnt);
         } else if (replace) {
             for (int i = lane; i < fanout; i += 32) {
                 const uint32_t r = philox_draw(p.rng_seed, h.ctr, (uint32_t)(tile0 + j), (uint32_t)i);
-                emit_edge<MODE, ARRIVAL>(p, h, tab, v, p.indices[start + (long long)__umulhi(r, (uint32_t)deg)], off + i);
+                emit_edge<PtrT, MODE, ARRIVAL>(p, h, tab, sm, team_size, team_cnt, v,
+                                               p.indices[start + (long long)__umulhi(r, (uint32_t)deg)], off + i, first_cnt);
             }
         } else {
             uint32_t r = 0;
@@ -434,13 +513,14 @@ __device__ __forceinline__ void sample_tile_wide(const KParams& p, const Hop& h,
                 __syncwarp();
             }
             for (int i = lane; i < fanout; i += 32)
-                emit_edge<MODE, ARRIVAL>(p, h, tab, v, p.indices[start + (long long)picks[i]], off + i);
+                emit_edge<PtrT, MODE, ARRIVAL>(p, h, tab, sm, team_size, team_cnt, v, p.indices[start + (long long)picks[i]], off + i,
+                                               first_cnt);
         }
         __syncwarp();
     }
 }
 
-// Phase A: per-CTA sum of min(deg, fanout) over the CTA's slice of the seeds.
+// Phase A of the drop-in sampler: per-CTA sum of min(deg, fanout) over the CTA's slice of the seeds.
 template <typename PtrT>
 __device__ __forceinline__ void phase_count_seeds(const KParams& p, const Hop& h, const Team& t, Smem& sm,
                                                   int32_t* team_sums) {
@@ -465,6 +545,20 @@ __device__ __forceinline__ void phase_count_seeds(const KParams& p, const Hop& h
     if (threadIdx.x == 0) __stcg(team_sums + t.rank, total);
 }
 
+// Phase A of the fused kernel: the same sum from the degrees cached when the nodes joined the list (coalesced);
+// also resets this CTA's count of first occurrences.
+__device__ __forceinline__ void phase_count_cached(const Hop& h, const Team& t, Smem& sm, int32_t* team_sums, int32_t* team_cnt) {
+    int s0, s1;
+    chunk_of(h.n_seeds, t.rank, t.size, s0, s1);
+    int acc = 0;
+    for (int s = s0 + (int)threadIdx.x; s < s1; s += kThreads) acc += min(__ldcg(h.node_deg + s), h.fanout);
+    const int total = block_sum(acc, sm.scan);
+    if (threadIdx.x == 0) {
+        __stcg(team_sums + t.rank, total);
+        __stcg(team_cnt + t.rank, 0);
+    }
+}
+
 // Sum of the team's partials before `rank` and over the whole team.
 __device__ __forceinline__ void team_prefix(const int32_t* team_sums, const Team& t, Smem& sm, int& before, int& total) {
     int a = 0, b = 0;
@@ -480,10 +574,20 @@ __device__ __forceinline__ void team_prefix(const int32_t* team_sums, const Team
 // Phase B: offsets, picks, source reads, table inserts.  Returns the CTA's first edge and edge count.
 template <typename PtrT, int MODE, bool ARRIVAL>
 __device__ __forceinline__ void phase_sample(const KParams& p, const Hop& h, const Table& tab, const Team& t,
-                                             Smem& sm, uint32_t* picks, const int32_t* team_sums, int& e0, int& e1,
-                                             int& e_total) {
+                                             Smem& sm, uint32_t* picks, const int32_t* team_sums, int32_t* team_cnt, int& e0,
+                                             int& e1, int& e_total) {
     int before, total;
-    team_prefix(team_sums, t, sm, before, total);
+    if (MODE == MODE_FUSED) {
+        // the edge ranges of all CTAs of the team (an edge number's owner is looked up when it is displaced)
+        const int x = (int)threadIdx.x < t.size ? __ldcg(team_sums + threadIdx.x) : 0;
+        const int excl = block_excl_scan(x, sm.scan, total);
+        if ((int)threadIdx.x < t.size) sm.prefix[threadIdx.x] = excl;
+        if (threadIdx.x == 0) sm.prefix[t.size] = total;
+        __syncthreads();
+        before = sm.prefix[t.rank];
+    } else {
+        team_prefix(team_sums, t, sm, before, total);
+    }
     e_total = total;
     int s0, s1;
     chunk_of(h.n_seeds, t.rank, t.size, s0, s1);
@@ -492,6 +596,7 @@ __device__ __forceinline__ void phase_sample(const KParams& p, const Hop& h, con
         if (h.blk_indptr) h.blk_indptr[h.n_seeds] = total;
     }
     int running = before;
+    int first_cnt = 0;
     e0 = before;
     for (int tile0 = s0; tile0 < s1; tile0 += kThreads) {
         const int s = tile0 + (int)threadIdx.x;
@@ -500,7 +605,12 @@ __device__ __forceinline__ void phase_sample(const KParams& p, const Hop& h, con
             const int v = __ldcg(h.nodes + s);
             long long start;
             int deg;
-            load_adj<PtrT>(p, v, start, deg);
+            if (MODE == MODE_FUSED) {
+                start = __ldcg(h.node_start + s);
+                deg = __ldcg(h.node_deg + s);
+            } else {
+                load_adj<PtrT>(p, v, start, deg);
+            }
             k = min(deg, h.fanout);
             sm.v[threadIdx.x] = v;
             sm.start[threadIdx.x] = start;
@@ -515,25 +625,133 @@ __device__ __forceinline__ void phase_sample(const KParams& p, const Hop& h, con
         __syncthreads();
         const int tile_n = min(kThreads, s1 - tile0);
         if (h.fanout <= 8)
-            sample_tile_groups<MODE, ARRIVAL, 8>(p, h, tab, sm, picks, tile0, tile_n);
+            sample_tile_groups<PtrT, MODE, ARRIVAL, 8>(p, h, tab, sm, t.size, team_cnt, tile0, tile_n, first_cnt);
         else if (h.fanout <= 16)
-            sample_tile_groups<MODE, ARRIVAL, 16>(p, h, tab, sm, picks, tile0, tile_n);
+            sample_tile_groups<PtrT, MODE, ARRIVAL, 16>(p, h, tab, sm, t.size, team_cnt, tile0, tile_n, first_cnt);
         else if (h.fanout <= kGroupPathMaxFanout)
-            sample_tile_groups<MODE, ARRIVAL, 32>(p, h, tab, sm, picks, tile0, tile_n);
+            sample_tile_groups<PtrT, MODE, ARRIVAL, 32>(p, h, tab, sm, t.size, team_cnt, tile0, tile_n, first_cnt);
         else
-            sample_tile_wide<MODE, ARRIVAL>(p, h, tab, sm, picks, tile0, tile_n);
+            sample_tile_wide<PtrT, MODE, ARRIVAL>(p, h, tab, sm, t.size, team_cnt, picks, tile0, tile_n, first_cnt);
         running += tile_total;
         __syncthreads();
     }
     e1 = running;
+    if (MODE == MODE_FUSED && !ARRIVAL) {
+        const int mine = block_sum(first_cnt, sm.scan);
+        if (threadIdx.x == 0 && mine != 0) atomicAdd(team_cnt + t.rank, mine);
+    }
 }
 
-__device__ __forceinline__ bool is_first(const Table& tab, int marker, int e) {
-    if (marker >= 0) return false;
-    const unsigned long long cur = ld_slot(tab.slots + (uint32_t)~marker);
-    return (uint32_t)cur == (kPending | (uint32_t)e);
+// ---- fused kernel, first-occurrence order ------------------------------------------------------------------------------
+// Phase D: the possibly-first edges that still hold their slot are the first occurrences.  Local ids in edge order;
+// the node, its adjacency offset and degree (unless this is the last hop) join the list; the edge entry becomes the id.
+// Eight consecutive edges per thread: two 128-bit loads of entries, then up to eight slot loads in flight.
+template <typename PtrT>
+__device__ __forceinline__ int phase_rank_tracked(const KParams& p, const Hop& h, const Table& tab, int32_t* edges, int e0, int e1,
+                                                  int n_before, const Team& t, Smem& sm, const int32_t* team_cnt) {
+    int before, total;
+    team_prefix(team_cnt, t, sm, before, total);
+    int running = n_before + before;
+    constexpr int kPer = 8;
+    for (int tile0 = e0 & ~3; tile0 < e1; tile0 += kPer * kThreads) {
+        const int eb = tile0 + kPer * (int)threadIdx.x;
+        int m[kPer];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int at = eb + 4 * half;
+            int4 x = make_int4(0, 0, 0, 0);
+            if (at + 3 >= e0 && at + 3 < e1) {
+                x = __ldcg(reinterpret_cast<const int4*>(edges + at));  // the row is 16-byte aligned
+            } else if (at < e1 && at + 3 >= e0) {  // the range's last entries: never read beyond e1
+                x.x = __ldcg(edges + at);
+                if (at + 1 < e1) x.y = __ldcg(edges + at + 1);
+                if (at + 2 < e1) x.z = __ldcg(edges + at + 2);
+            }
+            m[4 * half + 0] = x.x;
+            m[4 * half + 1] = x.y;
+            m[4 * half + 2] = x.z;
+            m[4 * half + 3] = x.w;
+        }
+        unsigned long long cur[kPer];
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+            const bool mine = eb + q >= e0 && eb + q < e1 && m[q] < 0 && ((~m[q]) & kTentative);
+            if (!mine) m[q] = 0;
+            cur[q] = mine ? ld_slot(tab.slots + ((~m[q]) & kSlotMask)) : 0ULL;
+        }
+        int firsts = 0;
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+            if (!(m[q] < 0 && (uint32_t)cur[q] == (kPending | (uint32_t)(eb + q)))) m[q] = 0;  // keep first occurrences
+            firsts += m[q] < 0 ? 1 : 0;
+        }
+        int tile_total;
+        int local = running + block_excl_scan(firsts, sm.scan, tile_total);
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+            if (m[q] < 0) {
+                const uint32_t pos = (uint32_t)((~m[q]) & kSlotMask);
+                const uint32_t key = (uint32_t)(cur[q] >> 32);
+                if ((int64_t)local < h.nodes_cap) {
+                    h.nodes[local] = (int)key;
+                    tab.slots[pos] = ((unsigned long long)key << 32) | (uint32_t)local;
+                    edges[eb + q] = local;
+                    if (!h.last_hop && (int64_t)local < h.deg_cap) {
+                        long long start;
+                        int deg;
+                        load_adj<PtrT>(p, (int)key, start, deg);
+                        __stcg(h.node_start + local, start);
+                        __stcg(h.node_deg + local, deg);
+                    }
+                } else {
+                    set_status(p.status, FGL_ERR_CAPACITY);
+                    tab.slots[pos] = ((unsigned long long)key << 32);
+                    edges[eb + q] = 0;
+                }
+                ++local;
+            }
+        }
+        running += tile_total;
+    }
+    return n_before + total;
 }
 
+// Phase E: the entries that are still pending take the local id their slot now holds.
+__device__ __forceinline__ void phase_relabel_tracked(const Table& tab, int32_t* edges, int e0, int e1) {
+    constexpr int kPer = 8;
+    for (int tile0 = e0 & ~3; tile0 < e1; tile0 += kPer * kThreads) {
+        const int eb = tile0 + kPer * (int)threadIdx.x;
+        int m[kPer];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int at = eb + 4 * half;
+            int4 x = make_int4(0, 0, 0, 0);
+            if (at + 3 >= e0 && at + 3 < e1) {
+                x = __ldcg(reinterpret_cast<const int4*>(edges + at));
+            } else if (at < e1 && at + 3 >= e0) {  // the range's last entries: never read beyond e1
+                x.x = __ldcg(edges + at);
+                if (at + 1 < e1) x.y = __ldcg(edges + at + 1);
+                if (at + 2 < e1) x.z = __ldcg(edges + at + 2);
+            }
+            m[4 * half + 0] = x.x;
+            m[4 * half + 1] = x.y;
+            m[4 * half + 2] = x.z;
+            m[4 * half + 3] = x.w;
+        }
+        unsigned long long cur[kPer];
+#pragma unroll
+        for (int q = 0; q < kPer; ++q) {
+            const bool mine = eb + q >= e0 && eb + q < e1 && m[q] < 0;
+            if (!mine) m[q] = 0;
+            cur[q] = mine ? ld_slot(tab.slots + ((~m[q]) & kSlotMask)) : 0ULL;
+        }
+#pragma unroll
+        for (int q = 0; q < kPer; ++q)
+            if (m[q] < 0) edges[eb + q] = (int)((uint32_t)cur[q] & ~kPending);
+    }
+}
+
+// ---- drop-in id map (fgl_map): counting pass, rank, relabel over entries that are local ids or ~slot --------------------
 // Phase C: number of first occurrences among the CTA's edges.
 __device__ __forceinline__ void phase_count_first(const Table& tab, const int32_t* edges, int e0, int e1, const Team& t,
                                                   Smem& sm, int32_t* team_sums) {
@@ -555,8 +773,8 @@ __device__ __forceinline__ void phase_count_first(const Table& tab, const int32_
 
 // Phase D: local ids in first-occurrence order; returns the new node count.
 __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, const int32_t* edges, int e0, int e1,
-                                          int32_t* nodes, int32_t* node_pos, int64_t nodes_cap, int n_before,
-                                          const Team& t, Smem& sm, const int32_t* team_sums) {
+                                          int32_t* nodes, int64_t nodes_cap, int n_before, const Team& t, Smem& sm,
+                                          const int32_t* team_sums) {
     int before, total;
     team_prefix(team_sums, t, sm, before, total);
     int running = n_before + before;
@@ -584,7 +802,6 @@ __device__ __forceinline__ int phase_rank(const KParams& p, const Table& tab, co
                 const uint32_t key = (uint32_t)(cur[q] >> 32);
                 if ((int64_t)local < nodes_cap) {
                     nodes[local] = (int)key;
-                    if (node_pos) node_pos[local] = (int)pos;
                     tab.slots[pos] = ((unsigned long long)key << 32) | (uint32_t)local;
                 } else {
                     set_status(p.status, FGL_ERR_CAPACITY);
@@ -613,20 +830,6 @@ __device__ __forceinline__ void phase_relabel(const Table& tab, int32_t* edges, 
     }
 }
 
-#ifdef FGL_PHASE_TIMING
-__device__ __forceinline__ void phase_stamp(const KParams& p, int team_id, const Team& t, int& slot) {
-    if (team_id == 0 && t.rank == 0 && threadIdx.x == 0 && slot < 500) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        p.dbg[slot] = now;
-    }
-    ++slot;
-}
-#define FGL_STAMP() phase_stamp(p, team_id, t, dbg_slot)
-#else
-#define FGL_STAMP()
-#endif
-
 // ----------------------------------------------------------------------------------------------
 // kernels
 // ----------------------------------------------------------------------------------------------
@@ -644,102 +847,99 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
     t.bar = p.barriers + (size_t)team_id * 16;
     t.status = p.status;
     int32_t* team_sums = p.team_sums + (size_t)team_id * p.team_size;
+    int32_t* team_cnt = p.team_cnt + (size_t)team_id * p.team_size;
     Table tab;
     tab.slots = p.table + (size_t)team_id * (size_t)p.table_slots;
     tab.mask = (uint32_t)(p.table_slots - 1);
     tab.shift = p.table_shift;
 
-#ifdef FGL_PHASE_TIMING
-    int dbg_slot = 0;
-#endif
     for (int b = team_id; b < p.n_batches; b += p.n_teams) {
-        FGL_STAMP();  // batch start
         Hop h;
         h.nodes = p.nodes + (size_t)b * p.nodes_stride;
         h.nodes_cap = p.nodes_stride;
         h.counts = p.counts + (size_t)b * FGL_COUNTS_STRIDE;
         h.out_dst = p.out_dst;
+        h.node_start = nullptr;
+        h.node_deg = nullptr;
+        h.deg_cap = 0;
         int n0 = p.seed_counts ? __ldg(p.seed_counts + b) : p.n_seeds_host;
         n0 = max(0, min(n0, (int)min((int64_t)0x7fffffff, p.seed_stride)));
         const int32_t* seeds = p.seeds + (size_t)b * p.seed_stride;
 
         if (MODE == MODE_FUSED) {
-            // The team's table is empty here: the host cleared it once and every mini-batch removes its own
-            // entries at the end.  Insert the seeds with local id = position and remember their slots.
-            h.node_pos = p.node_pos + (size_t)team_id * p.nodes_stride;
+            // The team's table is empty here: the host cleared it once and every mini-batch clears it again at its
+            // end.  Insert the seeds with local id = position; cache their adjacency offsets and degrees.
+            h.node_start = p.node_start + (size_t)team_id * p.deg_stride;
+            h.node_deg = p.node_deg + (size_t)team_id * p.deg_stride;
+            h.deg_cap = p.deg_stride;
             if (t.rank == 0 && threadIdx.x < FGL_COUNTS_STRIDE) h.counts[threadIdx.x] = threadIdx.x == 0 ? n0 : 0;
             int s0, s1;
             chunk_of(n0, t.rank, t.size, s0, s1);
             for (int s = s0 + (int)threadIdx.x; s < s1; s += kThreads) {
                 const int v = seeds[s];
                 h.nodes[s] = v;
-                int pos = -1;
-                if (v < 0 || (int64_t)v >= p.n_nodes)
+                long long start = 0;
+                int deg = 0;
+                if (v < 0 || (int64_t)v >= p.n_nodes) {
                     set_status(p.status, FGL_ERR_BOUNDS);
-                else
-                    pos = table_insert_seed(tab, (uint32_t)v, (uint32_t)s, p.status);
-                h.node_pos[s] = pos;
+                } else {
+                    table_insert_seed(tab, (uint32_t)v, (uint32_t)s, p.status);
+                    load_adj<PtrT>(p, v, start, deg);
+                }
+                __stcg(h.node_start + s, start);
+                __stcg(h.node_deg + s, deg);
             }
-            // the same CTA reads nodes[s0..s1) in phase A, so no barrier is needed before it; the
-            // barrier after phase A orders the seed inserts before the first source insert
+            // the same CTA (the same thread, even) reads these entries back in phases A and B of the first hop, so no
+            // barrier is needed before them; the barrier after phase A orders the seed inserts before the first
+            // source insert
         } else {
-            h.node_pos = nullptr;
             h.nodes = const_cast<int32_t*>(seeds);  // MODE_SAMPLE reads the seeds in place
         }
 
         int n_cur = n0;
         for (int hop = 0; hop < p.n_hops; ++hop) {
             h.hop = hop;
+            h.last_hop = hop + 1 == p.n_hops;
             h.fanout = p.fanout[hop];
             h.n_seeds = n_cur;
             h.ctr = p.rng_ctr + (uint64_t)b * 8u + (uint64_t)hop;
             h.blk_indptr = p.blk_indptr[hop] ? p.blk_indptr[hop] + (size_t)b * p.blk_indptr_stride[hop] : nullptr;
             h.blk_src = p.blk_src[hop] + (size_t)b * p.blk_src_stride[hop];
 
-            FGL_STAMP();  // A start
-            phase_count_seeds<PtrT>(p, h, t, sm, team_sums);
+            if (MODE == MODE_FUSED)
+                phase_count_cached(h, t, sm, team_sums, team_cnt);
+            else
+                phase_count_seeds<PtrT>(p, h, t, sm, team_sums);
             if (MODE == MODE_FUSED && ARRIVAL && t.rank == 0 && threadIdx.x == 0) h.counts[hop + 1] = n_cur;
-            FGL_STAMP();  // A done
             if (!team_barrier(t, &sm.flag)) return;
-            FGL_STAMP();  // barrier 1 done
 
             int e0, e1, e_total;
-            phase_sample<PtrT, MODE, ARRIVAL>(p, h, tab, t, sm, picks, team_sums, e0, e1, e_total);
+            phase_sample<PtrT, MODE, ARRIVAL>(p, h, tab, t, sm, picks, team_sums, team_cnt, e0, e1, e_total);
             if (MODE == MODE_SAMPLE) break;
-            FGL_STAMP();  // B done
             if (!team_barrier(t, &sm.flag)) return;
-            FGL_STAMP();  // barrier 2 done
 
             if (!ARRIVAL) {
-                phase_count_first(tab, h.blk_src, e0, e1, t, sm, team_sums);
-                FGL_STAMP();  // C done
-                if (!team_barrier(t, &sm.flag)) return;
-                FGL_STAMP();  // barrier 3 done
-                n_cur = phase_rank(p, tab, h.blk_src, e0, e1, h.nodes, h.node_pos, h.nodes_cap, n_cur, t, sm, team_sums);
+                n_cur = phase_rank_tracked<PtrT>(p, h, tab, h.blk_src, e0, e1, n_cur, t, sm, team_cnt);
                 n_cur = (int)min((int64_t)n_cur, h.nodes_cap);
                 if (t.rank == 0 && threadIdx.x == 0) h.counts[hop + 1] = n_cur;
-                FGL_STAMP();  // D done
                 if (!team_barrier(t, &sm.flag)) return;
-                FGL_STAMP();  // barrier 4 done
+                phase_relabel_tracked(tab, h.blk_src, e0, e1);
             } else {
                 n_cur = (int)min((int64_t)__ldcg(h.counts + hop + 1), h.nodes_cap);
+                phase_relabel(tab, h.blk_src, e0, e1);
             }
-            phase_relabel(tab, h.blk_src, e0, e1);
-            FGL_STAMP();  // E done
-            // the next hop's phase A only reads nodes[] (complete since the last barrier); its barrier
-            // keeps the next inserts behind every CTA's relabel reads
+            // the next hop's phase A only reads the degrees cached before the last barrier; its barrier keeps the
+            // next inserts behind every CTA's relabel reads
         }
         if (MODE == MODE_SAMPLE) break;
-        // Clean-up walk: once every CTA has finished reading the table, empty exactly the slots this
-        // mini-batch filled (16 MB of table stay untouched and L2-resident instead of being rewritten).
+        // Once every CTA has finished reading the table, clear it for the next mini-batch: a coalesced sweep of the
+        // team's (L2-resident) slots.
         if (!team_barrier(t, &sm.flag)) return;
         {
-            int c0, c1;
-            chunk_of(n_cur, t.rank, t.size, c0, c1);
-            for (int i = c0 + (int)threadIdx.x; i < c1; i += kThreads) {
-                const int pos = __ldcg(h.node_pos + i);
-                if (pos >= 0) tab.slots[pos] = kEmpty;
-            }
+            const int64_t vecs = p.table_slots / 2;  // two slots per 128-bit store
+            uint4* base = reinterpret_cast<uint4*>(tab.slots);
+            const uint4 ones = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+            for (int64_t i = (int64_t)t.rank * kThreads + threadIdx.x; i < vecs; i += (int64_t)t.size * kThreads) base[i] = ones;
         }
         if (b + p.n_teams < p.n_batches) {
             if (!team_barrier(t, &sm.flag)) return;
@@ -765,6 +965,7 @@ __global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant_
     const int n_seeds = p.n_seeds_host;
     const int n_edges = (int)p.map_edges;
     int32_t* unique = p.nodes;
+    const int64_t nodes_cap = p.nodes_stride;
 
     int s0, s1;
     chunk_of(n_seeds, t.rank, t.size, s0, s1);
@@ -781,19 +982,13 @@ __global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant_
 
     int e0, e1;
     chunk_of(n_edges, t.rank, t.size, e0, e1);
-    Hop h;
-    h.nodes = unique;
-    h.nodes_cap = p.nodes_stride;
-    h.counts = p.counts;
-    h.hop = 0;
-    h.blk_src = p.map_src;
     for (int e = e0 + (int)threadIdx.x; e < e1; e += kThreads) {
         const int g = p.map_src[e];
         if (g < 0) {
             set_status(p.status, FGL_ERR_BOUNDS);
             p.map_src[e] = 0;
         } else {
-            // same path as the fused kernel; n_nodes is not known here
+            // same table as the fused kernel; n_nodes is not known here
             bool created;
             int r = table_insert<ARRIVAL>(tab, (uint32_t)g, (uint32_t)e, p.status, created);
             if (ARRIVAL && created) {
@@ -803,7 +998,7 @@ __global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant_
                 base = grp.shfl(base, 0);
                 const int local = base + (int)grp.thread_rank();
                 const uint32_t pos = (uint32_t)~r;
-                if ((int64_t)local < h.nodes_cap) {
+                if ((int64_t)local < nodes_cap) {
                     unique[local] = g;
                     atomicExch(tab.slots + pos, ((unsigned long long)(uint32_t)g << 32) | (uint32_t)local);
                     r = local;
@@ -825,8 +1020,8 @@ __global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant_
     if (!ARRIVAL) {
         phase_count_first(tab, p.map_src, e0, e1, t, sm, team_sums);
         if (!team_barrier(t, &sm.flag)) return;
-        const int n_total = phase_rank(p, tab, p.map_src, e0, e1, unique, nullptr, h.nodes_cap, n_seeds, t, sm, team_sums);
-        if (t.rank == 0 && threadIdx.x == 0) p.counts[1] = (int)min((int64_t)n_total, h.nodes_cap);
+        const int n_total = phase_rank(p, tab, p.map_src, e0, e1, unique, nodes_cap, n_seeds, t, sm, team_sums);
+        if (t.rank == 0 && threadIdx.x == 0) p.counts[1] = (int)min((int64_t)n_total, nodes_cap);
         if (!team_barrier(t, &sm.flag)) return;
     }
     phase_relabel(tab, p.map_src, e0, e1);
@@ -870,24 +1065,27 @@ static int launch_coop(Workspace* ws, K kernel, int grid, size_t dyn_smem, KPara
     return FGL_OK;
 }
 
-// scratch layout: [barriers: n_teams * 16 u64][team_sums: n_teams * team_size i32][counts: 16 i32]
-//                 [node_pos: n_teams * nodes_stride i32]; only the part before node_pos is zeroed per call
-static int64_t scratch_head(int n_teams, int grid) { return (int64_t)n_teams * 128 + (((int64_t)grid * 4 + 127) / 128) * 128 + 128; }
+// scratch layout: [barriers: n_teams * 16 u64][team_sums: grid i32][team_cnt: grid i32][counts: 16 i32]
+//                 [node_start: n_teams * deg_stride i64][node_deg: n_teams * deg_stride i32]
+// Only the part before node_start is zeroed per call.
+static int64_t sums_bytes(int grid) { return (((int64_t)grid * 4 + 127) / 128) * 128; }
 
-static int64_t scratch_need(int n_teams, int grid, int64_t nodes_stride = 0) {
-    return scratch_head(n_teams, grid) + (int64_t)n_teams * nodes_stride * 4;
+static int64_t scratch_head(int n_teams, int grid) { return (int64_t)n_teams * 128 + 2 * sums_bytes(grid) + 128; }
+
+static int64_t scratch_need(int n_teams, int grid, int64_t deg_stride = 0) {
+    return scratch_head(n_teams, grid) + (int64_t)n_teams * deg_stride * 12;
 }
 
-static void place_scratch(Workspace* ws, KParams& kp, int n_teams, int grid, int32_t** call_counts) {
+static void place_scratch(Workspace* ws, KParams& kp, int n_teams, int grid, int64_t deg_stride, int32_t** call_counts) {
     char* base = ws->scratch;
     kp.barriers = (unsigned long long*)base;
     kp.team_sums = (int32_t*)(base + (size_t)n_teams * 128);
+    kp.team_cnt = (int32_t*)(base + (size_t)n_teams * 128 + sums_bytes(grid));
     if (call_counts) *call_counts = (int32_t*)(base + scratch_head(n_teams, grid) - 128);
-    kp.node_pos = (int32_t*)(base + scratch_head(n_teams, grid));
+    kp.node_start = (long long*)(base + scratch_head(n_teams, grid));
+    kp.node_deg = (int32_t*)(base + scratch_head(n_teams, grid) + (size_t)n_teams * deg_stride * 8);
+    kp.deg_stride = deg_stride;
     kp.status = ws->status;
-#ifdef FGL_PHASE_TIMING
-    kp.dbg = (unsigned long long*)(ws->status + 16);
-#endif
 }
 
 template <int MODE>
@@ -906,11 +1104,9 @@ static int occupancy_sample_map(Workspace* ws, bool is64, bool arrival, size_t d
 #undef FGL_OCC
 }
 
-// dynamic shared memory: a row of picks per seed of a tile (fanout <= 32) or per warp (wider fanouts)
+// dynamic shared memory: a row of picks per warp for fanouts beyond 32 (narrower fanouts keep their picks in registers)
 static size_t picks_smem(int max_fanout) {
-    const size_t per_seed = (size_t)kThreads * (std::min(max_fanout, kGroupPathMaxFanout) | 1) * sizeof(uint32_t);
-    const size_t per_warp = max_fanout > kGroupPathMaxFanout ? (size_t)kWarps * max_fanout * sizeof(uint32_t) : 0;
-    return std::max(per_seed, per_warp);
+    return max_fanout > kGroupPathMaxFanout ? (size_t)kWarps * max_fanout * sizeof(uint32_t) : 0;
 }
 
 }  // namespace fgl
@@ -953,7 +1149,7 @@ int fgl_sample(fgl_ws* ws, const void* indptr, int indptr_is_64, const int32_t* 
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
     int32_t* call_counts = nullptr;
-    place_scratch(ws, kp, 1, grid, &call_counts);
+    place_scratch(ws, kp, 1, grid, 0, &call_counts);
     kp.indptr = indptr;
     kp.indices = indices;
     kp.n_nodes = n_nodes;
@@ -1019,7 +1215,7 @@ int fgl_map(fgl_ws* ws, int32_t* src, int32_t* dst, const int32_t* seeds, int32_
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
     int32_t* call_counts = nullptr;
-    place_scratch(ws, kp, 1, grid, &call_counts);
+    place_scratch(ws, kp, 1, grid, 0, &call_counts);
     kp.n_nodes = 0x7fffffff;
     kp.flags = flags;
     kp.n_teams = 1;
@@ -1055,13 +1251,6 @@ int fgl_map(fgl_ws* ws, int32_t* src, int32_t* dst, const int32_t* seeds, int32_
     return FGL_OK;
 }
 
-#ifdef FGL_PHASE_TIMING
-// Instrumented builds only: copies the phase timestamps (ns) of team 0 / CTA 0 of the last fused launch.
-int fgl_debug_phase_times(fgl_ws* ws, unsigned long long* out, int n) {
-    return cudaMemcpy(out, ws->status + 16, sizeof(unsigned long long) * (size_t)n, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 2;
-}
-#endif
-
 int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     if (!ws || !a || !a->indptr || !a->indices || a->n_nodes <= 0 || a->n_batches < 0 || a->n_hops < 1 ||
         a->n_hops > FGL_MAX_HOPS || !a->seeds || !a->seed_counts || !a->nodes || !a->counts || a->seed_stride < 0)
@@ -1079,6 +1268,9 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
             return FGL_ERR_INVALID;
     }
     if (a->nodes_stride < cap[a->n_hops]) return FGL_ERR_INVALID;
+    for (int h = 0; h < a->n_hops; ++h)   // the relabelling passes read and write the edge entries four at a time
+        if (((uintptr_t)a->block_src[h] & 15) != 0 || a->block_src_stride[h] % 4 != 0) return FGL_ERR_INVALID;
+    const int64_t deg_stride = (cap[a->n_hops - 1] + 31) / 32 * 32;   // nodes that can still become seeds
     std::lock_guard<std::mutex> lock(ws->mu);
     DeviceGuard guard(ws->device);
     cudaStream_t st = (cudaStream_t)stream;
@@ -1096,8 +1288,9 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     // if it fills up the launch reports FGL_ERR_PROBE and the caller retries without a hint)
     int64_t slots = pow2_at_least(cap[a->n_hops] + cap[a->n_hops] / 2 + 1);
     if (a->table_slots_hint > 0) slots = std::min(slots, pow2_at_least(a->table_slots_hint));
-    if (slots > (1LL << 31)) return FGL_ERR_CAPACITY;
-    rc = ws_ensure(ws, slots * n_teams, scratch_need(n_teams, grid, a->nodes_stride));
+    if (slots > (1LL << 29)) return FGL_ERR_CAPACITY;   // pending edge entries keep a slot number in 29 bits
+    if (team_size > kMaxTeam) return FGL_ERR_INVALID;
+    rc = ws_ensure(ws, slots * n_teams, scratch_need(n_teams, grid, deg_stride));
     if (rc != FGL_OK) return rc;
     if (ws->table_dirty) {
         FGL_CUDA_OK(ws, cudaMemsetAsync(ws->table, 0xFF, sizeof(unsigned long long) * (size_t)ws->table_slots, st));
@@ -1105,7 +1298,7 @@ int fgl_sample_map_fused(fgl_ws* ws, const fgl_fused_args* a, void* stream) {
     }
     KParams kp;
     std::memset(&kp, 0, sizeof(kp));
-    place_scratch(ws, kp, n_teams, grid, nullptr);
+    place_scratch(ws, kp, n_teams, grid, deg_stride, nullptr);
     kp.indptr = a->indptr;
     kp.indices = a->indices;
     kp.n_nodes = a->n_nodes;
