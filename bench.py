@@ -327,15 +327,18 @@ def run_sharded_leg(cfg, args, tr, indptr, rank, world, device, barrier, max_ove
             rows = fb.nodes[b].long()[fb.block_src[hop][b, :n_e].long()]
             remote_edges += int(((rows // rps) != rank).sum())
             edges += n_e
-        ms = max_over_ranks(statistics.median(times))
+        my_ms = statistics.median(times)
+        ms = max_over_ranks(my_ms)
         all_equal = max_over_ranks(0.0 if equal else 1.0) == 0.0
-        remote_gbs = remote_edges * D * 4 / (ms * 1e-3) / 1e9
+        # NVLink ingress of the busiest rank: its own remote bytes over its own launch time
+        remote_gbs = max_over_ranks(remote_edges * D * 4 / (my_ms * 1e-3) / 1e9)
         out = {"status": "ok" if all_equal else "mismatch", "table": f"{n} rows x {D} fp32, {world} shards of {rps} rows",
-               "window_rows": total, "window_edges": edges, "launch_ms": ms, "remote_edge_fraction": remote_edges / max(1, edges),
+               "window_rows": total, "window_edges": edges, "launch_ms": ms,
+               "remote_edge_fraction_max": max_over_ranks(remote_edges / max(1, edges)),
                "remote_gb_per_s_per_gpu": remote_gbs, "nvlink_peak_gb_per_s": 900.0, "frac_of_nvlink": remote_gbs / 900.0,
                "equal_to_local_copy": all_equal,
-               "note": "rank 0's remote bytes over the slowest rank's median launch time; rows a window re-reads are "
-                       "served by this GPU's L2, so the figure can exceed the link rate"}
+               "note": "largest over the ranks of (a rank's remote row bytes / its median launch time); rows a window re-reads "
+                       "are served by the reading GPU's L2, so the figure can exceed the link rate"}
     got = want = fb = None
     # nobody unmaps a shard while a peer may still read it
     torch.cuda.synchronize()
