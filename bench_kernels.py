@@ -198,7 +198,17 @@ def run(indptr, indices, feat, train, fanouts, batch: int, window: int, peak_gbs
         ms = _timed(lambda i: res.__setitem__("dx", fastgl.aggregate_backward(fastgl.AGG_MEAN, ptr_b, src_b, dy, n_src0)), reps, flush)
         entry("agg_bwd_kernel mean (fgl_agg_bwd)", f"{n_dst0} gradient rows scattered over {n_e0} edges into {n_src0} rows, D={dim}",
               4 * dim * (n_dst0 + n_src0) + 4 * n_e0 + 4 * (n_dst0 + 1), ms, note="includes zero-filling the result")
-        del x, y, dy
+        tb = fastgl.transpose_block(ptr_b, src_b, n_dst0, n_src0)
+        dxg = torch.empty((n_src0, dim), device=dev)
+        ms = _timed(lambda i: fastgl.aggregate_backward(fastgl.AGG_MEAN, ptr_b, src_b, dy, n_src0, transposed=tb, out=dxg), reps, flush)
+        entry("agg_bwd_gather_kernel mean (fgl_agg_bwd_gather)", f"{n_dst0} gradient rows gathered over {n_e0} edges into {n_src0} rows, "
+              f"D={dim}", 4 * dim * (n_dst0 + n_src0) + 8 * n_e0 + 4 * (n_src0 + 1), ms,
+              note="deterministic; no zero-fill; the transposition is timed separately")
+        if dim == dims[0]:
+            ms = _timed(lambda i: fastgl.transpose_block(ptr_b, src_b, n_dst0, n_src0, out=tb), reps, flush)
+            entry("block transposition (fgl_block_transpose)", f"{n_e0} edges, {n_src0} sources", 12 * n_e0 + 12 * n_src0, ms,
+                  note="histogram, scan, fill, hub list: once per block, whatever the row width")
+        del x, y, dy, dxg, tb
         res.pop("dx", None)
 
     # ---- row gather -----------------------------------------------------------------------------------------

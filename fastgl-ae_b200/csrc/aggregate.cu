@@ -1149,3 +1149,342 @@ int fgl_agg_bwd_self(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int3
 }
 
 }  // extern "C"
+
+// ================================================================================================================
+// Backward as a gather over the transposed block CSR (deterministic, no atomics on the gradient, no zero-fill pass)
+// ================================================================================================================
+// The scatter above adds every edge's contribution with a vector reduction: its speed is the L2's reduction rate
+// and the order of the additions -- hence the last bits of the result -- changes from run to run.  Here the block is
+// transposed once (per-source lists of destination rows: histogram, scan, fill) and every gradient row dx[s] is
+// then produced by exactly one warp (sources with at most 32 in-block out-edges) or one CTA (hubs), which adds the
+// rows dy[d] of its list in ascending order of d.  The order is a property of the block, not of the schedule, so two
+// runs give the same bits; dx[s] is written once, with the self term folded in, so it needs no initialisation.
+// Replaces K9 / K11 (aggregate_acc_kernel.cu:468-517, :555-596) like agg_bwd_kernel does.
+namespace fgl {
+
+struct GatherParams {
+    const int32_t* indptr;    // block CSR over destinations (mean weights)
+    const int32_t* t_indptr;  // transposed: per source, [n_src + 1]
+    const int32_t* t_dst;     // destination rows, grouped by source (order within a group: arbitrary)
+    const int32_t* hubs;      // [0] number of sources with more than 32 entries, then their ids
+    const int32_t* src_deg;
+    const int32_t* dst_deg;
+    const float* dy;
+    const float* dy_self;
+    float* dx;
+    int64_t ldy, ld_self, ldx;
+    int32_t dim, n_dst, n_src;
+    const int32_t* n_dst_dev;
+};
+
+constexpr int kHubThreshold = 32;
+
+template <int MODE>
+__device__ __forceinline__ float gather_weight(const GatherParams& p, int d) {
+    if (MODE == FGL_AGG_MEAN) return 1.0f / (float)(__ldg(p.indptr + d + 1) - __ldg(p.indptr + d));
+    if (MODE == FGL_AGG_SYMNORM) return 1.0f / sqrtf((float)__ldg(p.dst_deg + d));
+    return 1.0f;
+}
+
+// Histogram of the sources (pass 0) and placement of every edge's destination row behind its source's cursor (pass 1).
+__global__ void __launch_bounds__(256) transpose_edges_kernel(const int32_t* __restrict__ indptr, const int32_t* __restrict__ src,
+                                                              int n_dst, int n_src, const int32_t* __restrict__ n_dst_dev,
+                                                              int32_t* __restrict__ cnt, const int32_t* __restrict__ t_indptr,
+                                                              int32_t* __restrict__ cursor, int32_t* __restrict__ t_dst,
+                                                              int64_t t_cap, int32_t* __restrict__ status, int pass) {
+    const int lane = threadIdx.x & 31;
+    const int warp_global = blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = gridDim.x * 8;
+    if (n_dst_dev) n_dst = min(max(__ldg(n_dst_dev), 0), n_dst);
+    for (int d = warp_global; d < n_dst; d += n_warps) {
+        const int a = __ldg(indptr + d), b = __ldg(indptr + d + 1);
+        for (int e = a + lane; e < b; e += 32) {
+            const int s = __ldg(src + e);
+            if (s < 0 || s >= n_src) {
+                if (status) set_status(status, FGL_ERR_BOUNDS);
+                continue;
+            }
+            if (pass == 0) {
+                atomicAdd(cnt + s, 1);
+            } else {
+                const int64_t at = (int64_t)__ldg(t_indptr + s) + atomicAdd(cursor + s, 1);
+                if (at < t_cap) t_dst[at] = d;
+                else if (status) set_status(status, FGL_ERR_CAPACITY);
+            }
+        }
+    }
+}
+
+// The list of hubs: sources with more than kHubThreshold entries.  hubs[0] was zeroed by the host.
+__global__ void __launch_bounds__(256) list_hubs_kernel(const int32_t* __restrict__ t_indptr, int n_src, int32_t* __restrict__ hubs) {
+    for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < n_src; s += gridDim.x * blockDim.x)
+        if (__ldg(t_indptr + s + 1) - __ldg(t_indptr + s) > kHubThreshold) hubs[1 + atomicAdd(hubs, 1)] = s;
+}
+
+__device__ __forceinline__ int warp_sort_ascending(int v, int lane) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const int other = __shfl_xor_sync(0xffffffffu, v, j);
+            const bool up = (lane & k) == 0, lower = (lane & j) == 0;
+            v = (lower == up) ? min(v, other) : max(v, other);
+        }
+    }
+    return v;
+}
+
+// A warp per source row with at most 32 entries: sort the destination rows, add them in that order.
+template <int VEC, int MODE, int NACC>
+__global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams p) {
+    using V = Vec<VEC>;
+    using T = typename V::T;
+    constexpr int UNR = NACC == 1 ? 8 : (NACC == 2 ? 4 : 2);
+    const int lane = threadIdx.x & 31;
+    const int warp_global = blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = gridDim.x * 8;
+    const int chunks = p.dim / VEC;
+    const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
+    for (int s = warp_global; s < p.n_src; s += n_warps) {
+        const int a = __ldg(p.t_indptr + s), deg = __ldg(p.t_indptr + s + 1) - a;
+        if (deg > kHubThreshold) continue;  // a CTA of agg_bwd_hub_kernel owns this row
+        int d = lane < deg ? __ldg(p.t_dst + a + lane) : 0x7fffffff;
+        d = warp_sort_ascending(d, lane);
+        const float w = lane < deg ? gather_weight<MODE>(p, d) : 0.0f;
+        const float ws = (MODE == FGL_AGG_SYMNORM && deg > 0) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
+        const bool self = p.dy_self != nullptr && s < n_dst;
+        const T* self_row = reinterpret_cast<const T*>(p.dy_self + (self ? (int64_t)s * p.ld_self : 0));
+        T* out = reinterpret_cast<T*>(p.dx + (int64_t)s * p.ldx);
+        for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
+            T acc[NACC];
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
+            for (int j0 = 0; j0 < deg; j0 += UNR) {
+                T v[UNR][NACC];
+                float wj[UNR];
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int j = min(j0 + u, deg - 1);
+                    const int dj = __shfl_sync(0xffffffffu, d, j);
+                    wj[u] = __shfl_sync(0xffffffffu, w, j);
+                    const T* row = reinterpret_cast<const T*>(p.dy + (int64_t)dj * p.ldy);
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k) {
+                        const int c = c0 + k * 32 + lane;
+                        v[u][k] = c < chunks ? __ldg(row + c) : V::zero();
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNR; ++u)
+                    if (j0 + u < deg) {
+#pragma unroll
+                        for (int k = 0; k < NACC; ++k) V::fma(acc[k], wj[u], v[u][k]);
+                    }
+            }
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) {
+                const int c = c0 + k * 32 + lane;
+                if (c < chunks) {
+                    T r = (MODE == FGL_AGG_SYMNORM) ? V::scale(acc[k], ws) : acc[k];
+                    if (self) V::fma(r, 1.0f, __ldg(self_row + c));
+                    out[c] = r;
+                }
+            }
+        }
+    }
+}
+
+// A CTA per hub.  The hub's destination rows are counted into a shared-memory array over a window of the destination
+// range (16-bit counts, two per word), which orders them without sorting; warp k then adds the rows of the k-th eighth
+// of the window in ascending order, and the eight partial sums are folded in a fixed order.
+constexpr int kHubWindow = 32768;
+
+template <int VEC, int MODE, int NACC>
+__global__ void __launch_bounds__(256) agg_bwd_hub_kernel(const GatherParams p) {
+    using V = Vec<VEC>;
+    using T = typename V::T;
+    extern __shared__ __align__(16) unsigned char hub_smem[];
+    uint32_t* cnt32 = reinterpret_cast<uint32_t*>(hub_smem);                            // kHubWindow / 2 words
+    T* part = reinterpret_cast<T*>(hub_smem + kHubWindow * 2);                           // [8][NACC][32]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = p.dim / VEC;
+    const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
+    const int n_hubs = min(__ldg(p.hubs), p.n_src);
+    constexpr int UNR = 4;
+    for (int h = blockIdx.x; h < n_hubs; h += gridDim.x) {
+        const int s = __ldg(p.hubs + 1 + h);
+        const int a = __ldg(p.t_indptr + s), b = __ldg(p.t_indptr + s + 1);
+        const float ws = (MODE == FGL_AGG_SYMNORM) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
+        const bool self = p.dy_self != nullptr && s < n_dst;
+        for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
+            T total[NACC];  // warp 0 keeps the row's running sum over the windows
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) total[k] = V::zero();
+            for (int w0 = 0; w0 < n_dst; w0 += kHubWindow) {
+                for (int i = threadIdx.x; i < kHubWindow / 2; i += 256) cnt32[i] = 0u;
+                __syncthreads();
+                for (int e = a + (int)threadIdx.x; e < b; e += 256) {
+                    const int off = __ldg(p.t_dst + e) - w0;
+                    if (off >= 0 && off < kHubWindow) atomicAdd(cnt32 + (off >> 1), 1u << (16 * (off & 1)));
+                }
+                __syncthreads();
+                T acc[NACC];
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
+                const int lo = warp * (kHubWindow / 8), hi = min(lo + kHubWindow / 8, n_dst - w0);
+                for (int base = lo; base < hi; base += 32) {
+                    const uint32_t word = cnt32[(base + lane) >> 1];
+                    const int c = (int)((word >> (16 * ((base + lane) & 1))) & 0xffffu);
+                    unsigned m = __ballot_sync(0xffffffffu, c > 0);
+                    while (m) {  // warp-uniform
+                        int dd[UNR];
+                        float wd[UNR];
+                        T v[UNR][NACC];
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                            dd[u] = -1;
+                            wd[u] = 0.0f;
+                            if (m) {
+                                const int j = __ffs(m) - 1;
+                                m &= m - 1;
+                                dd[u] = w0 + base + j;
+                                wd[u] = (float)__shfl_sync(0xffffffffu, c, j);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                            const int dj = dd[u] < 0 ? 0 : dd[u];
+                            if (dd[u] >= 0) wd[u] *= gather_weight<MODE>(p, dj);
+                            const T* row = reinterpret_cast<const T*>(p.dy + (int64_t)dj * p.ldy);
+#pragma unroll
+                            for (int k = 0; k < NACC; ++k) {
+                                const int cc = c0 + k * 32 + lane;
+                                v[u][k] = cc < chunks ? __ldg(row + cc) : V::zero();
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u)
+                            if (dd[u] >= 0) {
+#pragma unroll
+                                for (int k = 0; k < NACC; ++k) V::fma(acc[k], wd[u], v[u][k]);
+                            }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) part[(warp * NACC + k) * 32 + lane] = acc[k];
+                __syncthreads();
+                if (warp == 0) {
+                    for (int q = 0; q < 8; ++q)
+#pragma unroll
+                        for (int k = 0; k < NACC; ++k) V::fma(total[k], 1.0f, part[(q * NACC + k) * 32 + lane]);
+                }
+                __syncthreads();
+            }
+            if (warp == 0) {
+                T* out = reinterpret_cast<T*>(p.dx + (int64_t)s * p.ldx);
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) {
+                    const int c = c0 + k * 32 + lane;
+                    if (c < chunks) {
+                        T r = (MODE == FGL_AGG_SYMNORM) ? V::scale(total[k], ws) : total[k];
+                        if (self) V::fma(r, 1.0f, __ldg(reinterpret_cast<const T*>(p.dy_self + (int64_t)s * p.ld_self) + c));
+                        out[c] = r;
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int VEC, int MODE>
+static void launch_gather_nacc(const GatherParams& p, int sms, cudaStream_t st) {
+    const int chunks = p.dim / VEC;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(((int64_t)p.n_src + 7) / 8, (int64_t)sms * 8));
+    const int hub_grid = 2 * sms;
+#define FGL_GATHER(NACC)                                                                                           \
+    {                                                                                                              \
+        const size_t dyn = (size_t)kHubWindow * 2 + sizeof(typename Vec<VEC>::T) * 8 * NACC * 32;                  \
+        agg_bwd_gather_kernel<VEC, MODE, NACC><<<grid, 256, 0, st>>>(p);                                           \
+        cudaFuncSetAttribute(agg_bwd_hub_kernel<VEC, MODE, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
+        agg_bwd_hub_kernel<VEC, MODE, NACC><<<hub_grid, 256, dyn, st>>>(p);                                        \
+    }
+    if (chunks <= 32) FGL_GATHER(1)
+    else if (chunks <= 64) FGL_GATHER(2)
+    else FGL_GATHER(4)
+#undef FGL_GATHER
+}
+
+template <int VEC>
+static void launch_gather_mode(int mode, const GatherParams& p, int sms, cudaStream_t st) {
+    if (mode == FGL_AGG_SUM) launch_gather_nacc<VEC, FGL_AGG_SUM>(p, sms, st);
+    if (mode == FGL_AGG_MEAN) launch_gather_nacc<VEC, FGL_AGG_MEAN>(p, sms, st);
+    if (mode == FGL_AGG_SYMNORM) launch_gather_nacc<VEC, FGL_AGG_SYMNORM>(p, sms, st);
+}
+
+}  // namespace fgl
+
+extern "C" {
+
+int fgl_block_transpose(fgl_ws* ws, const int32_t* indptr, const int32_t* src, int32_t n_dst, int32_t n_src, int32_t* t_indptr,
+                        int32_t* t_dst, int64_t t_cap, int32_t* hubs, int32_t* work, const int32_t* n_dst_dev, void* stream) {
+    if (!ws || n_dst < 0 || n_src < 0 || t_cap < 0) return FGL_ERR_INVALID;
+    if (!t_indptr || !hubs || (n_src > 0 && !work) || (t_cap > 0 && !t_dst) || (n_dst > 0 && (!indptr || !src))) return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    int sms = ws->sm_count > 0 ? ws->sm_count : 148;
+    if (cudaMemsetAsync(hubs, 0, sizeof(int32_t), st) != cudaSuccess) return FGL_ERR_CUDA;
+    if (n_src == 0) return cudaMemsetAsync(t_indptr, 0, sizeof(int32_t), st) == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+    if (cudaMemsetAsync(work, 0, sizeof(int32_t) * 2 * (size_t)n_src, st) != cudaSuccess) return FGL_ERR_CUDA;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(((int64_t)n_dst + 7) / 8, (int64_t)sms * 8));
+    {
+        DeviceGuard guard(ws->device);
+        if (n_dst > 0)
+            transpose_edges_kernel<<<grid, 256, 0, st>>>(indptr, src, n_dst, n_src, n_dst_dev, work, nullptr, nullptr, nullptr, 0,
+                                                         ws->status, 0);
+    }
+    int rc = fgl_exclusive_sum(ws, work, n_src, t_indptr, stream);
+    if (rc != FGL_OK) return rc;
+    DeviceGuard guard(ws->device);
+    if (n_dst > 0)
+        transpose_edges_kernel<<<grid, 256, 0, st>>>(indptr, src, n_dst, n_src, n_dst_dev, nullptr, t_indptr, work + n_src, t_dst,
+                                                     t_cap, ws->status, 1);
+    list_hubs_kernel<<<std::max(1, std::min((n_src + 255) / 256, sms * 4)), 256, 0, st>>>(t_indptr, n_src, hubs);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_agg_bwd_gather(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* t_indptr, const int32_t* t_dst,
+                       const int32_t* hubs, const int32_t* src_deg, const int32_t* dst_deg, const float* dy, int64_t ldy,
+                       const float* dy_self, int64_t ld_self, int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx,
+                       const int32_t* n_dst_dev, void* stream) {
+    if (!ws || mode < FGL_AGG_SUM || mode > FGL_AGG_SYMNORM || n_dst < 0 || n_src < 0 || dim < 1 || ldy < dim || ldx < dim)
+        return FGL_ERR_INVALID;
+    if (dy_self && (ld_self < dim || n_dst > n_src)) return FGL_ERR_INVALID;
+    if (n_src == 0) return FGL_OK;
+    if (!dx || !t_indptr || !hubs || (n_dst > 0 && (!dy || !t_dst || !indptr))) return FGL_ERR_INVALID;
+    if (mode == FGL_AGG_SYMNORM && (!src_deg || !dst_deg)) return FGL_ERR_INVALID;
+    GatherParams p{};
+    p.indptr = indptr;
+    p.t_indptr = t_indptr;
+    p.t_dst = t_dst;
+    p.hubs = hubs;
+    p.src_deg = src_deg;
+    p.dst_deg = dst_deg;
+    p.dy = dy;
+    p.dy_self = dy_self;
+    p.dx = dx;
+    p.ldy = ldy;
+    p.ld_self = ld_self;
+    p.ldx = ldx;
+    p.dim = dim;
+    p.n_dst = n_dst;
+    p.n_src = n_src;
+    p.n_dst_dev = n_dst_dev;
+    DeviceGuard guard(ws->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int sms = ws->sm_count > 0 ? ws->sm_count : 148;
+    switch (pick_vec(dim, dy, ldy, dx, ldx, dy_self, dy_self ? ld_self : 4)) {
+        case 4: launch_gather_mode<4>(mode, p, sms, st); break;
+        case 2: launch_gather_mode<2>(mode, p, sms, st); break;
+        default: launch_gather_mode<1>(mode, p, sms, st); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -113,6 +113,42 @@ __global__ void __launch_bounds__(kStageThreads) stage_segments_kernel(const __g
     }
 }
 
+// Pairwise overlap of the node lists of a window: overlap[i][j] = |nodes_i & nodes_j| (Match-Reorder's match degree,
+// utilis.py:41-48, without one N-sized boolean mask per mini-batch).  One word per node holds a bit per mini-batch:
+// pass 0 sets the bits, pass 1 reads every node's word back and counts, per mini-batch, the other mini-batches that
+// hold the node too, pass 2 clears the words the lists touched, so the mask is zero again when the call returns.
+__global__ void __launch_bounds__(256) window_overlap_kernel(const int32_t* __restrict__ nodes, int64_t nodes_stride,
+                                                             const int32_t* __restrict__ counts, int64_t counts_stride,
+                                                             int64_t n_nodes, uint32_t* __restrict__ mask,
+                                                             int32_t* __restrict__ overlap, int n_batches, int pass) {
+    __shared__ int hist[32];
+    const int b = blockIdx.y;
+    const int n = min(max(__ldg(counts + (int64_t)b * counts_stride), 0), (int)min((int64_t)0x7fffffff, nodes_stride));
+    if (pass == 1) {
+        if (threadIdx.x < 32) hist[threadIdx.x] = 0;
+        __syncthreads();
+    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int id = __ldg(nodes + (int64_t)b * nodes_stride + i);
+        if (id < 0 || (int64_t)id >= n_nodes) continue;
+        if (pass == 0) {
+            atomicOr(mask + id, 1u << b);
+        } else if (pass == 1) {
+            unsigned m = __ldcg(mask + id);
+            while (m) {
+                atomicAdd(&hist[__ffs(m) - 1], 1);
+                m &= m - 1;
+            }
+        } else {
+            mask[id] = 0u;
+        }
+    }
+    if (pass == 1) {
+        __syncthreads();
+        if ((int)threadIdx.x < n_batches && hist[threadIdx.x] != 0) atomicAdd(overlap + b * n_batches + threadIdx.x, hist[threadIdx.x]);
+    }
+}
+
 // Self-test of the bounded wait: every CTA arrives at a team barrier that expects one arrival more than the grid
 // has, so the wait runs out after spin_limit polls, records FGL_ERR_TIMEOUT, raises the abort flag and returns.
 __global__ void __launch_bounds__(32) barrier_timeout_kernel(unsigned long long* bar, int32_t* status, long long spin_limit,
@@ -168,6 +204,19 @@ int fgl_stage_segments(const fgl_segment* segs, int32_t n_segs, int32_t* words_d
     if (blocks == 0) blocks = 1;
     if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
     stage_segments_kernel<<<(unsigned)blocks, kStageThreads, 0, (cudaStream_t)stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_window_overlap(const int32_t* nodes, int64_t nodes_stride, const int32_t* counts, int64_t counts_stride,
+                       int32_t n_batches, int64_t n_nodes, uint32_t* mask, int32_t* overlap, void* stream) {
+    if (n_batches < 0 || n_batches > 32 || nodes_stride < 0 || counts_stride < 1 || n_nodes < 0) return FGL_ERR_INVALID;
+    if (n_batches == 0) return FGL_OK;
+    if (!nodes || !counts || !mask || !overlap) return FGL_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(overlap, 0, sizeof(int32_t) * (size_t)n_batches * n_batches, st) != cudaSuccess) return FGL_ERR_CUDA;
+    const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>(148 * 4 / n_batches + 1, (nodes_stride + 255) / 256)), n_batches);
+    for (int pass = 0; pass < 3; ++pass)
+        window_overlap_kernel<<<grid, 256, 0, st>>>(nodes, nodes_stride, counts, counts_stride, n_nodes, mask, overlap, n_batches, pass);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

@@ -33,7 +33,7 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
-    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -414,12 +414,46 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     return row_off
 
 
+class TransposedBlock:
+    """Per-source lists of the destination rows of a block (``fgl_block_transpose``): what the deterministic backward
+    gather reads.  Built once per block with ``transpose_block``; the buffers can be reused for the next block of at
+    most the same size (``transpose_block(..., out=tb)``)."""
+
+    def __init__(self, n_src: int, edge_cap: int, device):
+        self.n_src, self.edge_cap = int(n_src), int(edge_cap)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.t_indptr = torch.zeros(self.n_src + 1, **i32)
+        self.t_dst = torch.zeros(max(1, self.edge_cap), **i32)
+        self.hubs = torch.zeros(self.n_src + 1, **i32)
+        self.work = torch.zeros(max(1, 2 * self.n_src), **i32)
+
+
+def transpose_block(edge_ptr, src_edges, dst_nodes, src_nodes, n_dst_dev=None, out: TransposedBlock | None = None):
+    """Transpose a block CSR (destination rows -> per-source lists).  ``src_edges`` holds at least ``edge_ptr[dst_nodes]``
+    entries; ``out`` reuses buffers sized for at least ``src_nodes`` sources and ``src_edges.numel()`` edges."""
+    _check_i32(edge_ptr, "edge_ptr")
+    _check_i32(src_edges, "src_edges")
+    dev = edge_ptr.device
+    n_src, n_dst = int(src_nodes), int(dst_nodes)
+    if out is None:
+        out = TransposedBlock(n_src, src_edges.numel(), dev)
+    elif out.n_src < n_src or out.edge_cap < src_edges.numel():
+        raise RuntimeError("the TransposedBlock is too small for this block")
+    ws = _ws(dev)
+    rc = lib().fgl_block_transpose(ws, _ptr(edge_ptr), _ptr(src_edges), ctypes.c_int32(n_dst), ctypes.c_int32(n_src),
+                                   _ptr(out.t_indptr), _ptr(out.t_dst), ctypes.c_int64(out.edge_cap), _ptr(out.hubs),
+                                   _ptr(out.work), _ptr(n_dst_dev), _stream(dev))
+    _raise(rc, "transpose_block", ws)
+    return out
+
+
 def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_degs=None, dst_norm_degs=None,
-                       n_dst_dev=None, d_self=None, out=None):
+                       n_dst_dev=None, d_self=None, out=None, transposed: TransposedBlock | None = None):
     """d_x[src] += w * d_out[d] over every edge; returns d_x float32[src_nodes, dim].  ``n_dst_dev`` as in
     ``aggregate``.  ``d_self`` (float32[n_dst, dim], rows may be a column slice) is the gradient of a self term:
     d_x starts from it in its first n_dst rows instead of from zero.  ``d_out`` may be a column slice too;
-    ``out`` receives the result when given."""
+    ``out`` receives the result when given.  With ``transposed`` (``transpose_block`` of the same block) the result is
+    gathered row by row in a fixed order -- bit-reproducible -- instead of scattered with atomic reductions."""
     _check_i32(edge_ptr, "edge_ptr")
     _check_i32(src_edges, "src_edges")
     _check_rows_f32(d_out, "d_input")
@@ -440,6 +474,20 @@ def aggregate_backward(mode, edge_ptr, src_edges, d_out, src_nodes, src_norm_deg
         if out.size(0) < int(src_nodes) or out.size(1) != dim:
             raise RuntimeError("out must be float32[src_nodes, dim]")
         d_x = out
+    if transposed is not None:
+        if d_self is not None:
+            _check_rows_f32(d_self, "d_self")
+            if d_self.size(0) != n_dst or d_self.size(1) != dim:
+                raise RuntimeError("d_self must be float32[n_dst, dim]")
+        ws = _ws(dev)
+        rc = lib().fgl_agg_bwd_gather(ws, ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(transposed.t_indptr), _ptr(transposed.t_dst),
+                                      _ptr(transposed.hubs), _ptr(src_norm_degs), _ptr(dst_norm_degs), _ptr(d_out),
+                                      ctypes.c_int64(d_out.stride(0)), _ptr(d_self),
+                                      ctypes.c_int64(d_self.stride(0) if d_self is not None else dim), ctypes.c_int32(dim),
+                                      ctypes.c_int32(n_dst), ctypes.c_int32(int(src_nodes)), _ptr(d_x),
+                                      ctypes.c_int64(d_x.stride(0)), _ptr(n_dst_dev), _stream(dev))
+        _raise(rc, "aggregate_backward (gather)", ws)
+        return d_x
     with _on_device(dev):
         if d_self is None:
             rc = lib().fgl_agg_bwd(_ws(dev), ctypes.c_int32(mode), _ptr(edge_ptr), _ptr(src_edges), _ptr(src_norm_degs),
@@ -917,6 +965,28 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
     ws = _ws(dev)
     rc = lib().fgl_sample_map_fused(ws, ctypes.byref(a), _stream(dev))
     _raise(rc, "sample_map_fused", ws)
+    return out
+
+
+def window_overlap(nodes, counts, n_nodes, mask, out=None):
+    """int32[W, W] pairwise overlap of the node lists ``nodes[b, :counts[b]]`` of a window (W <= 32), computed on the
+    device without a read-back.  ``counts``: int32 CUDA tensor (any stride); ``mask``: int32[n_nodes] scratch, zero on
+    entry and zero again afterwards."""
+    _check_i32(nodes, "nodes")
+    _check_i32(mask, "mask")
+    if nodes.dim() != 2 or nodes.size(0) > 32 or counts.dtype != torch.int32 or counts.dim() != 1 or counts.numel() != nodes.size(0):
+        raise RuntimeError("nodes must be int32[W <= 32, stride] with one int32 count per row")
+    if mask.numel() < int(n_nodes):
+        raise RuntimeError("mask must hold one word per node")
+    dev = nodes.device
+    W = nodes.size(0)
+    if out is None:
+        out = torch.empty((W, W), dtype=torch.int32, device=dev)
+    with _on_device(dev):
+        rc = lib().fgl_window_overlap(_ptr(nodes), ctypes.c_int64(nodes.stride(0)), ctypes.c_void_p(counts.data_ptr()),
+                                      ctypes.c_int64(counts.stride(0)), ctypes.c_int32(W), ctypes.c_int64(int(n_nodes)), _ptr(mask),
+                                      _ptr(out), _stream(dev))
+    _raise(rc, "window_overlap")
     return out
 
 

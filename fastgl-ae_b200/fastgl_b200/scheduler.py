@@ -92,7 +92,14 @@ class MatchReorder:
         buf = self._pinned.get((key, W))
         if buf is None:
             buf = self._pinned[(key, W)] = torch.zeros((W, W), dtype=torch.float32).pin_memory()
-        buf.copy_(overlap_matrix_padded(nodes, counts, self.num_nodes), non_blocking=True)
+        if nodes.is_cuda and W <= 32:
+            import fastgl
+            if getattr(self, "_mask", None) is None or self._mask.device != nodes.device:
+                self._mask = torch.zeros(self.num_nodes, dtype=torch.int32, device=nodes.device)
+            ov = fastgl.window_overlap(nodes, counts, self.num_nodes, self._mask).to(torch.float32)
+        else:
+            ov = overlap_matrix_padded(nodes, counts, self.num_nodes)
+        buf.copy_(ov, non_blocking=True)
 
     def order(self, sizes, key=0) -> list[int]:
         """The greedy chain for the window whose overlap ``enqueue(..., key)`` produced (its copy must have

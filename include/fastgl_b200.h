@@ -165,6 +165,15 @@ typedef struct fgl_segment {
 int fgl_stage_segments(const fgl_segment* segs, int32_t n_segs, int32_t* words_dst, const int32_t* words,
                        int32_t n_words, void* stream);
 
+/* Pairwise overlap of the node lists of a window of mini-batches, on the device: overlap[i * n_batches + j] =
+ * |nodes_i & nodes_j| (the diagonal holds the list lengths).  This is the quantity behind Match-Reorder's match
+ * degree (match_reorder.reorder, utilis.py:41-48), which the reference derives from one N-sized boolean mask per
+ * mini-batch (utilis.py:27-28).  nodes is int32 [n_batches][nodes_stride] as fgl_sample_map_fused leaves it, the
+ * list of batch b being its first counts[b * counts_stride] entries (ids distinct within a list); n_batches <= 32.
+ * mask is caller-owned scratch of n_nodes 32-bit words that must be zero on entry and is zero again on return. */
+int fgl_window_overlap(const int32_t* nodes, int64_t nodes_stride, const int32_t* counts, int64_t counts_stride,
+                       int32_t n_batches, int64_t n_nodes, uint32_t* mask, int32_t* overlap, void* stream);
+
 /* Exclusive scan with the total appended; replaces exclusive_sum_cuda (utilis.cu:17-41; binding
  * aggregate_acc.cpp:514-520).  out has n + 1 entries. */
 int fgl_exclusive_sum(fgl_ws* ws, const int32_t* in, int64_t n, int32_t* out, void* stream);
@@ -279,6 +288,24 @@ int fgl_agg_bwd_self(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int3
                      const int32_t* dst_deg, const float* dy, int64_t ldy, const float* dy_self, int64_t ld_self,
                      int32_t dim, int32_t n_dst, int32_t n_src, float* dx, int64_t ldx, const int32_t* n_dst_dev,
                      void* stream);
+
+/* Aggregation backward as a gather, deterministic: the same result as fgl_agg_bwd / fgl_agg_bwd_self (the scatters
+ * K9 / K11 of the reference, aggregate_acc_kernel.cu:468-517, :555-596, which add with atomics in arbitrary order), but
+ * every row dx[s] is produced by one warp -- or, for a source with more than 32 edges in the block, one CTA -- that
+ * adds the rows dy[d] of the edges (d, s) in ascending order of d.  Two runs give the same bits; dx needs no
+ * initialisation (rows without edges become zero, or dy_self[s]); dy_self may be NULL.
+ *
+ * fgl_block_transpose builds the per-source lists once per block: t_indptr (n_src + 1 offsets), t_dst (the edges'
+ * destination rows grouped by source, t_cap >= number of edges), hubs (n_src + 1 words: the number of sources with
+ * more than 32 edges, then their ids).  work is scratch of 2 * n_src words.  A source id outside [0, n_src) records
+ * FGL_ERR_BOUNDS and is skipped.  n_dst_dev as in fgl_agg_fwd. */
+int fgl_block_transpose(fgl_ws* ws, const int32_t* indptr, const int32_t* src, int32_t n_dst, int32_t n_src,
+                        int32_t* t_indptr, int32_t* t_dst, int64_t t_cap, int32_t* hubs, int32_t* work,
+                        const int32_t* n_dst_dev, void* stream);
+int fgl_agg_bwd_gather(fgl_ws* ws, int32_t mode, const int32_t* indptr, const int32_t* t_indptr, const int32_t* t_dst,
+                       const int32_t* hubs, const int32_t* src_deg, const int32_t* dst_deg, const float* dy, int64_t ldy,
+                       const float* dy_self, int64_t ld_self, int32_t dim, int32_t n_dst, int32_t n_src, float* dx,
+                       int64_t ldx, const int32_t* n_dst_dev, void* stream);
 
 /* ---- Element-wise kernels of the training step around the aggregation path -----------------------------
  * None of these has a counterpart among the reference's CUDA operators: the reference leaves them to PyTorch,

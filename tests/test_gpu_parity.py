@@ -398,6 +398,66 @@ def test_aggregate_reports_an_out_of_range_id_and_matches_the_oracle_without_it(
     assert rel_err(dx.cpu().numpy(), refb) <= AGG_RTOL
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("dim", [47, 100, 256, 1024])
+def test_backward_gather_over_the_transposed_block_is_exact_to_tolerance_and_reproducible(fastgl, mode, dim):
+    """A power-law source side: one source with 12 000 in-block edges, a few dozen with hundreds, the rest with a
+    handful, repeated edges included.  The gather equals the oracle (and the scatter) to the aggregation tolerance,
+    gives the same bits twice, and folds the self gradient in."""
+    rng = np.random.default_rng(1000 + 7 * dim + mode)
+    n_dst, n_src = 40_000 if dim <= 256 else 14_000, 9000
+    deg = rng.integers(0, 9, size=n_dst)
+    indptr = np.zeros(n_dst + 1, dtype=np.int32)
+    indptr[1:] = np.cumsum(deg)
+    w = 1.0 / np.arange(1, n_src + 1) ** 1.1
+    src = rng.choice(n_src, size=int(indptr[-1]), p=w / w.sum()).astype(np.int32)
+    hub_rows = rng.choice(np.flatnonzero(deg > 0), size=min(12_000, int((deg > 0).sum())), replace=False)
+    src[indptr[hub_rows]] = 7                                     # source 7 is in 12 000 rows (n_dst > 32768: two windows)
+    dy = rng.standard_normal((n_dst, dim)).astype(np.float32)
+    dself = rng.standard_normal((n_dst if n_dst <= n_src else n_src, dim)).astype(np.float32)
+    sdeg = np.maximum(oc.cal_deg(src, n_src), 1)
+    ddeg = np.maximum(deg, 1).astype(np.int32)
+    d_ptr, d_src, d_dy, d_sdeg, d_ddeg = to_dev(indptr), to_dev(src), to_dev(dy), to_dev(sdeg), to_dev(ddeg)
+    tb = fastgl.transpose_block(d_ptr, d_src, n_dst, n_src)
+    fastgl.check_status(dev())
+    assert int(tb.hubs[0]) >= 1 and 7 in tb.hubs[1: 1 + int(tb.hubs[0])].tolist()
+    assert torch.equal(tb.t_indptr[1:].long(), torch.cumsum(torch.bincount(d_src.long(), minlength=n_src), 0))
+    got = fastgl.aggregate_backward(mode, d_ptr, d_src, d_dy, n_src, d_sdeg, d_ddeg, transposed=tb)
+    again = fastgl.aggregate_backward(mode, d_ptr, d_src, d_dy, n_src, d_sdeg, d_ddeg, transposed=tb)
+    assert torch.equal(got, again)                                # bit-reproducible
+    tb2 = fastgl.transpose_block(d_ptr, d_src, n_dst, n_src)     # another transposition (another fill order): same bits
+    assert torch.equal(got, fastgl.aggregate_backward(mode, d_ptr, d_src, d_dy, n_src, d_sdeg, d_ddeg, transposed=tb2))
+    ref = oc.aggregate_bwd(mode, indptr, src, dy, n_src, sdeg, ddeg)
+    assert rel_err(got.cpu().numpy(), ref) <= AGG_RTOL
+    scat = fastgl.aggregate_backward(mode, d_ptr, d_src, d_dy, n_src, d_sdeg, d_ddeg)
+    assert rel_err(scat.cpu().numpy(), ref) <= AGG_RTOL
+    if n_dst <= n_src:                                            # the self term (destinations are the first sources)
+        with_self = fastgl.aggregate_backward(mode, d_ptr, d_src, d_dy, n_src, d_sdeg, d_ddeg, transposed=tb, d_self=to_dev(dself))
+        want = ref.copy()
+        want[:n_dst] += dself
+        assert rel_err(with_self.cpu().numpy(), want) <= AGG_RTOL
+
+
+def test_backward_gather_with_a_self_term_and_a_device_side_row_count(fastgl):
+    rng = np.random.default_rng(77)
+    n_real, n_pad, n_src, dim = 900, 1024, 5000, 128
+    deg = rng.integers(0, 12, size=n_real)
+    indptr = np.zeros(n_pad + 1, dtype=np.int32)
+    indptr[1: n_real + 1] = np.cumsum(deg)
+    indptr[n_real + 1:] = indptr[n_real]
+    src = rng.integers(0, n_src, size=int(indptr[n_real]) + 64).astype(np.int32)   # stale entries beyond the real edges
+    dcat = rng.standard_normal((n_pad, 2 * dim)).astype(np.float32)                # padded rows hold garbage
+    d_ptr, d_src, d_cat = to_dev(indptr), to_dev(src), to_dev(dcat)
+    n_dev = torch.tensor([n_real], dtype=torch.int32, device=dev())
+    tb = fastgl.transpose_block(d_ptr, d_src, n_pad, n_src, n_dst_dev=n_dev)
+    got = fastgl.aggregate_backward(fastgl.AGG_MEAN, d_ptr, d_src, d_cat[:, dim:], n_src, n_dst_dev=n_dev, d_self=d_cat[:, :dim],
+                                    transposed=tb)
+    ref = oc.aggregate_bwd(oc.MODE_MEAN, indptr[: n_real + 1], src[: indptr[n_real]], dcat[:n_real, dim:], n_src)
+    ref[:n_real] += dcat[:n_real, :dim]
+    assert rel_err(got.cpu().numpy(), ref) <= AGG_RTOL
+    fastgl.check_status(dev())
+
+
 def test_gather_rows_reports_an_out_of_range_id(fastgl):
     table = torch.randn((1000, 100), device=dev())
     ids = torch.tensor([5, 1000, 999, -1, 0], dtype=torch.int32, device=dev())
@@ -405,6 +465,29 @@ def test_gather_rows_reports_an_out_of_range_id(fastgl):
     with pytest.raises(RuntimeError, match="out of range"):
         fastgl.check_status(dev())
     assert torch.equal(got[[0, 2, 4]], table[[5, 999, 0]]) and not got[[1, 3]].any()
+
+
+def test_window_overlap_kernel_matches_the_mask_product(fastgl):
+    """|nodes_i & nodes_j| for the node lists of a window, against the dense-mask product Match-Reorder is defined by."""
+    from fastgl_b200.scheduler import overlap_matrix
+    rng = np.random.default_rng(12)
+    n, W, stride = 200_000, 16, 40_000
+    counts = rng.integers(1000, stride, size=W).astype(np.int32)
+    counts[5] = 0
+    nodes = rng.integers(0, n, size=(W, stride)).astype(np.int32)        # stale ids beyond every list
+    lists = []
+    for b in range(W):
+        ids = rng.choice(n, size=counts[b], replace=False).astype(np.int32)
+        nodes[b, : counts[b]] = ids
+        lists.append(torch.from_numpy(ids).to(dev()))
+    padded_counts = torch.zeros((W, 16), dtype=torch.int32, device=dev())  # one column of a wider array, as the sampler leaves it
+    padded_counts[:, 3] = to_dev(counts)
+    mask = torch.zeros(n, dtype=torch.int32, device=dev())
+    got = fastgl.window_overlap(to_dev(nodes), padded_counts[:, 3], n, mask)
+    want = overlap_matrix(lists, n)
+    assert torch.equal(got.float(), want)
+    assert not mask.any()                                                  # left clean for the next window
+    assert torch.equal(fastgl.window_overlap(to_dev(nodes), padded_counts[:, 3], n, mask).float(), want)
 
 
 def test_bounded_barrier_wait_runs_out_and_the_workspace_recovers(fastgl):
