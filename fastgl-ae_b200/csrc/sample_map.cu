@@ -34,7 +34,11 @@ namespace cg = cooperative_groups;
 
 namespace fgl {
 
-constexpr int kThreads = 512;
+#ifndef FGL_SM_THREADS
+#define FGL_SM_THREADS 512
+#endif
+constexpr int kThreads = FGL_SM_THREADS;
+constexpr int kMinCtas = 1024 / FGL_SM_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr unsigned long long kEmpty = ~0ULL;
 constexpr uint32_t kPending = 0x80000000u;
@@ -347,7 +351,10 @@ __device__ __forceinline__ void emit_edge(const KParams& p, const Hop& h, const 
 // settling slot i after a ballot over the earlier lanes -- the picks never leave the registers.  Stages 1-4 issue the
 // dependent loads of the group's seeds stage by stage -- picked sources, first table probes, claims -- so that
 // kSeedsPerIter independent round trips are in flight per lane instead of one chain after the other.
-constexpr int kSeedsPerIter = 4;
+#ifndef FGL_SM_KS
+#define FGL_SM_KS 4
+#endif
+constexpr int kSeedsPerIter = FGL_SM_KS;
 constexpr int kGroupPathMaxFanout = 32;
 
 template <typename PtrT, int MODE, bool ARRIVAL, int G>
@@ -834,7 +841,7 @@ __device__ __forceinline__ void phase_relabel(const Table& tab, int32_t* edges, 
 // kernels
 // ----------------------------------------------------------------------------------------------
 template <typename PtrT, int MODE, bool ARRIVAL>
-__global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_constant__ KParams p) {
+__global__ void __launch_bounds__(kThreads, kMinCtas) sample_map_kernel(const __grid_constant__ KParams p) {
     __shared__ Smem sm;
     extern __shared__ uint32_t picks[];
     const int team_id = blockIdx.x / p.team_size;
@@ -949,7 +956,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_map_kernel(const __grid_co
 
 // Explicit-edge mapping (the drop-in transfer_edge_id).  The table was cleared by the host.
 template <bool ARRIVAL>
-__global__ void __launch_bounds__(kThreads, 2) map_kernel(const __grid_constant__ KParams p) {
+__global__ void __launch_bounds__(kThreads, kMinCtas) map_kernel(const __grid_constant__ KParams p) {
     __shared__ Smem sm;
     Team t;
     t.rank = blockIdx.x;
