@@ -350,6 +350,15 @@ def run_sharded_leg(cfg, args, tr, indptr, rank, world, device, barrier, max_ove
     return out
 
 
+DENSE_MATMUL = {
+    "fp32": "fp32: cuBLAS SIMT float32 kernels",
+    "3xtf32": "3xtf32: operands split into two TF32 parts each, one TF32 tensor-core GEMM over [hi|lo|hi].[hi;hi;lo] with float32 "
+              "accumulation; relative error 2e-6 (SIMT float32: 5e-7; single-pass TF32, the reference's own setting: 3e-4); "
+              "models without the hand-written step (GCN) run float32",
+    "tf32": "tf32: single-pass TF32",
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,9 +371,10 @@ def main():
     ap.add_argument("--table-slots", type=int, default=-1,
                     help="cap of the sampler's per-team hashtable (0: worst-case size; default: learnt from the first window)")
     ap.add_argument("--reorder", action="store_true", help="Match-Reorder each window")
-    ap.add_argument("--matmul", default="fp32", choices=["fp32", "tf32"],
-                    help="arithmetic of the dense-layer GEMMs that stay in PyTorch (tf32 is what the reference's "
-                         "pinned PyTorch 1.10.1 used by default on Ampere)")
+    ap.add_argument("--matmul", default="3xtf32", choices=["fp32", "3xtf32", "tf32"],
+                    help="arithmetic of the dense-layer GEMMs that stay in cuBLAS: fp32 = SIMT float32 kernels; 3xtf32 = "
+                         "error-compensated split into three TF32 tensor-core products, float32-level error; tf32 = "
+                         "single-pass TF32, what the reference's pinned PyTorch 1.10.1 used by default on Ampere")
     ap.add_argument("--no-graph", action="store_true", help="launch the per-batch step op by op instead of a CUDA graph")
     ap.add_argument("--cpu-steps", type=int, default=150, help="mini-batches of the CPU baseline sample (about 10 s of CPU work)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -446,7 +456,8 @@ def main():
     model.train()
     tr = Trainer(indptr, indices, feat, labels, train, model, cfg["fanouts"], batch_size=cfg["batch"], window=args.window,
                  reorder=args.reorder, rank=rank, world=world, n_teams=args.teams, cuda_graph=not args.no_graph,
-                 table_slots=None if args.table_slots < 0 else args.table_slots, grad_sync=args.grad_sync)
+                 table_slots=None if args.table_slots < 0 else args.table_slots, grad_sync=args.grad_sync,
+                 matmul="3xtf32" if args.matmul == "3xtf32" else "fp32")
 
     def barrier():
         if world > 1:
@@ -602,17 +613,19 @@ def main():
         n_windows = (args.steps + args.window - 1) // args.window
         n_layers = len(cfg["fanouts"])
         per_step = (5 * n_layers - 1) if tr.graphed is not None else 2 * (n_layers - 1)
+        if tr.graphed is not None and args.matmul == "3xtf32":
+            per_step += 3 * n_layers      # operand splits: the weights, the layer inputs, the output gradients
         launches = args.steps * per_step + 2 * n_windows
         epoch_s = steps_per_epoch * ms / args.steps * 1e-3
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32" if args.matmul == "fp32" else "tf32", "data": "synthetic", "config": config_json,
+                "vs_baseline": None, "dtype": "tf32" if args.matmul == "tf32" else "f32", "data": "synthetic", "config": config_json,
                 "repeats": len(regions), "ms_per_step_min": by_ms[0][0] / args.steps, "ms_per_step_max": by_ms[-1][0] / args.steps,
                 "settle_steps": 2 * args.window,
                 "per_gpu_value": value / world, "epoch_time_s": epoch_s,
                 "epoch_time_kind": "measured" if args.steps >= steps_per_epoch else f"extrapolated from {args.steps} steps",
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
-                "dense_matmul": args.matmul, "cuda_graph": not args.no_graph, "graph_fallback_steps": tr.graph_fallbacks,
+                "dense_matmul": DENSE_MATMUL[args.matmul], "cuda_graph": not args.no_graph, "graph_fallback_steps": tr.graph_fallbacks,
                 "gradient_sync": tr.grad_sync_kind(),
                 "e2e": {"value": e2e_edges / (ms_e2e * 1e-3), "unit": "edges/s", "ms_per_step": ms_e2e / args.steps,
                         "ms_per_step_min": e2e_by_ms[0][0] / args.steps, "ms_per_step_max": e2e_by_ms[-1][0] / args.steps,

@@ -338,6 +338,51 @@ adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restric
     }
 }
 
+// Splits fp32 values into two TF32-representable parts, x = hi + lo + O(2^-22 |x|): hi = x rounded to TF32's 10-bit
+// mantissa, lo = the (exactly representable) remainder rounded likewise.  A product A.B evaluated as
+// Ahi.Bhi + Alo.Bhi + Ahi.Blo by TF32 tensor-core GEMMs that accumulate in fp32 then carries fp32-level error (the
+// dropped lo.lo term is 2^-22 relative): the parts are stored with their low 13 mantissa bits zero, so the GEMM's own
+// conversion to TF32 loses nothing.  Each part can be written to several places (column or row blocks of wider
+// matrices), so that the three products become ONE GEMM over a three times longer inner dimension,
+// [Ahi | Alo | Ahi] . [Bhi ; Bhi ; Blo], instead of three launches.
+constexpr int kSplitMaxDst = 8;
+struct SplitDst {
+    float* ptr[kSplitMaxDst];
+    long long ld[kSplitMaxDst];
+    int lo_part[kSplitMaxDst];
+    int n;
+};
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+template <bool VEC4>
+__global__ void __launch_bounds__(kEwThreads)
+split_tf32_kernel(const float* __restrict__ x, int64_t rows, int cols, int64_t ldx, const SplitDst d) {
+    const int per_row = VEC4 ? cols / 4 : cols;
+    const int64_t total = rows * per_row;
+    for (int64_t g = (int64_t)blockIdx.x * kEwThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kEwThreads) {
+        const int64_t r = g / per_row;
+        const int c = (int)(g - r * per_row) * (VEC4 ? 4 : 1);
+        if (VEC4) {
+            const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
+            float4 h, l;
+            h.x = to_tf32(v.x); l.x = to_tf32(v.x - h.x);
+            h.y = to_tf32(v.y); l.y = to_tf32(v.y - h.y);
+            h.z = to_tf32(v.z); l.z = to_tf32(v.z - h.z);
+            h.w = to_tf32(v.w); l.w = to_tf32(v.w - h.w);
+            for (int q = 0; q < d.n; ++q) *reinterpret_cast<float4*>(d.ptr[q] + r * d.ld[q] + c) = d.lo_part[q] ? l : h;
+        } else {
+            const float v = x[r * ldx + c];
+            const float h = to_tf32(v), l = to_tf32(v - h);
+            for (int q = 0; q < d.n; ++q) d.ptr[q][r * d.ld[q] + c] = d.lo_part[q] ? l : h;
+        }
+    }
+}
+
 static int ew_grid(int64_t work_items) {
     const int64_t blocks = (work_items + kEwThreads - 1) / kEwThreads;
     return (int)(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -439,6 +484,30 @@ int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_av
     // step_dev[0] = completed steps, step_dev[1] = the kernel's arrival ticket (zero between launches)
     adam_kernel<<<ew_grid((n + 3) / 4), kEwThreads, 0, (cudaStream_t)stream>>>(
         param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, step_dev, (unsigned int*)(step_dev + 1));
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_split_tf32(const float* x, int64_t rows, int64_t cols, int64_t ldx, int n_dst, float* const* dst, const int64_t* ld_dst,
+                   const int32_t* lo_part, void* stream) {
+    if (rows < 0 || cols < 0 || cols > 0x7fffffffLL || ldx < cols || n_dst < 1 || n_dst > kSplitMaxDst || !dst || !ld_dst || !lo_part)
+        return FGL_ERR_INVALID;
+    if (rows == 0 || cols == 0) return FGL_OK;
+    if (!x) return FGL_ERR_INVALID;
+    SplitDst d{};
+    d.n = n_dst;
+    bool vec = cols % 4 == 0 && ldx % 4 == 0 && aligned16(x);
+    for (int q = 0; q < n_dst; ++q) {
+        if (!dst[q] || ld_dst[q] < cols) return FGL_ERR_INVALID;
+        d.ptr[q] = dst[q];
+        d.ld[q] = ld_dst[q];
+        d.lo_part[q] = lo_part[q] ? 1 : 0;
+        vec = vec && ld_dst[q] % 4 == 0 && aligned16(dst[q]);
+    }
+    const int64_t items = rows * (vec ? cols / 4 : cols);
+    if (vec)
+        split_tf32_kernel<true><<<ew_grid(items), kEwThreads, 0, (cudaStream_t)stream>>>(x, rows, (int)cols, ldx, d);
+    else
+        split_tf32_kernel<false><<<ew_grid(items), kEwThreads, 0, (cudaStream_t)stream>>>(x, rows, (int)cols, ldx, d);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

@@ -33,7 +33,7 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
-    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block", "split_tf32",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -650,6 +650,40 @@ def adam_step_(param, grad, exp_avg, exp_avg_sq, step_dev, lr=1e-3, betas=(0.9, 
                                  ctypes.c_float(lr), ctypes.c_float(betas[0]), ctypes.c_float(betas[1]), ctypes.c_float(eps),
                                  ctypes.c_float(weight_decay), _ptr(step_dev), _stream(dev))
     _raise(rc, "adam_step_")
+
+
+def split_tf32(x, dst=None):
+    """Error-compensated TF32 operands of a float32 matrix (``fgl_split_tf32``): ``hi`` = ``x`` rounded to TF32, ``lo`` =
+    the remainder rounded to TF32.  ``dst``: list of ``(matrix, "hi" | "lo")``, every matrix of ``x``'s shape with unit
+    column stride (a block of columns or rows of a wider matrix is fine); without it two new tensors ``(hi, lo)`` are
+    returned.  With ``torch.backends.cuda.matmul.allow_tf32`` on, ``[A_hi | A_lo | A_hi] @ [B_hi ; B_hi ; B_lo]`` is the
+    product ``A @ B`` to float32-level error on the tensor cores."""
+    if x.dim() == 1:
+        x = x.view(1, -1)
+    _check_rows_f32(x, "x")
+    ret = None
+    if dst is None:
+        ret = (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(x, memory_format=torch.contiguous_format))
+        dst = [(ret[0], "hi"), (ret[1], "lo")]
+    if not 1 <= len(dst) <= 8:
+        raise RuntimeError("split_tf32 takes 1 to 8 destinations")
+    ptrs = (ctypes.c_void_p * len(dst))()
+    lds = (ctypes.c_int64 * len(dst))()
+    parts = (ctypes.c_int32 * len(dst))()
+    for q, (t, part) in enumerate(dst):
+        _check_rows_f32(t, f"dst[{q}]")
+        if tuple(t.shape) != tuple(x.shape) or t.device != x.device:
+            raise RuntimeError("every destination must have x's shape and device")
+        if part not in ("hi", "lo"):
+            raise RuntimeError("a destination takes the part 'hi' or 'lo'")
+        ptrs[q], lds[q], parts[q] = t.data_ptr(), (t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))), int(part == "lo")
+    ldx = x.stride(0) if x.size(0) > 1 else max(x.stride(0), x.size(1))
+    dev = x.device
+    with _on_device(dev):
+        rc = lib().fgl_split_tf32(_ptr(x), ctypes.c_int64(x.size(0)), ctypes.c_int64(x.size(1)), ctypes.c_int64(ldx),
+                                  ctypes.c_int(len(dst)), ptrs, lds, parts, _stream(dev))
+    _raise(rc, "split_tf32")
+    return ret
 
 
 class PeerSync:

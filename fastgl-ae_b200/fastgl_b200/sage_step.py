@@ -8,6 +8,14 @@ one loss launch; and per layer two GEMMs, one scatter that starts from the self 
 ReLU/dropout backward that also produces the bias gradient.  The dense products stay with cuBLAS (torch.mm), as
 in the reference (aggregate_acc_kernel.cu:237,368); everything else is a kernel of this library.
 
+``matmul="3xtf32"`` evaluates every dense product on the tensor cores with float32-level error: both operands are
+split into two TF32-representable parts (``fastgl.split_tf32``) and ``A B = A_hi B_hi + A_lo B_hi + A_hi B_lo`` is ONE
+TF32 GEMM accumulating in float32 over a three times longer inner dimension, ``[A_hi | A_lo | A_hi] [B_hi ; B_hi ; B_lo]``
+(three separate GEMMs cost more in launches than the SIMT float32 product they replace).  The weight gradient
+``X^T dZ`` contracts over the rows, so it takes the 2 x 2 block product ``[X_hi | X_lo]^T [dZ_hi | dZ_lo]`` and adds the
+four blocks.  (The reference's pinned PyTorch 1.10 ran these products in single-pass TF32.)  ``matmul="fp32"`` keeps
+cuBLAS's SIMT float32 kernels.
+
 The model is the one of ``layers.GraphSAGE``: layer i computes ``z_i = [h_i[:n_dst] | mean_N(h_i)] W_i + b_i`` and
 ``h_{i+1} = dropout(relu(z_i))``; the last z is the logits.  ``layers.GraphSAGE`` under autograd is the reference
 the tests compare this program with.
@@ -20,7 +28,7 @@ import fastgl
 
 
 class SageStepProgram:
-    def __init__(self, model, grads, labels, x0, seeds, sizes, blocks, pad_dst, step_word, rng_seed=12345):
+    def __init__(self, model, grads, labels, x0, seeds, sizes, blocks, pad_dst, step_word, rng_seed=12345, matmul="fp32"):
         """``x0``: float32[pad_dst[0], 2*in] rows [self | neighbour mean] of the input layer; ``blocks[i]`` (i >= 1) the
         padded block of layer i with its real row count in ``sizes[i]``; ``seeds``: int32 node ids of the output rows
         (their labels are ``labels[seeds]``); ``sizes[len(blocks) - 1]`` = number of valid output rows;
@@ -55,19 +63,65 @@ class SageStepProgram:
             self.slabs.append(s)
             self.part.append(torch.zeros((s, 2 * ins[i], outs[i]), **f32) if s else None)
             self.ones.append(torch.ones((1, s), **f32) if s else None)
+        if matmul not in ("fp32", "3xtf32"):
+            raise ValueError("matmul must be 'fp32' or '3xtf32'")
+        self.split = matmul == "3xtf32"
+        if self.split:
+            ks = [2 * d for d in ins]
+            # [X_hi | X_lo | X_hi] of every layer input, [dZ_hi | dZ_lo | dZ_hi] of every output gradient,
+            # [W_hi ; W_hi ; W_lo] (forward) and [W_hi | W_hi | W_lo] (input gradient) of every weight
+            self.x3 = [torch.zeros((self.pad_dst[i], 3 * ks[i]), **f32) for i in range(L)]
+            self.g3 = [torch.zeros((self.pad_dst[i], 3 * outs[i]), **f32) for i in range(L)]
+            self.wv3 = [torch.zeros((3 * ks[i], outs[i]), **f32) for i in range(L)]
+            self.wc3 = [torch.zeros((ks[i], 3 * outs[i]), **f32) for i in range(L)]
+            self.part = [torch.zeros((s, 2 * ks[i], 2 * outs[i]), **f32) if s else torch.zeros((2 * ks[i], 2 * outs[i]), **f32)
+                         for i, s in enumerate(self.slabs)]
+
+    # ---- operands of the error-compensated products ------------------------------------------------------------------
+    @staticmethod
+    def _split3(x, x3):
+        c = x.size(1)
+        fastgl.split_tf32(x, [(x3[:, :c], "hi"), (x3[:, c: 2 * c], "lo"), (x3[:, 2 * c:], "hi")])
+
+    def _split_weight(self, i):
+        w = self.layers[i].weight.data
+        k, m = w.shape
+        v, c = self.wv3[i], self.wc3[i]
+        fastgl.split_tf32(w, [(v[:k], "hi"), (v[k: 2 * k], "hi"), (v[2 * k:], "lo"),
+                              (c[:, :m], "hi"), (c[:, m: 2 * m], "hi"), (c[:, 2 * m:], "lo")])
 
     def forward_backward(self) -> torch.Tensor:
         """Forward, loss and backward; the parameter gradients land in the flat gradient buffer.  Returns the loss
         (float32[1], a static buffer)."""
+        if self.split:      # the TF32 setting is read when a product is enqueued (or captured), not when it runs
+            keep = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                return self._forward_backward()
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = keep
+        return self._forward_backward()
+
+    def _forward_backward(self) -> torch.Tensor:
         L, p = self.L, self.p_drop
         training = self.model.training
         self.grads.zero()
+        split = self.split
+        x_split = set()
+        if split:
+            for i in range(L):
+                self._split_weight(i)
         last = self.layers[L - 1]
         fused_head = last.weight.size(1) <= 128        # output layer and loss in one launch
         for i, layer in enumerate(self.layers):
             if i == L - 1 and fused_head:
                 break
-            torch.mm(self.cat[i], layer.weight, out=self.z[i])
+            if split:
+                self._split3(self.cat[i], self.x3[i])
+                x_split.add(i)
+                torch.mm(self.x3[i], self.wv3[i], out=self.z[i])
+            else:
+                torch.mm(self.cat[i], layer.weight, out=self.z[i])
             if i < L - 1:
                 blk = self.blocks[i + 1]
                 d = self.layers[i + 1].input_dim
@@ -90,11 +144,18 @@ class SageStepProgram:
             layer = self.layers[i]
             if i == L - 1 and not fused_head:
                 fastgl.relu_dropout_backward_(dz, masked=False, dbias=layer.bias.grad)
+            if split:
+                self._split3(dz, self.g3[i])
+                if i not in x_split:
+                    self._split3(self.cat[i], self.x3[i])
             self._weight_grad(i, dz)
             if i > 0:
                 d = layer.input_dim
                 blk = self.blocks[i]
-                torch.mm(dz, layer.weight.t(), out=self.dcat[i])
+                if split:
+                    torch.mm(self.g3[i], self.wc3[i].t(), out=self.dcat[i])
+                else:
+                    torch.mm(dz, layer.weight.t(), out=self.dcat[i])
                 fastgl.aggregate_backward(fastgl.AGG_MEAN, blk.indptr, blk.src, self.dcat[i][:, d:], self.pad_dst[i - 1],
                                           n_dst_dev=blk.n_dst_dev, d_self=self.dcat[i][:, :d], out=self.dh[i])
                 dz = fastgl.relu_dropout_backward_(self.dh[i], out=self.z[i - 1], p_drop=p if training else 0.0,
@@ -104,8 +165,21 @@ class SageStepProgram:
     def _weight_grad(self, i: int, dz: torch.Tensor) -> None:
         x, gw = self.cat[i], self.layers[i].weight.grad
         s = self.slabs[i]
+        n, k, m = x.size(0), x.size(1), dz.size(1)
+        if self.split:
+            # [X_hi | X_lo]^T [dZ_hi | dZ_lo]: four k x m blocks (the lo-lo block is below float32's rounding; adding it
+            # costs nothing), folded together with the split-K slabs by one reduction -- not by a product with ones,
+            # which would round the partial sums to TF32
+            x2, g2 = self.x3[i][:, : 2 * k], self.g3[i][:, : 2 * m]
+            part = self.part[i]
+            if s:
+                torch.bmm(x2.unflatten(0, (s, n // s)).transpose(1, 2), g2.unflatten(0, (s, n // s)), out=part)
+                torch.sum(part.view(s, 2, k, 2, m), dim=(0, 1, 3), out=gw)
+            else:
+                torch.mm(x2.t(), g2, out=part)
+                torch.sum(part.view(2, k, 2, m), dim=(0, 2), out=gw)
+            return
         if s:
-            n, k, m = x.size(0), x.size(1), dz.size(1)
             torch.bmm(x.view(s, n // s, k).transpose(1, 2), dz.view(s, n // s, m), out=self.part[i])
             torch.mm(self.ones[i], self.part[i].view(s, k * m), out=gw.view(1, k * m))
         else:

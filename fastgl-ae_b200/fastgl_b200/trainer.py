@@ -134,7 +134,7 @@ class GraphedStep:
         self.step_in_graph = tr.world == 1 or tr.oneshot
         self.opt_graph = None
         self.program = SageStepProgram(tr.model, tr.grads, tr.labels, self.x0, self.seeds, self.sizes, self.blocks,
-                                       self.pad_dst, self.sizes[L: L + 1], rng_seed=tr.sampler.rng_seed)
+                                       self.pad_dst, self.sizes[L: L + 1], rng_seed=tr.sampler.rng_seed, matmul=tr.matmul)
 
     def fits(self, counts_row) -> bool:
         L = self.L
@@ -198,7 +198,8 @@ class GraphedStep:
 class Trainer:
     def __init__(self, indptr, indices, feat, labels, train_nids, model, fanouts, batch_size=1024, window=8,
                  lr=0.01, weight_decay=5e-4, reorder=False, rank=0, world=1, rng_seed=12345, n_teams=0,
-                 window_layer0=True, cuda_graph=False, table_direct=True, table_slots=None, grad_sync="auto"):
+                 window_layer0=True, cuda_graph=False, table_direct=True, table_slots=None, grad_sync="auto",
+                 matmul="fp32"):
         self.dev = feat.device
         self.feat, self.labels = feat, labels
         self.model = model
@@ -206,6 +207,9 @@ class Trainer:
         self.batch_size, self.window = int(batch_size), int(window)
         self.rank, self.world = rank, world
         self.n_teams = n_teams
+        # dense products of the hand-written step: "fp32" (cuBLAS SIMT kernels) or "3xtf32" (error-compensated TF32 on
+        # the tensor cores, float32-level error); the autograd fallback always follows torch's global setting
+        self.matmul = matmul
         self.table_direct = bool(table_direct)   # GCN: first layer reads the feature table through the block's ids
         # cap of the sampler's per-team hashtable: None = learn it from the first window, 0 = worst-case size
         self._auto_table = table_slots is None

@@ -358,6 +358,19 @@ int fgl_linear_softmax_xent(fgl_ws* ws, const float* x, int64_t ldx, int32_t k, 
 int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, int64_t n, float lr, float beta1,
                   float beta2, float eps, float weight_decay, int32_t* step_dev, void* stream);
 
+/* Error-compensated operands for tensor-core products of fp32 matrices: hi = x rounded to TF32 (10-bit mantissa,
+ * round to nearest), lo = (x - hi) rounded to TF32; both are stored as fp32 words whose low 13 mantissa bits are
+ * zero, so a TF32 GEMM reads them without loss.  A.B ~= Ahi.Bhi + Alo.Bhi + Ahi.Blo with fp32 accumulation has
+ * fp32-level error (the dropped lo.lo term is 2^-22 relative).  Each part can be written to several destinations
+ * -- row or column blocks of wider matrices -- so that the sum of the three products is one GEMM over a three
+ * times longer inner dimension: [Ahi | Alo | Ahi] . [Bhi ; Bhi ; Blo].  The reference leaves its dense products
+ * to torch::mm (aggregate_acc_kernel.cu:237,368), which on its pinned PyTorch 1.10 ran them in single-pass TF32.
+ * x: rows x cols with leading dimension ldx; dst[q] (q < n_dst <= 8): rows x cols with leading dimension
+ * ld_dst[q], receiving lo if lo_part[q] != 0, else hi.  dst, ld_dst and lo_part are host arrays.  No destination
+ * may overlap x. */
+int fgl_split_tf32(const float* x, int64_t rows, int64_t cols, int64_t ldx, int n_dst, float* const* dst, const int64_t* ld_dst,
+                   const int32_t* lo_part, void* stream);
+
 /* ---- Data-parallel gradient exchange -----------------------------------------------------------------------
  * The reference trains its replicas without synchronising gradients at all (train_fastgl.py:204-212,404-405);
  * a data-parallel run that is to converge like a single-GPU run needs the average of the ranks' gradients before

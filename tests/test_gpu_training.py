@@ -99,7 +99,7 @@ def test_cuda_graph_step_matches_the_op_by_op_step(window_layer0):
     assert graphed.graphed is not None and graphed.graph_fallbacks <= 2
     assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
     for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
-        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=5e-4)    # Adam turns rounding-level gradient differences into lr-sized ones
     assert eager.sampled_edges == graphed.sampled_edges
 
 
@@ -115,7 +115,7 @@ def test_cuda_graph_step_takes_the_short_last_batch_of_an_epoch():
     assert graphed.graph_fallbacks == 0 and graphed.epoch == 1
     assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
     for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
-        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=5e-4)    # Adam turns rounding-level gradient differences into lr-sized ones
     assert eager.sampled_edges == graphed.sampled_edges
 
 
@@ -129,7 +129,7 @@ def test_step_program_with_other_depths(fanouts, hidden):
     assert graphed.graphed is not None and graphed.graph_fallbacks <= 2
     assert np.allclose(le, lg, rtol=1e-4, atol=1e-4), (le, lg)
     for pe, pg in zip(eager.model.parameters(), graphed.model.parameters()):
-        assert torch.allclose(pe, pg, rtol=1e-3, atol=1e-4)
+        assert torch.allclose(pe, pg, rtol=1e-3, atol=5e-4)    # Adam turns rounding-level gradient differences into lr-sized ones
 
 
 def test_step_program_trains_with_dropout():
@@ -415,3 +415,36 @@ def test_match_reorder_trains_the_same_batches_in_another_order():
     assert runs[0][1] == runs[1][1]
     assert sorted(runs[1][2].last_order) == [0, 1, 2, 3]
     assert all(np.isfinite(runs[1][0])) and runs[1][0][-1] < runs[1][0][0] + 0.1
+
+
+def test_the_error_compensated_tf32_step_tracks_the_float32_step_and_the_float64_model():
+    """``matmul="3xtf32"``: every dense product of the hand-written step is three TF32 tensor-core products of split
+    operands.  On the CPU-runnable configuration at full size its losses must agree with the SIMT float32 step to
+    1e-4 over ten steps (single-pass TF32 would be off by 1e-3 and more) and track the float64 trajectory as the
+    float32 step does."""
+    from fastgl_b200.graphgen import rmat_graph, synthetic_node_data
+    from fastgl_b200.layers import GraphSAGE
+    from fastgl_b200.trainer import Trainer
+    import fastgl
+    dev = torch.device("cuda", 0)
+    indptr, indices = rmat_graph(100_000, 20.0, seed=12345, device=dev)
+    feat, labels, train = synthetic_node_data(100_000, 128, 10, 0.10, seed=12345, device=dev)
+    runs = {}
+    for kind in ("fp32", "3xtf32"):
+        torch.manual_seed(12345)
+        model = GraphSAGE(128, 256, 10, 3, dropout=0.0).to(dev)
+        tr = Trainer(indptr, indices, feat, labels, train, model, [15, 10, 5], batch_size=1024, window=8, cuda_graph=True,
+                     matmul=kind)
+        tr.prime()
+        runs[kind] = (np.asarray(tr.run_steps(10, read_loss_each_step=True)),
+                      torch.cat([p.detach().flatten() for p in model.parameters()]).double().cpu())
+        fastgl.check_status(dev)
+        assert tr.graph_fallbacks <= 1
+        assert torch.backends.cuda.matmul.allow_tf32 is False      # the program restores the global setting
+    (l32, p32), (l3x, p3x) = runs["fp32"], runs["3xtf32"]
+    assert np.allclose(l3x, l32, rtol=1e-4, atol=1e-5), (l3x, l32)
+    # Adam divides by the gradient's own magnitude, so a parameter whose gradient is at rounding level can move by the
+    # learning rate in either direction: compare the bulk, not the worst entry
+    diff = (p3x - p32).abs()
+    assert float(diff.mean()) <= 1e-5 and float((diff > 1e-4).double().mean()) <= 1e-3, (float(diff.mean()), float(diff.max()))
+    assert l3x[-1] < l3x[0]

@@ -260,3 +260,55 @@ def test_allreduce_adam_reduces_a_delivered_contribution_and_times_out_on_a_miss
         fastgl.check_status(DEV)
     assert torch.equal(p, before)
     fastgl.check_status(DEV)
+
+
+def test_split_tf32_parts_and_the_three_product_sum_reach_float32_accuracy():
+    """fgl_split_tf32: both parts are TF32-representable, they add up to x within 2^-21 |x|, and
+    A_lo B_hi + A_hi B_lo + A_hi B_hi under TF32 GEMMs is as close to the float64 product as the SIMT float32 GEMM,
+    while a single TF32 pass is an order of magnitude further away (so the test would notice a path that quietly
+    stayed in float32, or one that dropped the correction terms)."""
+    import fastgl
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(1_000_003, device=dev, generator=g) * torch.exp(4 * torch.randn(1_000_003, device=dev, generator=g))
+    x = torch.cat([x, torch.tensor([0.0, -0.0, 1.0, -1.0, 3.4e38, 1e-30], device=dev)])[: 1_000_004].contiguous()
+    hi, lo = fastgl.split_tf32(x)
+    assert int((hi.view(torch.int32) & 0x1FFF).abs().max()) == 0
+    assert int((lo.view(torch.int32) & 0x1FFF).abs().max()) == 0
+    rest = (x.double() - hi.double() - lo.double()).abs()
+    assert bool((rest <= x.double().abs() * 2.0 ** -21 + 1e-45).all())
+    a = torch.randn(4096, 200, device=dev, generator=g)
+    b = torch.randn(200, 256, device=dev, generator=g) * 0.1
+    ref = a.double() @ b.double()
+    scale = float(ref.abs().max())
+    keep = torch.backends.cuda.matmul.allow_tf32
+    try:
+        torch.backends.cuda.matmul.allow_tf32 = False
+        err_f32 = float(((a @ b).double() - ref).abs().max()) / scale
+        torch.backends.cuda.matmul.allow_tf32 = True
+        err_tf32 = float(((a @ b).double() - ref).abs().max()) / scale
+        (ah, al), (bh, bl) = fastgl.split_tf32(a), fastgl.split_tf32(b)
+        c = al @ bh
+        c.addmm_(ah, bl)
+        c.addmm_(ah, bh)
+        err_3x = float((c.double() - ref).abs().max()) / scale
+        # the same sum as one product over a three times longer inner dimension, the parts written in place by the kernel
+        a3 = torch.empty(4096, 600, device=dev)
+        b3 = torch.empty(600, 256, device=dev)
+        fastgl.split_tf32(a, [(a3[:, :200], "hi"), (a3[:, 200:400], "lo"), (a3[:, 400:], "hi")])
+        fastgl.split_tf32(b, [(b3[:200], "hi"), (b3[200:400], "hi"), (b3[400:], "lo")])
+        assert torch.equal(a3[:, :200], ah) and torch.equal(a3[:, 200:400], al) and torch.equal(b3[400:], bl)
+        err_cat = float(((a3 @ b3).double() - ref).abs().max()) / scale
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = keep
+    assert err_3x <= 4 * max(err_f32, 1e-7), (err_3x, err_f32)
+    # one long inner dimension accumulates in the tensor cores' float32 adders only (no SIMT adds between the three
+    # products), which costs a few units in the last place: still two orders of magnitude below a single TF32 pass
+    assert err_cat <= 5e-6, (err_cat, err_f32)
+    assert err_tf32 >= 10 * err_cat, (err_tf32, err_cat)
+    # odd widths take the scalar path
+    y = torch.randn(37, 47, device=dev, generator=g)
+    y3 = torch.zeros(37, 141, device=dev)
+    fastgl.split_tf32(y, [(y3[:, :47], "hi"), (y3[:, 47:94], "lo"), (y3[:, 94:], "hi")])
+    yh, yl = fastgl.split_tf32(y)
+    assert torch.equal(y3[:, :47], yh) and torch.equal(y3[:, 47:94], yl) and torch.equal(y3[:, 94:], yh)
