@@ -532,7 +532,8 @@ def main():
     peak, peak_kind = load_peaks()
     full = [(s_.elapsed_time(e_), fb) for s_, e_, fb in tr.layer0_events if fb.n_batches == args.window]
     agg_ms = [t for t, _ in full]
-    roofline = {"kernel": "agg_fwd_kernel<4, MEAN, row_map> over a window (layer 0)", "bound": "hbm", "achieved": None,
+    roofline = {"kernel": "first-layer aggregation over a window (agg_fwd_staged_kernel<MEAN, row_map> for rows of up to 128 floats, "
+                          "agg_fwd_kernel beyond)", "bound": "hbm", "achieved": None,
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": None, "traffic": None}
     sample_roofline = None
     if agg_ms:

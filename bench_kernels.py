@@ -23,6 +23,11 @@ import torch
 import fastgl
 
 
+def _fwd_kernel_name(dim: int) -> str:
+    """The forward kernel fgl_agg_fwd picks for contiguous rows of ``dim`` floats in one dense table."""
+    return "agg_fwd_staged_kernel" if dim % 4 == 0 and dim <= 128 else "agg_fwd_kernel"
+
+
 def _timed(fn, reps: int, flush: torch.Tensor) -> float:
     """Median milliseconds of ``fn(i)`` over ``reps`` launches, L2 flushed before each."""
     for i in range(2):
@@ -170,13 +175,13 @@ def run(indptr, indices, feat, train, fanouts, batch: int, window: int, peak_gbs
     total = sum(n_dst)
     buf = torch.empty((total, 2 * D), dtype=torch.float32, device=dev)
     ms = _timed(lambda i: fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, feat, buf[:, D:], self_out=buf[:, :D]), reps, flush)
-    entry("agg_fwd_kernel, window mode (fgl_agg_fwd_window)", f"{window} blocks, {total} rows, {sum(n_edges)} edges, D={D}, "
+    entry(f"{_fwd_kernel_name(D)}, window mode (fgl_agg_fwd_window)", f"{window} blocks, {total} rows, {sum(n_edges)} edges, D={D}, "
           "row map + self rows", sum(alg), ms)
     outs = torch.empty((n_dst[0], D), dtype=torch.float32, device=dev)
     r_src = int(torch.unique(fb.block_src[hop][b0, :n_e0]).numel())
     ms = _timed(lambda i: fastgl.aggregate(fastgl.AGG_MEAN, fb.block_indptr[hop][b0], fb.block_src[hop][b0], feat, n_dst0,
                                            zero_deg_passthrough=False, row_map=fb.nodes[b0], out=outs), reps, flush)
-    entry("agg_fwd_kernel, one block (fgl_agg_fwd)", f"{n_dst0} rows, {n_e0} edges, D={D}, row map",
+    entry(f"{_fwd_kernel_name(D)}, one block (fgl_agg_fwd)", f"{n_dst0} rows, {n_e0} edges, D={D}, row map",
           4 * D * (r_src + n_dst0) + 4 * r_src + 4 * n_e0 + 4 * (n_dst0 + 1), ms)
     del buf, outs
 
@@ -192,7 +197,7 @@ def run(indptr, indices, feat, train, fanouts, batch: int, window: int, peak_gbs
             kw = dict(src_norm_degs=src_deg, dst_norm_degs=dst_deg) if mode == fastgl.AGG_SYMNORM else {}
             ms = _timed(lambda i: fastgl.aggregate(mode, ptr_b, src_b, x, n_dst0, out=y, **kw), reps, flush)
             extra = 4 * (n_src0 + n_dst0) if mode == fastgl.AGG_SYMNORM else 0
-            entry(f"agg_fwd_kernel {label} (fgl_agg_fwd)", f"{n_dst0} rows, {n_e0} edges, {r_src} distinct sources, D={dim}",
+            entry(f"{_fwd_kernel_name(dim)} {label} (fgl_agg_fwd)", f"{n_dst0} rows, {n_e0} edges, {r_src} distinct sources, D={dim}",
                   4 * dim * (r_src + n_dst0) + 4 * n_e0 + 4 * (n_dst0 + 1) + extra, ms)
         dy = torch.randn((n_dst0, dim), device=dev)
         ms = _timed(lambda i: res.__setitem__("dx", fastgl.aggregate_backward(fastgl.AGG_MEAN, ptr_b, src_b, dy, n_src0)), reps, flush)

@@ -330,11 +330,14 @@ def random_block(rng, n_dst, n_src, max_deg, zero_frac=0.1):
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
-@pytest.mark.parametrize("dim", [1, 47, 100, 128, 256, 602, 1024])
+@pytest.mark.parametrize("dim", [1, 6, 47, 100, 128, 130, 256, 260, 602, 1024])
 def test_aggregate_forward_backward(fastgl, mode, dim):
+    """Every forward kernel: rows staged through one 512-byte slot (100, 128), wider rows swept with several
+    accumulators and a ragged last pass (130, 260, 602), 8-byte-aligned strides (6, 130, 602), odd widths (1, 47);
+    in-degrees up to 40, i.e. beyond the 15 rows of a staged pass and beyond the 32 ids a warp keeps in registers."""
     rng = np.random.default_rng(dim * 3 + mode)
     n_dst, n_src = 700, 2500
-    indptr, src = random_block(rng, n_dst, n_src, 40 if dim < 600 else 15)
+    indptr, src = random_block(rng, n_dst, n_src, 40)
     x = rng.standard_normal((n_src, dim)).astype(np.float32)
     dy = rng.standard_normal((n_dst, dim)).astype(np.float32)
     sdeg = np.maximum(oc.cal_deg(src, n_src), 1)
@@ -349,11 +352,12 @@ def test_aggregate_forward_backward(fastgl, mode, dim):
 
 @pytest.mark.parametrize("mode", [0, 2])
 @pytest.mark.parametrize("with_map", [False, True])
-def test_aggregate_reports_an_out_of_range_id_and_matches_the_oracle_without_it(fastgl, mode, with_map):
+@pytest.mark.parametrize("dim", [100, 602])
+def test_aggregate_reports_an_out_of_range_id_and_matches_the_oracle_without_it(fastgl, mode, with_map, dim):
     """One edge carries a source id beyond the input rows (and one a negative id): the ids are never dereferenced,
     the status word reports them, and the result equals the oracle's on the block with those two edges removed."""
     rng = np.random.default_rng(99 + mode)
-    n_dst, n_src, n_table, dim = 300, 900, 5000, 100
+    n_dst, n_src, n_table = 300, 900, 5000
     indptr, src = random_block(rng, n_dst, n_src, 40, zero_frac=0.0)
     row_map = rng.permutation(n_table)[:n_src].astype(np.int32) if with_map else None
     table = rng.standard_normal((n_table if with_map else n_src, dim)).astype(np.float32)
@@ -508,7 +512,7 @@ def test_bounded_barrier_wait_runs_out_and_the_workspace_recovers(fastgl):
     assert torch.equal(out[1:].long(), torch.cumsum(degs.long(), 0))
 
 
-@pytest.mark.parametrize("dim", [100, 128, 256])
+@pytest.mark.parametrize("dim", [100, 128, 256, 602])
 def test_aggregate_sampled_block_shapes_with_row_map(fastgl, dim):
     # in-degrees 0..15 (the sampled-block case) plus a few long rows, both zero-degree conventions
     rng = np.random.default_rng(dim)
@@ -529,11 +533,12 @@ def test_aggregate_sampled_block_shapes_with_row_map(fastgl, dim):
     fastgl.check_status()
 
 
-def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph):
+@pytest.mark.parametrize("dim", [100, 602, 1024])
+def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph, dim):
     indptr, indices = graph
     rng = np.random.default_rng(23)
     n = len(indptr) - 1
-    feat = rng.standard_normal((n, 100)).astype(np.float32)
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
     seeds = rng.choice(n, size=(5, 200), replace=False).astype(np.int32)
     counts = np.array([200, 200, 7, 0, 200], dtype=np.int32)
     fan = [5, 10, 15]
@@ -542,8 +547,8 @@ def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph):
     hop = 2
     total = int(fb.counts_host()[:, hop].sum())
     for _ in range(1):
-        out = torch.full((total, 100), 7.0, device=dev())
-        self_out = torch.full((total, 100), 7.0, device=dev())
+        out = torch.full((total, dim), 7.0, device=dev())
+        self_out = torch.full((total, dim), 7.0, device=dev())
         row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, d_feat, out, self_out=self_out)
         assert row_off[-1] == total
         for b in range(5):
