@@ -72,9 +72,20 @@ bias_relu_dropout_kernel(float* __restrict__ y, int64_t ld, int64_t n_rows, int 
 constexpr int kBwdMaxColsPerThread = 8;   // dim <= 8 * 256
 constexpr int kBwdRowBatch = 8;
 
+// SPLIT: dz is not written back over dy but as [hi | lo | hi] TF32 parts (see split_tf32_kernel) into split3, the three
+// blocks block_stride columns apart: the form in which the error-compensated products read it.
+// x rounded to TF32 (10-bit mantissa, round to nearest), as an fp32 value
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+template <bool SPLIT>
 __global__ void __launch_bounds__(kEwThreads)
 relu_dropout_bwd_kernel(float* __restrict__ dy, int64_t ldy, const float* __restrict__ out, int64_t ldo, int64_t n_rows,
-                        int rows_per_cta, int dim, float keep_scale, float* __restrict__ dbias, int flags) {
+                        int rows_per_cta, int dim, float keep_scale, float* __restrict__ dbias, int flags,
+                        float* __restrict__ split3, int64_t ld3, int block_stride) {
     const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
     const int64_t r1 = r0 + rows_per_cta < n_rows ? r0 + rows_per_cta : n_rows;
     const bool mask = flags & FGL_EW_RELU;
@@ -90,8 +101,16 @@ relu_dropout_bwd_kernel(float* __restrict__ dy, int64_t ldy, const float* __rest
             }
 #pragma unroll
             for (int k = 0; k < kBwdRowBatch; ++k) {
-                if (mask) {
-                    g[k] = o[k] > 0.f ? g[k] * keep_scale : 0.f;
+                if (mask) g[k] = o[k] > 0.f ? g[k] * keep_scale : 0.f;
+                if (SPLIT) {
+                    if (r + k < r1) {
+                        const float h = to_tf32(g[k]), l = to_tf32(g[k] - h);
+                        float* d3 = split3 + (r + k) * ld3 + c;
+                        d3[0] = h;
+                        d3[block_stride] = l;
+                        d3[2 * block_stride] = h;
+                    }
+                } else if (mask) {
                     if (r + k < r1) dy[(r + k) * ldy + c] = g[k];
                 }
                 acc += g[k];
@@ -353,12 +372,6 @@ struct SplitDst {
     int n;
 };
 
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
-}
-
 template <bool VEC4>
 __global__ void __launch_bounds__(kEwThreads)
 split_tf32_kernel(const float* __restrict__ x, int64_t rows, int cols, int64_t ldx, const SplitDst d) {
@@ -380,6 +393,23 @@ split_tf32_kernel(const float* __restrict__ x, int64_t rows, int cols, int64_t l
             const float h = to_tf32(v), l = to_tf32(v - h);
             for (int q = 0; q < d.n; ++q) d.ptr[q][r * d.ld[q] + c] = d.lo_part[q] ? l : h;
         }
+    }
+}
+
+// out[r, c] = sum over slabs s and blocks (a, b) of part[s][a * rows + r][b * block_stride + c]: folds the 2 x 2 block
+// product [X_hi | X_lo]^T [dZ_hi | dZ_lo] (and its split-K slabs) into the weight gradient.  A thread per output.
+__global__ void __launch_bounds__(kEwThreads)
+fold_blocks_kernel(const float* __restrict__ part, int n_slabs, int n_a, int n_b, int rows, int cols, int block_stride,
+                   int64_t ld_part, int64_t slab_stride, float* __restrict__ out, int64_t ldo) {
+    const int64_t total = (int64_t)rows * cols;
+    for (int64_t g = (int64_t)blockIdx.x * kEwThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kEwThreads) {
+        const int r = (int)(g / cols), c = (int)(g - (int64_t)r * cols);
+        float acc = 0.f;
+        for (int s = 0; s < n_slabs; ++s)
+            for (int a = 0; a < n_a; ++a)
+                for (int b = 0; b < n_b; ++b)
+                    acc += part[s * slab_stride + ((int64_t)a * rows + r) * ld_part + (int64_t)b * block_stride + c];
+        out[(int64_t)r * ldo + c] = acc;
     }
 }
 
@@ -421,21 +451,41 @@ int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, con
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 
-int fgl_relu_dropout_bwd(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
-                         float* dbias, int32_t flags, void* stream) {
+static int relu_dropout_bwd_launch(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
+                                   float* dbias, int32_t flags, float* split3, int64_t ld3, int64_t block_stride, void* stream) {
     if (n_rows < 0 || dim <= 0 || dim > kBwdMaxColsPerThread * kEwThreads || ldy < dim || (n_rows > 0 && !dy) ||
         !(p_drop >= 0.f && p_drop < 1.f))
         return FGL_ERR_INVALID;
     if ((flags & FGL_EW_RELU) && (!out || ldo < dim)) return FGL_ERR_INVALID;
+    if (split3 && (block_stride < dim || block_stride > 0x3fffffffLL || ld3 < 2 * block_stride + dim)) return FGL_ERR_INVALID;
     if (n_rows == 0) return FGL_OK;
     // bands of 8..64 rows, sized so that the grid has at least two CTAs per SM where the matrix allows it
     int64_t rows_per_cta = (n_rows / (2 * 148)) / kBwdRowBatch * kBwdRowBatch;
-    rows_per_cta = rows_per_cta < kBwdRowBatch ? kBwdRowBatch : (rows_per_cta > 64 ? 64 : rows_per_cta);
+    const int64_t band_max = split3 ? 16 : 64;   // three stores per element: shorter bands, more CTAs in flight
+    rows_per_cta = rows_per_cta < kBwdRowBatch ? kBwdRowBatch : (rows_per_cta > band_max ? band_max : rows_per_cta);
     const int64_t blocks = (n_rows + rows_per_cta - 1) / rows_per_cta;
     if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
-    relu_dropout_bwd_kernel<<<(unsigned)blocks, kEwThreads, 0, (cudaStream_t)stream>>>(
-        dy, ldy, out, ldo, n_rows, (int)rows_per_cta, dim, p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f, dbias, flags);
+    const float keep = p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f;
+    if (split3)
+        relu_dropout_bwd_kernel<true><<<(unsigned)blocks, kEwThreads, 0, (cudaStream_t)stream>>>(
+            dy, ldy, out, ldo, n_rows, (int)rows_per_cta, dim, keep, dbias, flags, split3, ld3, (int)block_stride);
+    else
+        relu_dropout_bwd_kernel<false><<<(unsigned)blocks, kEwThreads, 0, (cudaStream_t)stream>>>(
+            dy, ldy, out, ldo, n_rows, (int)rows_per_cta, dim, keep, dbias, flags, nullptr, 0, 0);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_relu_dropout_bwd(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
+                         float* dbias, int32_t flags, void* stream) {
+    return relu_dropout_bwd_launch(dy, ldy, out, ldo, n_rows, dim, p_drop, dbias, flags, nullptr, 0, 0, stream);
+}
+
+int fgl_relu_dropout_bwd_split(const float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim,
+                               float p_drop, float* dbias, int32_t flags, float* split3, int64_t ld3, int64_t block_stride,
+                               void* stream) {
+    if (!split3) return FGL_ERR_INVALID;
+    return relu_dropout_bwd_launch(const_cast<float*>(dy), ldy, out, ldo, n_rows, dim, p_drop, dbias, flags, split3, ld3,
+                                   block_stride, stream);
 }
 
 int fgl_softmax_xent(fgl_ws* ws, const float* logits, int64_t ld, const int64_t* labels, const int32_t* label_ids,
@@ -508,6 +558,18 @@ int fgl_split_tf32(const float* x, int64_t rows, int64_t cols, int64_t ldx, int 
         split_tf32_kernel<true><<<ew_grid(items), kEwThreads, 0, (cudaStream_t)stream>>>(x, rows, (int)cols, ldx, d);
     else
         split_tf32_kernel<false><<<ew_grid(items), kEwThreads, 0, (cudaStream_t)stream>>>(x, rows, (int)cols, ldx, d);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_fold_blocks(const float* part, int32_t n_slabs, int32_t n_a, int32_t n_b, int32_t rows, int32_t cols, int32_t block_stride,
+                    int64_t ld_part, int64_t slab_stride, float* out, int64_t ldo, void* stream) {
+    if (n_slabs < 1 || n_a < 1 || n_b < 1 || rows < 0 || cols < 0 || block_stride < cols || ldo < cols ||
+        ld_part < (int64_t)(n_b - 1) * block_stride + cols || slab_stride < (int64_t)n_a * rows * ld_part)
+        return FGL_ERR_INVALID;
+    if (rows == 0 || cols == 0) return FGL_OK;
+    if (!part || !out) return FGL_ERR_INVALID;
+    fold_blocks_kernel<<<ew_grid((int64_t)rows * cols), kEwThreads, 0, (cudaStream_t)stream>>>(
+        part, n_slabs, n_a, n_b, rows, cols, block_stride, ld_part, slab_stride, out, ldo);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

@@ -33,7 +33,7 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
-    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block", "split_tf32",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block", "split_tf32", "split_tf32_raw", "fold_blocks",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -535,9 +535,11 @@ def bias_relu_dropout_(y, bias=None, p_drop=0.0, relu=True, rng_seed=None, rng_c
     return y
 
 
-def relu_dropout_backward_(dy, out=None, p_drop=0.0, dbias=None, masked=True):
+def relu_dropout_backward_(dy, out=None, p_drop=0.0, dbias=None, masked=True, split3=None, block_stride=None):
     """In place over ``dy``: the gradient through dropout(relu(.)) given the forward output ``out`` (``masked``), and
-    ``dbias += column sums`` of the result.  Returns ``dy``."""
+    ``dbias += column sums`` of the result.  Returns ``dy``.  With ``split3`` (a float32 matrix of ``dy``'s rows) the
+    result is written there instead, as ``[hi | lo | hi]`` TF32 parts ``block_stride`` (default: ``dy``'s width) columns
+    apart, and ``dy`` is left as it was; returns ``split3``."""
     _check_rows_f32(dy, "dy")
     if masked:
         _check_rows_f32(out, "out")
@@ -548,6 +550,19 @@ def relu_dropout_backward_(dy, out=None, p_drop=0.0, dbias=None, masked=True):
         if dbias.numel() != dy.size(1):
             raise RuntimeError("dbias must have one entry per column")
     dev = dy.device
+    if split3 is not None:
+        _check_rows_f32(split3, "split3")
+        bs = dy.size(1) if block_stride is None else int(block_stride)
+        if split3.size(0) != dy.size(0) or bs < dy.size(1) or split3.size(1) < 2 * bs + dy.size(1):
+            raise RuntimeError("split3 must have dy's rows and room for three blocks block_stride columns apart")
+        with _on_device(dev):
+            rc = lib().fgl_relu_dropout_bwd_split(_ptr(dy), ctypes.c_int64(dy.stride(0)), _ptr(out if masked else None),
+                                                  ctypes.c_int64(out.stride(0) if masked else dy.size(1)), ctypes.c_int64(dy.size(0)),
+                                                  ctypes.c_int32(dy.size(1)), ctypes.c_float(p_drop), _ptr(dbias),
+                                                  ctypes.c_int32(1 if masked else 0), _ptr(split3), ctypes.c_int64(split3.stride(0)),
+                                                  ctypes.c_int64(bs), _stream(dev))
+        _raise(rc, "relu_dropout_backward_")
+        return split3
     with _on_device(dev):
         rc = lib().fgl_relu_dropout_bwd(_ptr(dy), ctypes.c_int64(dy.stride(0)), _ptr(out if masked else None),
                                         ctypes.c_int64(out.stride(0) if masked else dy.size(1)), ctypes.c_int64(dy.size(0)),
@@ -684,6 +699,38 @@ def split_tf32(x, dst=None):
                                   ctypes.c_int(len(dst)), ptrs, lds, parts, _stream(dev))
     _raise(rc, "split_tf32")
     return ret
+
+
+def fold_blocks(part, n_a, n_b, rows, cols, block_stride, out):
+    """``out[r, c] = sum_{s, a, b} part[s, a * rows + r, b * block_stride + c]`` (``fgl_fold_blocks``): ``part`` is a
+    contiguous float32 tensor ``[slabs, n_a * rows, width]`` or ``[n_a * rows, width]``."""
+    _check_f32(part, "part")
+    _check_rows_f32(out, "out")
+    if part.dim() == 2:
+        part = part.unsqueeze(0)
+    if part.dim() != 3 or part.size(1) != n_a * rows or tuple(out.shape) != (rows, cols):
+        raise RuntimeError("part must be [slabs, n_a * rows, width] and out [rows, cols]")
+    dev = part.device
+    with _on_device(dev):
+        rc = lib().fgl_fold_blocks(_ptr(part), ctypes.c_int32(part.size(0)), ctypes.c_int32(n_a), ctypes.c_int32(n_b),
+                                   ctypes.c_int32(rows), ctypes.c_int32(cols), ctypes.c_int32(block_stride),
+                                   ctypes.c_int64(part.size(2)), ctypes.c_int64(part.size(1) * part.size(2)), _ptr(out),
+                                   ctypes.c_int64(out.stride(0)), _stream(dev))
+    _raise(rc, "fold_blocks")
+    return out
+
+
+def split_tf32_raw(src_ptr: int, rows: int, cols: int, ldx: int, dst, device) -> None:
+    """``split_tf32`` on raw addresses: ``dst`` is a list of ``(address, leading dimension, is_lo)``.  For per-step
+    staging, where building tensor views would cost more host time than the launch."""
+    n = len(dst)
+    ptrs = (ctypes.c_void_p * n)(*[d[0] for d in dst])
+    lds = (ctypes.c_int64 * n)(*[d[1] for d in dst])
+    parts = (ctypes.c_int32 * n)(*[int(bool(d[2])) for d in dst])
+    with _on_device(device):
+        rc = lib().fgl_split_tf32(ctypes.c_void_p(src_ptr), ctypes.c_int64(rows), ctypes.c_int64(cols), ctypes.c_int64(ldx),
+                                  ctypes.c_int(n), ptrs, lds, parts, _stream(device))
+    _raise(rc, "split_tf32_raw")
 
 
 class PeerSync:

@@ -66,29 +66,40 @@ class SageStepProgram:
         if matmul not in ("fp32", "3xtf32"):
             raise ValueError("matmul must be 'fp32' or '3xtf32'")
         self.split = matmul == "3xtf32"
+        # set by a caller that fills x3[0] itself while it stages the mini-batch (then cat[0] is not read at all)
+        self.x0_presplit = False
         if self.split:
             ks = [2 * d for d in ins]
+            # block width of the output-side operands: a multiple of four floats, so that every block starts 16-byte
+            # aligned and cuBLAS can use its vectorised tensor-core kernels (47 classes -> 48; the padding stays zero)
+            self.mp = [(m + 3) // 4 * 4 for m in outs]
             # [X_hi | X_lo | X_hi] of every layer input, [dZ_hi | dZ_lo | dZ_hi] of every output gradient,
             # [W_hi ; W_hi ; W_lo] (forward) and [W_hi | W_hi | W_lo] (input gradient) of every weight
             self.x3 = [torch.zeros((self.pad_dst[i], 3 * ks[i]), **f32) for i in range(L)]
-            self.g3 = [torch.zeros((self.pad_dst[i], 3 * outs[i]), **f32) for i in range(L)]
+            self.g3 = [torch.zeros((self.pad_dst[i], 3 * self.mp[i]), **f32) for i in range(L)]
             self.wv3 = [torch.zeros((3 * ks[i], outs[i]), **f32) for i in range(L)]
-            self.wc3 = [torch.zeros((ks[i], 3 * outs[i]), **f32) for i in range(L)]
-            self.part = [torch.zeros((s, 2 * ks[i], 2 * outs[i]), **f32) if s else torch.zeros((2 * ks[i], 2 * outs[i]), **f32)
+            self.wc3 = [torch.zeros((ks[i], 3 * self.mp[i]), **f32) for i in range(L)]
+            # the tensor cores need far fewer split-K slabs than the SIMT product to fill the GPU, and every slab is
+            # 2k x 2m floats that the fold has to read back
+            self.slabs = [next((s for s in (8, 4) if n % s == 0 and n // s >= 256), 0) for n in self.pad_dst]
+            self.part = [torch.zeros((s, 2 * ks[i], 2 * self.mp[i]), **f32) if s else torch.zeros((2 * ks[i], 2 * self.mp[i]), **f32)
                          for i, s in enumerate(self.slabs)]
 
     # ---- operands of the error-compensated products ------------------------------------------------------------------
     @staticmethod
-    def _split3(x, x3):
+    def _split3(x, x3, width=None):
+        """[hi | lo | hi] of ``x`` into ``x3``, whose three blocks are ``width`` (default: ``x``'s) columns apart."""
         c = x.size(1)
-        fastgl.split_tf32(x, [(x3[:, :c], "hi"), (x3[:, c: 2 * c], "lo"), (x3[:, 2 * c:], "hi")])
+        w = c if width is None else width
+        fastgl.split_tf32(x, [(x3[:, :c], "hi"), (x3[:, w: w + c], "lo"), (x3[:, 2 * w: 2 * w + c], "hi")])
 
     def _split_weight(self, i):
         w = self.layers[i].weight.data
         k, m = w.shape
+        mp = self.mp[i]
         v, c = self.wv3[i], self.wc3[i]
         fastgl.split_tf32(w, [(v[:k], "hi"), (v[k: 2 * k], "hi"), (v[2 * k:], "lo"),
-                              (c[:, :m], "hi"), (c[:, m: 2 * m], "hi"), (c[:, 2 * m:], "lo")])
+                              (c[:, :m], "hi"), (c[:, mp: mp + m], "hi"), (c[:, 2 * mp: 2 * mp + m], "lo")])
 
     def forward_backward(self) -> torch.Tensor:
         """Forward, loss and backward; the parameter gradients land in the flat gradient buffer.  Returns the loss
@@ -117,7 +128,8 @@ class SageStepProgram:
             if i == L - 1 and fused_head:
                 break
             if split:
-                self._split3(self.cat[i], self.x3[i])
+                if not (i == 0 and self.x0_presplit):
+                    self._split3(self.cat[i], self.x3[i])
                 x_split.add(i)
                 torch.mm(self.x3[i], self.wv3[i], out=self.z[i])
             else:
@@ -145,7 +157,8 @@ class SageStepProgram:
             if i == L - 1 and not fused_head:
                 fastgl.relu_dropout_backward_(dz, masked=False, dbias=layer.bias.grad)
             if split:
-                self._split3(dz, self.g3[i])
+                if dz is not None:          # the output layer's gradient; the inner ones were written split already
+                    self._split3(dz, self.g3[i], self.mp[i])
                 if i not in x_split:
                     self._split3(self.cat[i], self.x3[i])
             self._weight_grad(i, dz)
@@ -158,26 +171,32 @@ class SageStepProgram:
                     torch.mm(dz, layer.weight.t(), out=self.dcat[i])
                 fastgl.aggregate_backward(fastgl.AGG_MEAN, blk.indptr, blk.src, self.dcat[i][:, d:], self.pad_dst[i - 1],
                                           n_dst_dev=blk.n_dst_dev, d_self=self.dcat[i][:, :d], out=self.dh[i])
-                dz = fastgl.relu_dropout_backward_(self.dh[i], out=self.z[i - 1], p_drop=p if training else 0.0,
-                                                   dbias=self.layers[i - 1].bias.grad)
+                if split:       # straight into the operand form of layer i - 1's two gradient products
+                    fastgl.relu_dropout_backward_(self.dh[i], out=self.z[i - 1], p_drop=p if training else 0.0,
+                                                  dbias=self.layers[i - 1].bias.grad, split3=self.g3[i - 1],
+                                                  block_stride=self.mp[i - 1])
+                    dz = None
+                else:
+                    dz = fastgl.relu_dropout_backward_(self.dh[i], out=self.z[i - 1], p_drop=p if training else 0.0,
+                                                       dbias=self.layers[i - 1].bias.grad)
         return self.loss
 
-    def _weight_grad(self, i: int, dz: torch.Tensor) -> None:
+    def _weight_grad(self, i: int, dz=None) -> None:
         x, gw = self.cat[i], self.layers[i].weight.grad
         s = self.slabs[i]
-        n, k, m = x.size(0), x.size(1), dz.size(1)
+        n, k, m = x.size(0), x.size(1), gw.size(1)
         if self.split:
             # [X_hi | X_lo]^T [dZ_hi | dZ_lo]: four k x m blocks (the lo-lo block is below float32's rounding; adding it
             # costs nothing), folded together with the split-K slabs by one reduction -- not by a product with ones,
             # which would round the partial sums to TF32
-            x2, g2 = self.x3[i][:, : 2 * k], self.g3[i][:, : 2 * m]
+            mp = self.mp[i]
+            x2, g2 = self.x3[i][:, : 2 * k], self.g3[i][:, : 2 * mp]
             part = self.part[i]
             if s:
                 torch.bmm(x2.unflatten(0, (s, n // s)).transpose(1, 2), g2.unflatten(0, (s, n // s)), out=part)
-                torch.sum(part.view(s, 2, k, 2, m), dim=(0, 1, 3), out=gw)
             else:
                 torch.mm(x2.t(), g2, out=part)
-                torch.sum(part.view(2, k, 2, m), dim=(0, 2), out=gw)
+            fastgl.fold_blocks(part, 2, 2, k, m, mp, gw)
             return
         if s:
             torch.bmm(x.view(s, n // s, k).transpose(1, 2), dz.view(s, n // s, m), out=self.part[i])

@@ -135,6 +135,7 @@ class GraphedStep:
         self.opt_graph = None
         self.program = SageStepProgram(tr.model, tr.grads, tr.labels, self.x0, self.seeds, self.sizes, self.blocks,
                                        self.pad_dst, self.sizes[L: L + 1], rng_seed=tr.sampler.rng_seed, matmul=tr.matmul)
+        self.program.x0_presplit = self.program.split
 
     def fits(self, counts_row) -> bool:
         L = self.L
@@ -147,9 +148,18 @@ class GraphedStep:
         buf, row_off = layer0
         n_dst = [int(counts_row[L - 1 - i]) for i in range(L)]
         row_bytes = buf.stride(0) * 4
-        segs = [(self.x0.data_ptr(), buf.data_ptr() + row_off[b] * row_bytes, n_dst[0] * row_bytes),
-                # only the batch's own seeds: the rows after a short batch keep earlier (valid) node ids
-                (self.seeds.data_ptr(), fb.nodes.data_ptr() + b * fb.nodes.stride(0) * 4, n_dst[L - 1] * 4)]
+        # only the batch's own seeds: the rows after a short batch keep earlier (valid) node ids
+        segs = [(self.seeds.data_ptr(), fb.nodes.data_ptr() + b * fb.nodes.stride(0) * 4, n_dst[L - 1] * 4)]
+        prog = self.program
+        if prog.split:
+            # the input layer's rows go straight from the window buffer into the operand form of the error-compensated
+            # products, [hi | lo | hi]; the plain copy in x0 is not needed
+            x3, c = prog.x3[0], buf.size(1)
+            base, ld3 = x3.data_ptr(), x3.stride(0)
+            fastgl.split_tf32_raw(buf.data_ptr() + row_off[b] * row_bytes, n_dst[0], c, buf.stride(0),
+                                  [(base, ld3, 0), (base + 4 * c, ld3, 1), (base + 8 * c, ld3, 0)], self.tr.dev)
+        else:
+            segs.append((self.x0.data_ptr(), buf.data_ptr() + row_off[b] * row_bytes, n_dst[0] * row_bytes))
         for i in range(1, L):
             h = L - 1 - i
             ptr, src = fb.block_indptr[h], fb.block_src[h]

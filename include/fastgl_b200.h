@@ -330,6 +330,13 @@ int fgl_bias_relu_dropout(float* y, int64_t ld, int64_t n_rows, int32_t dim, con
 int fgl_relu_dropout_bwd(float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim, float p_drop,
                          float* dbias, int32_t flags, void* stream);
 
+/* fgl_relu_dropout_bwd whose result is not written back over dy but as error-compensated TF32 operands (see
+ * fgl_split_tf32): split3[r, c] = hi, split3[r, block_stride + c] = lo, split3[r, 2 * block_stride + c] = hi of
+ * dz[r, c]; split3 has leading dimension ld3 >= 2 * block_stride + dim.  dy is only read. */
+int fgl_relu_dropout_bwd_split(const float* dy, int64_t ldy, const float* out, int64_t ldo, int64_t n_rows, int32_t dim,
+                               float p_drop, float* dbias, int32_t flags, float* split3, int64_t ld3, int64_t block_stride,
+                               void* stream);
+
 /* Mean softmax cross-entropy over the first n_valid rows and its gradient.  The label of row r is
  * labels[label_ids ? label_ids[r] : r] (labels: int64[n_labels], values in [0, n_classes); an index or a label
  * outside its range records FGL_ERR_BOUNDS in the workspace's status word and the row contributes nothing).  n_valid is read from n_valid_dev[0] when that is not NULL.
@@ -370,6 +377,13 @@ int fgl_adam_step(float* param, const float* grad, float* exp_avg, float* exp_av
  * may overlap x. */
 int fgl_split_tf32(const float* x, int64_t rows, int64_t cols, int64_t ldx, int n_dst, float* const* dst, const int64_t* ld_dst,
                    const int32_t* lo_part, void* stream);
+
+/* out[r, c] = sum over s < n_slabs, a < n_a, b < n_b of part[s][a * rows + r][b * block_stride + c], part being
+ * n_slabs matrices of n_a * rows rows with leading dimension ld_part, slab_stride floats apart.  Folds the 2 x 2
+ * block product [X_hi | X_lo]^T [dZ_hi | dZ_lo] of split operands (fgl_split_tf32) and its split-K slabs into the
+ * rows x cols weight gradient, in float32 (a product with a vector of ones would round the partial sums to TF32). */
+int fgl_fold_blocks(const float* part, int32_t n_slabs, int32_t n_a, int32_t n_b, int32_t rows, int32_t cols, int32_t block_stride,
+                    int64_t ld_part, int64_t slab_stride, float* out, int64_t ldo, void* stream);
 
 /* ---- Data-parallel gradient exchange -----------------------------------------------------------------------
  * The reference trains its replicas without synchronising gradients at all (train_fastgl.py:204-212,404-405);

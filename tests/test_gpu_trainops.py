@@ -312,3 +312,33 @@ def test_split_tf32_parts_and_the_three_product_sum_reach_float32_accuracy():
     fastgl.split_tf32(y, [(y3[:, :47], "hi"), (y3[:, 47:94], "lo"), (y3[:, 94:], "hi")])
     yh, yl = fastgl.split_tf32(y)
     assert torch.equal(y3[:, :47], yh) and torch.equal(y3[:, 47:94], yl) and torch.equal(y3[:, 94:], yh)
+
+
+def test_fold_blocks_and_the_split_form_of_the_relu_backward():
+    """fgl_fold_blocks against torch's sum over slabs and blocks; fgl_relu_dropout_bwd_split against the in-place
+    backward followed by fgl_split_tf32 (same parts bit for bit, same bias gradient, dy untouched)."""
+    import fastgl
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(9)
+    part = torch.randn(3, 2 * 50, 2 * 48, device=dev, generator=g)
+    out = torch.full((50, 47), 9.0, device=dev)
+    fastgl.fold_blocks(part, 2, 2, 50, 47, 48, out)
+    ref = part.view(3, 2, 50, 2, 48)[..., :47].double().sum(dim=(0, 1, 3))
+    assert float((out.double() - ref).abs().max()) <= 1e-5
+    one = torch.randn(2 * 50, 2 * 48, device=dev, generator=g)
+    fastgl.fold_blocks(one, 2, 2, 50, 47, 48, out)
+    assert float((out.double() - one.view(2, 50, 2, 48)[..., :47].double().sum(dim=(0, 2))).abs().max()) <= 1e-5
+
+    for rows, dim, stride in ((1000, 256, 256), (37, 47, 48), (5000, 64, 64)):
+        dy = torch.randn(rows, dim, device=dev, generator=g)
+        fwd = torch.relu(torch.randn(rows, dim, device=dev, generator=g))
+        keep = dy.clone()
+        plain, db_plain = dy.clone(), torch.zeros(dim, device=dev)
+        fastgl.relu_dropout_backward_(plain, out=fwd, p_drop=0.5, dbias=db_plain)
+        hi, lo = fastgl.split_tf32(plain)
+        s3, db = torch.zeros(rows, 3 * stride, device=dev), torch.zeros(dim, device=dev)
+        got = fastgl.relu_dropout_backward_(dy, out=fwd, p_drop=0.5, dbias=db, split3=s3, block_stride=stride)
+        assert got is s3 and torch.equal(dy, keep)
+        assert torch.equal(s3[:, :dim], hi) and torch.equal(s3[:, stride: stride + dim], lo)
+        assert torch.equal(s3[:, 2 * stride: 2 * stride + dim], hi)
+        assert torch.allclose(db, db_plain, rtol=1e-4, atol=1e-3)      # other bands, another order of the column sums
