@@ -116,6 +116,30 @@ def run(indptr, indices, feat, train, fanouts, batch: int, window: int, peak_gbs
           note=f"{edges / (ms_cap * 1e-3) / 1e6:.0f} M sampled edges/s; the default above uses 4 teams and worst-case tables")
     del capped
 
+    # what the memory system sustains for the sampler's access pattern alone: isolated 4-byte reads in this graph's
+    # adjacency array, then the same followed by a probe of as many table bytes as the launch above holds
+    n_tables = min(window, 16)
+    probe_table = torch.zeros(1 << max(12, math.ceil(math.log2(n_tables * cap_slots))), dtype=torch.int64, device=dev)
+    acc = {}
+
+    def probe_reads(i):
+        acc["n"] = fastgl.probe_access_pattern(indices, None, iters=64)
+    ms_p = _timed(probe_reads, reps, flush)
+    entry("access probe: isolated 4-byte reads (fgl_probe_access_pattern)", f"{indices.numel() * 4 / 1e6:.0f} MB adjacency array, "
+          f"{acc['n']} reads", 32 * acc["n"], ms_p,
+          note=f"{acc['n'] / (ms_p * 1e-3) / 1e9:.1f} G reads/s; bytes = 32 per read, the sector the sampler's formula charges per pick")
+
+    def probe_pairs(i):
+        probe_table.zero_()
+        acc["n"] = fastgl.probe_access_pattern(indices, probe_table, iters=64)
+    t_zero = _timed(lambda i: probe_table.zero_(), reps, flush)
+    ms_pp = max(_timed(probe_pairs, reps, flush) - t_zero, 1e-6)
+    entry("access probe: read + dependent table probe (fgl_probe_access_pattern)", f"{indices.numel() * 4 / 1e6:.0f} MB adjacency array, "
+          f"{probe_table.numel() * 8 / 1e6:.0f} MB of table, {acc['n']} pairs", 40 * acc["n"], ms_pp,
+          note=f"{acc['n'] / (ms_pp * 1e-3) / 1e9:.1f} G pairs/s against the sampler's {edges / (ms_cap * 1e-3) / 1e9:.1f} G edges/s; "
+               "bytes = 32 + 8 per pair; the time of zero-filling the table is subtracted")
+    del probe_table
+
     # the reference's own numbering (atomic arrival order) skips the two ranking phases
     arr = {"fb": None}
 

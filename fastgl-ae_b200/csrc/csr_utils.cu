@@ -113,6 +113,51 @@ __global__ void __launch_bounds__(kStageThreads) stage_segments_kernel(const __g
     }
 }
 
+// Measurement probe: the rate at which this GPU serves the sampler's access pattern when nothing else is done --
+// isolated 4-byte reads at hashed positions of an array (a pick in a hub's neighbour list), each followed, if a
+// table is given, by a dependent 8-byte load of a hashed slot and a compare-and-swap when the slot looks empty (the
+// first probe of the id map's insert).  Four independent chains per thread are in flight.  The sampler's roofline
+// by bytes assumes 32 useful bytes per pick at streaming bandwidth; this is what the memory system really sustains.
+__device__ __forceinline__ uint32_t probe_mix(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7feb352du;
+    x ^= x >> 15;
+    x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+
+__global__ void __launch_bounds__(512, 2) access_probe_kernel(const int32_t* __restrict__ a, uint32_t n_words,
+                                                              unsigned long long* __restrict__ table, uint32_t table_mask,
+                                                              int iters, int32_t* __restrict__ sink) {
+    constexpr int K = 4;
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long acc = 0;
+    for (int it = 0; it < iters; ++it) {
+        int v[K];
+#pragma unroll
+        for (int q = 0; q < K; ++q) {
+            const uint32_t r = probe_mix(tid * 977u + (uint32_t)(it * K + q) * 0x9E3779B1u);
+            v[q] = __ldg(a + (uint32_t)(((uint64_t)r * n_words) >> 32));
+        }
+        if (table) {
+            unsigned long long s[K];
+#pragma unroll
+            for (int q = 0; q < K; ++q) s[q] = *(volatile unsigned long long*)(table + (probe_mix((uint32_t)v[q]) & table_mask));
+#pragma unroll
+            for (int q = 0; q < K; ++q) {
+                if (s[q] == 0ULL)
+                    s[q] = atomicCAS(table + (probe_mix((uint32_t)v[q]) & table_mask), 0ULL, ((unsigned long long)(uint32_t)v[q] << 32) | 1u);
+                acc += s[q];
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < K; ++q) acc += (unsigned)v[q];
+        }
+    }
+    if (acc == 0x7fffffffffffULL) sink[0] = (int32_t)acc;   // keeps the loads alive
+}
+
 // Pairwise overlap of the node lists of a window: overlap[i][j] = |nodes_i & nodes_j| (Match-Reorder's match degree,
 // utilis.py:41-48, without one N-sized boolean mask per mini-batch).  One word per node holds a bit per mini-batch:
 // pass 0 sets the bits, pass 1 reads every node's word back and counts, per mini-batch, the other mini-batches that
@@ -217,6 +262,19 @@ int fgl_window_overlap(const int32_t* nodes, int64_t nodes_stride, const int32_t
     const dim3 grid((unsigned)std::max<int64_t>(1, std::min<int64_t>(148 * 4 / n_batches + 1, (nodes_stride + 255) / 256)), n_batches);
     for (int pass = 0; pass < 3; ++pass)
         window_overlap_kernel<<<grid, 256, 0, st>>>(nodes, nodes_stride, counts, counts_stride, n_nodes, mask, overlap, n_batches, pass);
+    return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+}
+
+int fgl_probe_access_pattern(const int32_t* array, int64_t n_words, uint64_t* table, int64_t table_slots, int32_t iters,
+                             int32_t* sink, int64_t* n_accesses, void* stream) {
+    if (!array || n_words < 1 || n_words > 0xffffffffLL || iters < 1 || !sink || !n_accesses) return FGL_ERR_INVALID;
+    if (table && (table_slots < 1 || table_slots > 0x80000000LL || (table_slots & (table_slots - 1)))) return FGL_ERR_INVALID;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = sms * 2;
+    access_probe_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(array, (uint32_t)n_words, (unsigned long long*)table,
+                                                               table ? (uint32_t)(table_slots - 1) : 0u, iters, sink);
+    *n_accesses = (int64_t)grid * 512 * 4 * iters;
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
 

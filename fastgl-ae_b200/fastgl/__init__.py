@@ -33,7 +33,7 @@ __all__ = [
     "sample_node", "transfer_edge_id", "cal_deg", "exclusive_sum", "forward_gcn", "backward_gcn",
     "forwaed_gin", "backward_gin", "forward_gat", "backward_gat", "edge_weight_grad", "sample_node_csr", "aggregate", "aggregate_backward", "aggregate_window",
     "sample_map_fused", "fused_capacity", "stage_segments", "stage_segments_raw", "gather_rows", "ShardedTable", "set_sampling", "seed", "FusedBatch",
-    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block", "split_tf32", "split_tf32_raw", "fold_blocks",
+    "exclusive_sum_noalloc", "exclusive_sum_noalloc_status", "check_status", "status_str", "PeerSync", "allreduce_adam_", "window_overlap", "TransposedBlock", "transpose_block", "split_tf32", "split_tf32_raw", "fold_blocks", "probe_access_pattern",
     "AGG_SUM", "AGG_MEAN", "AGG_SYMNORM",
 ]
 
@@ -718,6 +718,26 @@ def fold_blocks(part, n_a, n_b, rows, cols, block_stride, out):
                                    ctypes.c_int64(out.stride(0)), _stream(dev))
     _raise(rc, "fold_blocks")
     return out
+
+
+def probe_access_pattern(array, table=None, iters=64) -> int:
+    """Enqueue the access-pattern probe (``fgl_probe_access_pattern``) on the current stream: isolated 4-byte reads of
+    ``array`` (int32 CUDA tensor), each followed by a probe of ``table`` (int64 CUDA tensor, a power of two of zeroed
+    slots) when one is given.  Returns the number of accesses the launch performs; time the stream around it."""
+    _check_i32(array, "array")
+    if table is not None:
+        _check_input(table, "table")
+        if table.dtype != torch.int64:
+            raise RuntimeError("table must be int64")
+    dev = array.device
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    n = ctypes.c_int64(0)
+    with _on_device(dev):
+        rc = lib().fgl_probe_access_pattern(_ptr(array), ctypes.c_int64(array.numel()), _ptr(table),
+                                            ctypes.c_int64(0 if table is None else table.numel()), ctypes.c_int32(iters),
+                                            _ptr(sink), ctypes.byref(n), _stream(dev))
+    _raise(rc, "probe_access_pattern")
+    return int(n.value)
 
 
 def split_tf32_raw(src_ptr: int, rows: int, cols: int, ldx: int, dst, device) -> None:

@@ -87,6 +87,17 @@ int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream);
  * workspace works as before. */
 int fgl_selftest_barrier_timeout(fgl_ws* ws, int32_t n_ctas, int64_t spin_limit, void* stream);
 
+/* Measurement probe (no counterpart in the reference): launches a kernel that performs the sampler's memory access
+ * pattern and nothing else -- per access one 4-byte read at a hashed position of array[n_words] (the cost of
+ * picking a neighbour in a long adjacency list) and, if table is given (table_slots 64-bit words, a power of two,
+ * zero-filled by the caller), a dependent load of a hashed slot plus a compare-and-swap when it looks empty (the
+ * first probe of the id map's insert).  Every thread of 2 CTAs x 512 threads per SM keeps four chains in flight
+ * for iters rounds; *n_accesses receives the number of accesses the launch performs, so that the caller, timing
+ * the stream, gets accesses per second: the roofline of the fused sampler by access count rather than by bytes.
+ * sink: one int32 of device memory the kernel may write. */
+int fgl_probe_access_pattern(const int32_t* array, int64_t n_words, uint64_t* table, int64_t table_slots, int32_t iters,
+                             int32_t* sink, int64_t* n_accesses, void* stream);
+
 /* Neighbour sampling; replaces sample_node_cuda (sample.cu:102-203; binding aggregate_acc.cpp:491-512).
  * indptr has n_nodes + 1 entries of int32 (indptr_is_64 = 0, as the reference) or int64.  For seed i
  * the k_i = min(deg, fanout) sampled sources land at out_src[out_indptr[i] .. out_indptr[i+1]); a seed
