@@ -397,19 +397,46 @@ split_tf32_kernel(const float* __restrict__ x, int64_t rows, int cols, int64_t l
 }
 
 // out[r, c] = sum over slabs s and blocks (a, b) of part[s][a * rows + r][b * block_stride + c]: folds the 2 x 2 block
-// product [X_hi | X_lo]^T [dZ_hi | dZ_lo] (and its split-K slabs) into the weight gradient.  A thread per output.
-__global__ void __launch_bounds__(kEwThreads)
+// product [X_hi | X_lo]^T [dZ_hi | dZ_lo] (and its split-K slabs) into the weight gradient.  A warp per group of 32
+// consecutive outputs of one row; the slabs are spread over the warps of a CTA (every lane keeps the n_a * n_b loads of
+// its slab in flight together) and meet in shared memory, where they are added in slab order.
+constexpr int kFoldWarps = 8;
+
+__global__ void __launch_bounds__(kFoldWarps * 32)
 fold_blocks_kernel(const float* __restrict__ part, int n_slabs, int n_a, int n_b, int rows, int cols, int block_stride,
                    int64_t ld_part, int64_t slab_stride, float* __restrict__ out, int64_t ldo) {
-    const int64_t total = (int64_t)rows * cols;
-    for (int64_t g = (int64_t)blockIdx.x * kEwThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kEwThreads) {
-        const int r = (int)(g / cols), c = (int)(g - (int64_t)r * cols);
+    __shared__ float partial[kFoldWarps][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int groups_per_row = (cols + 31) / 32;
+    const int64_t n_groups = (int64_t)rows * groups_per_row;
+    for (int64_t g = blockIdx.x; g < n_groups; g += gridDim.x) {
+        const int r = (int)(g / groups_per_row), c = (int)(g - (int64_t)r * groups_per_row) * 32 + lane;
         float acc = 0.f;
-        for (int s = 0; s < n_slabs; ++s)
-            for (int a = 0; a < n_a; ++a)
-                for (int b = 0; b < n_b; ++b)
-                    acc += part[s * slab_stride + ((int64_t)a * rows + r) * ld_part + (int64_t)b * block_stride + c];
-        out[(int64_t)r * ldo + c] = acc;
+        if (c < cols) {
+            for (int s = warp; s < n_slabs; s += kFoldWarps) {
+                const float* base = part + s * slab_stride + (int64_t)r * ld_part + c;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (n_a == 2 && n_b == 2) {   // the 2 x 2 block product: four independent loads
+                    v[0] = base[0];
+                    v[1] = base[block_stride];
+                    v[2] = base[(int64_t)rows * ld_part];
+                    v[3] = base[(int64_t)rows * ld_part + block_stride];
+                } else {
+                    for (int a = 0; a < n_a; ++a)
+                        for (int b = 0; b < n_b; ++b) v[0] += base[(int64_t)a * rows * ld_part + (int64_t)b * block_stride];
+                }
+                acc += (v[0] + v[1]) + (v[2] + v[3]);
+            }
+        }
+        partial[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && c < cols) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < kFoldWarps; ++w) t += partial[w][lane];
+            out[(int64_t)r * ldo + c] = t;
+        }
+        __syncthreads();
     }
 }
 
@@ -568,7 +595,8 @@ int fgl_fold_blocks(const float* part, int32_t n_slabs, int32_t n_a, int32_t n_b
         return FGL_ERR_INVALID;
     if (rows == 0 || cols == 0) return FGL_OK;
     if (!part || !out) return FGL_ERR_INVALID;
-    fold_blocks_kernel<<<ew_grid((int64_t)rows * cols), kEwThreads, 0, (cudaStream_t)stream>>>(
+    const int64_t groups = (int64_t)rows * ((cols + 31) / 32);
+    fold_blocks_kernel<<<(unsigned)std::min<int64_t>(groups, 148 * 16), kFoldWarps * 32, 0, (cudaStream_t)stream>>>(
         part, n_slabs, n_a, n_b, rows, cols, block_stride, ld_part, slab_stride, out, ldo);
     return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
 }
