@@ -120,6 +120,85 @@ relu_dropout_bwd_kernel(float* __restrict__ dy, int64_t ldy, const float* __rest
     }
 }
 
+// The same backward for matrices whose rows are whole 16-byte vectors (dim % 4 == 0, dim <= 1024): a thread owns four
+// consecutive columns, the CTA's 256 threads cover 256 / (dim / 4) rows per pass and four passes are in flight, so
+// every access is 16 bytes wide.  The column sums of the threads that share a column group meet in shared memory.
+template <bool SPLIT>
+__global__ void __launch_bounds__(kEwThreads)
+relu_dropout_bwd_vec_kernel(float* __restrict__ dy, int64_t ldy, const float* __restrict__ out, int64_t ldo, int64_t n_rows,
+                            int rows_per_cta, int dim, float keep_scale, float* __restrict__ dbias, int flags,
+                            float* __restrict__ split3, int64_t ld3, int block_stride) {
+    __shared__ float4 sums[kEwThreads];
+    const int groups = dim >> 2;                       // column groups of four floats; <= 256
+    const int lanes = kEwThreads / groups;             // rows covered per pass
+    const int cg = threadIdx.x % groups, rl = threadIdx.x / groups;
+    const bool active = rl < lanes;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_cta;
+    const int64_t r1 = r0 + rows_per_cta < n_rows ? r0 + rows_per_cta : n_rows;
+    const bool mask = flags & FGL_EW_RELU;
+    constexpr int kPasses = 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active) {
+        for (int64_t r = r0 + rl; r < r1; r += (int64_t)lanes * kPasses) {
+            float4 g[kPasses], o[kPasses];
+#pragma unroll
+            for (int k = 0; k < kPasses; ++k) {
+                const int64_t rr = r + (int64_t)k * lanes;
+                const bool in = rr < r1;
+                g[k] = in ? *reinterpret_cast<const float4*>(dy + rr * ldy + 4 * cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+                o[k] = (in && mask) ? *reinterpret_cast<const float4*>(out + rr * ldo + 4 * cg) : make_float4(1.f, 1.f, 1.f, 1.f);
+            }
+#pragma unroll
+            for (int k = 0; k < kPasses; ++k) {
+                const int64_t rr = r + (int64_t)k * lanes;
+                if (mask) {
+                    g[k].x = o[k].x > 0.f ? g[k].x * keep_scale : 0.f;
+                    g[k].y = o[k].y > 0.f ? g[k].y * keep_scale : 0.f;
+                    g[k].z = o[k].z > 0.f ? g[k].z * keep_scale : 0.f;
+                    g[k].w = o[k].w > 0.f ? g[k].w * keep_scale : 0.f;
+                }
+                if (rr < r1) {
+                    if (SPLIT) {
+                        float4 h, l;
+                        h.x = to_tf32(g[k].x); l.x = to_tf32(g[k].x - h.x);
+                        h.y = to_tf32(g[k].y); l.y = to_tf32(g[k].y - h.y);
+                        h.z = to_tf32(g[k].z); l.z = to_tf32(g[k].z - h.z);
+                        h.w = to_tf32(g[k].w); l.w = to_tf32(g[k].w - h.w);
+                        float* d3 = split3 + rr * ld3 + 4 * cg;
+                        *reinterpret_cast<float4*>(d3) = h;
+                        *reinterpret_cast<float4*>(d3 + block_stride) = l;
+                        *reinterpret_cast<float4*>(d3 + 2 * block_stride) = h;
+                    } else if (mask) {
+                        *reinterpret_cast<float4*>(dy + rr * ldy + 4 * cg) = g[k];
+                    }
+                }
+                acc.x += g[k].x;
+                acc.y += g[k].y;
+                acc.z += g[k].z;
+                acc.w += g[k].w;
+            }
+        }
+    }
+    if (!dbias) return;
+    sums[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x < groups) {
+        float4 t = sums[threadIdx.x];
+        for (int q = 1; q < lanes; ++q) {
+            const float4 v = sums[q * groups + threadIdx.x];
+            t.x += v.x;
+            t.y += v.y;
+            t.z += v.z;
+            t.w += v.w;
+        }
+        float* b = dbias + 4 * threadIdx.x;
+        if (t.x != 0.f) atomicAdd(b, t.x);
+        if (t.y != 0.f) atomicAdd(b + 1, t.y);
+        if (t.z != 0.f) atomicAdd(b + 2, t.z);
+        if (t.w != 0.f) atomicAdd(b + 3, t.w);
+    }
+}
+
 // Mean softmax cross-entropy over the first n_valid rows, and its gradient; a warp per row.
 // row_loss[r] = logsumexp(z_r) - z_r[label_r] (0 for rows that do not count);
 // dlogits[r, c] = (softmax(z_r)[c] - [c == label_r]) / n_valid for r < n_valid and 0 below.
@@ -493,6 +572,24 @@ static int relu_dropout_bwd_launch(float* dy, int64_t ldy, const float* out, int
     const int64_t blocks = (n_rows + rows_per_cta - 1) / rows_per_cta;
     if (blocks > 0x7fffffffLL) return FGL_ERR_INVALID;
     const float keep = p_drop > 0.f ? 1.f / (1.f - p_drop) : 1.f;
+    const bool mask = (flags & FGL_EW_RELU) != 0;
+    const bool vec = dim % 4 == 0 && dim <= 4 * kEwThreads && ldy % 4 == 0 && aligned16(dy) && (!mask || (ldo % 4 == 0 && aligned16(out))) &&
+                     (!dbias || aligned16(dbias)) && (!split3 || (ld3 % 4 == 0 && block_stride % 4 == 0 && aligned16(split3)));
+    if (vec) {
+        // whole 16-byte vectors: 16 rows x (256 threads / column groups) per CTA pass
+        const int lanes = kEwThreads / (dim / 4);
+        int64_t band = (int64_t)lanes * 4 * (split3 ? 1 : 2);
+        while (band < 16) band *= 2;
+        const int64_t nb = (n_rows + band - 1) / band;
+        if (nb > 0x7fffffffLL) return FGL_ERR_INVALID;
+        if (split3)
+            relu_dropout_bwd_vec_kernel<true><<<(unsigned)nb, kEwThreads, 0, (cudaStream_t)stream>>>(
+                dy, ldy, out, ldo, n_rows, (int)band, dim, keep, dbias, flags, split3, ld3, (int)block_stride);
+        else
+            relu_dropout_bwd_vec_kernel<false><<<(unsigned)nb, kEwThreads, 0, (cudaStream_t)stream>>>(
+                dy, ldy, out, ldo, n_rows, (int)band, dim, keep, dbias, flags, nullptr, 0, 0);
+        return cudaGetLastError() == cudaSuccess ? FGL_OK : FGL_ERR_CUDA;
+    }
     if (split3)
         relu_dropout_bwd_kernel<true><<<(unsigned)blocks, kEwThreads, 0, (cudaStream_t)stream>>>(
             dy, ldy, out, ldo, n_rows, (int)rows_per_cta, dim, keep, dbias, flags, split3, ld3, (int)block_stride);
