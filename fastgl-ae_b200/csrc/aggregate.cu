@@ -17,6 +17,8 @@
 // two atomicExch in a retry loop).
 #include <algorithm>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace fgl {
@@ -1233,7 +1235,39 @@ __device__ __forceinline__ int warp_sort_ascending(int v, int lane) {
     return v;
 }
 
-// A warp per source row with at most 32 entries: sort the destination rows, add them in that order.
+// acc += sum over j < deg of w_j * dy[d_j, columns c0 ..], lane j holding (d_j, w_j); U rows' loads in flight.
+template <int VEC, int NACC, int U>
+__device__ __forceinline__ void gather_add_rows(const GatherParams& p, int d, float w, int deg, int c0, int chunks, int lane,
+                                                typename Vec<VEC>::T (&acc)[NACC]) {
+    using V = Vec<VEC>;
+    using T = typename V::T;
+    for (int j0 = 0; j0 < deg; j0 += U) {
+        T v[U][NACC];
+        float wj[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = min(j0 + u, deg - 1);
+            const int dj = __shfl_sync(0xffffffffu, d, j);
+            wj[u] = __shfl_sync(0xffffffffu, w, j);
+            const T* row = reinterpret_cast<const T*>(p.dy + (int64_t)dj * p.ldy);
+#pragma unroll
+            for (int k = 0; k < NACC; ++k) {
+                const int c = c0 + k * 32 + lane;
+                v[u][k] = c < chunks ? __ldg(row + c) : V::zero();
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (j0 + u < deg) {
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) V::fma(acc[k], wj[u], v[u][k]);
+            }
+    }
+}
+
+// A warp per source row with at most 32 entries: sort the destination rows, add them in that order.  Most sources of a
+// sampled block have one or two entries: those skip the sorting network (one entry) and request only as many rows as
+// they have (the unrolled batch of eight would otherwise load a single row eight times).
 template <int VEC, int MODE, int NACC>
 __global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams p) {
     using V = Vec<VEC>;
@@ -1245,9 +1279,9 @@ __global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams 
     const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
     for (int s = warp_global; s < p.n_src; s += n_warps) {
         const int a = __ldg(p.t_indptr + s), deg = __ldg(p.t_indptr + s + 1) - a;
-        if (deg > kHubThreshold) continue;  // a CTA of agg_bwd_hub_kernel owns this row
+        if (deg > kHubThreshold) continue;  // a hub kernel owns this row
         int d = lane < deg ? __ldg(p.t_dst + a + lane) : 0x7fffffff;
-        d = warp_sort_ascending(d, lane);
+        if (deg > 1) d = warp_sort_ascending(d, lane);
         const float w = lane < deg ? gather_weight<MODE>(p, d) : 0.0f;
         const float ws = (MODE == FGL_AGG_SYMNORM && deg > 0) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
         const bool self = p.dy_self != nullptr && s < n_dst;
@@ -1257,28 +1291,14 @@ __global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams 
             T acc[NACC];
 #pragma unroll
             for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
-            for (int j0 = 0; j0 < deg; j0 += UNR) {
-                T v[UNR][NACC];
-                float wj[UNR];
-#pragma unroll
-                for (int u = 0; u < UNR; ++u) {
-                    const int j = min(j0 + u, deg - 1);
-                    const int dj = __shfl_sync(0xffffffffu, d, j);
-                    wj[u] = __shfl_sync(0xffffffffu, w, j);
-                    const T* row = reinterpret_cast<const T*>(p.dy + (int64_t)dj * p.ldy);
-#pragma unroll
-                    for (int k = 0; k < NACC; ++k) {
-                        const int c = c0 + k * 32 + lane;
-                        v[u][k] = c < chunks ? __ldg(row + c) : V::zero();
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < UNR; ++u)
-                    if (j0 + u < deg) {
-#pragma unroll
-                        for (int k = 0; k < NACC; ++k) V::fma(acc[k], wj[u], v[u][k]);
-                    }
-            }
+            if (deg <= 1)
+                gather_add_rows<VEC, NACC, 1>(p, d, w, deg, c0, chunks, lane, acc);
+            else if (deg <= 2 || UNR <= 2)
+                gather_add_rows<VEC, NACC, 2>(p, d, w, deg, c0, chunks, lane, acc);
+            else if (deg <= 4 || UNR <= 4)
+                gather_add_rows<VEC, NACC, 4>(p, d, w, deg, c0, chunks, lane, acc);
+            else
+                gather_add_rows<VEC, NACC, 8>(p, d, w, deg, c0, chunks, lane, acc);
 #pragma unroll
             for (int k = 0; k < NACC; ++k) {
                 const int c = c0 + k * 32 + lane;
@@ -1292,9 +1312,173 @@ __global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams 
     }
 }
 
-// A CTA per hub.  The hub's destination rows are counted into a shared-memory array over a window of the destination
-// range (16-bit counts, two per word), which orders them without sorting; warp k then adds the rows of the k-th eighth
-// of the window in ascending order, and the eight partial sums are folded in a fixed order.
+// Hubs of at most kHubSortMax entries.  The hub's destination rows are sorted in shared memory (bitonic network over the
+// list padded to a power of two), warp k then adds the rows of the k-th eighth of the sorted list in order and the eight
+// partial sums are folded in a fixed order: the result does not depend on the order in which the transposition's
+// atomics filled the list.  16 KB of list per CTA, so several hubs are in flight per SM.
+//   CLUSTER = false: a CTA per hub of up to kHubSplitMin entries.
+//   CLUSTER = true:  a thread-block cluster of eight CTAs per hub of kHubSplitMin + 1 .. kHubSortMax entries.  CTA r
+//                    keeps the entries whose destination lies in the r-th eighth of the destination range (a fixed
+//                    partition, whatever the order of the list), sorts and adds them as above, and rank 0 folds the
+//                    eight CTA sums in rank order, reading them through distributed shared memory.  A hub of 4000
+//                    entries is then 8 x 8 warps deep instead of 8.
+constexpr int kHubSortMax = 4096;
+constexpr int kHubSplitMin = 512;
+constexpr int kHubCluster = 8;
+
+template <int VEC, int MODE, int NACC, bool CLUSTER>
+__global__ void __launch_bounds__(256) agg_bwd_hub_sorted_kernel(const GatherParams p) {
+    namespace cg = cooperative_groups;
+    using V = Vec<VEC>;
+    using T = typename V::T;
+    extern __shared__ __align__(16) unsigned char hub_smem[];
+    __shared__ int s_count;
+    int* list = reinterpret_cast<int*>(hub_smem);                          // kHubSortMax entries
+    T* part = reinterpret_cast<T*>(hub_smem + kHubSortMax * sizeof(int));  // [8][NACC][32]
+    T* cta_sum = part + 8 * NACC * 32;                                     // [NACC][32], CLUSTER only
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunks = p.dim / VEC;
+    const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
+    const int n_hubs = min(__ldg(p.hubs), p.n_src);
+    const int rank = CLUSTER ? (int)cg::this_cluster().block_rank() : 0;
+    const int unit = CLUSTER ? blockIdx.x / kHubCluster : blockIdx.x;
+    const int n_units = CLUSTER ? gridDim.x / kHubCluster : gridDim.x;
+    const int seg = (n_dst + kHubCluster - 1) / kHubCluster;  // destination rows per cluster rank
+    constexpr int UNR = NACC == 1 ? 8 : (NACC == 2 ? 4 : 2);
+    // This unit (CTA or cluster) looks after the hubs h = unit (mod n_units).  Which of them are of its size class is
+    // found 256 at a time, a thread per hub, and compacted in index order -- every CTA of a cluster arrives at the same
+    // list -- instead of one dependent pair of loads per hub in turn; longer lists are counted by agg_bwd_hub_kernel.
+    __shared__ int s_sel[256];
+    __shared__ int s_wcnt[8];
+    for (int base = 0; base < n_hubs; base += 256 * n_units) {
+        const int h_t = base + (int)threadIdx.x * n_units + unit;
+        bool ok = false;
+        if (h_t < n_hubs) {
+            const int s_t = __ldg(p.hubs + 1 + h_t);
+            const int deg_t = __ldg(p.t_indptr + s_t + 1) - __ldg(p.t_indptr + s_t);
+            ok = CLUSTER ? (deg_t > kHubSplitMin && deg_t <= kHubSortMax) : (deg_t <= kHubSplitMin);
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) s_wcnt[warp] = __popc(bal);
+        __syncthreads();
+        int sel_before = 0, n_sel = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (q < warp) sel_before += s_wcnt[q];
+            n_sel += s_wcnt[q];
+        }
+        if (ok) s_sel[sel_before + __popc(bal & ((1u << lane) - 1u))] = h_t;
+        __syncthreads();
+        for (int q_sel = 0; q_sel < n_sel; ++q_sel) {
+            const int s = __ldg(p.hubs + 1 + s_sel[q_sel]);
+            const int a = __ldg(p.t_indptr + s), deg = __ldg(p.t_indptr + s + 1) - a;
+            int m = deg;
+            if (CLUSTER) {
+                if (threadIdx.x == 0) s_count = 0;
+                __syncthreads();
+                for (int i = threadIdx.x; i < deg; i += 256) {
+                    const int d = __ldg(p.t_dst + a + i);
+                    if (d >= rank * seg && d < (rank + 1) * seg) list[atomicAdd(&s_count, 1)] = d;
+                }
+                __syncthreads();
+                m = s_count;
+            } else {
+                for (int i = threadIdx.x; i < deg; i += 256) list[i] = __ldg(p.t_dst + a + i);
+            }
+            int n2 = 64;
+            while (n2 < m) n2 <<= 1;
+            for (int i = m + (int)threadIdx.x; i < n2; i += 256) list[i] = 0x7fffffff;
+            __syncthreads();
+            for (int k = 2; k <= n2; k <<= 1) {
+                for (int j = k >> 1; j > 0; j >>= 1) {
+                    for (int i = threadIdx.x; i < n2; i += 256) {
+                        const int l = i ^ j;
+                        if (l > i) {
+                            const int x = list[i], y = list[l];
+                            if ((x > y) == ((i & k) == 0)) {
+                                list[i] = y;
+                                list[l] = x;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                }
+            }
+            const float ws = (MODE == FGL_AGG_SYMNORM) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
+            const bool self = p.dy_self != nullptr && s < n_dst;
+            const int per = (m + 7) / 8;
+            const int lo = warp * per, hi = min(lo + per, m);
+            for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
+                T acc[NACC];
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) acc[k] = V::zero();
+                for (int j0 = lo; j0 < hi; j0 += UNR) {
+                    T v[UNR][NACC];
+                    float wj[UNR];
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+                        const int dj = list[min(j0 + u, hi - 1)];
+                        wj[u] = gather_weight<MODE>(p, dj);
+                        const T* row = reinterpret_cast<const T*>(p.dy + (int64_t)dj * p.ldy);
+#pragma unroll
+                        for (int k = 0; k < NACC; ++k) {
+                            const int c = c0 + k * 32 + lane;
+                            v[u][k] = c < chunks ? __ldg(row + c) : V::zero();
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u)
+                        if (j0 + u < hi) {
+#pragma unroll
+                            for (int k = 0; k < NACC; ++k) V::fma(acc[k], wj[u], v[u][k]);
+                        }
+                }
+#pragma unroll
+                for (int k = 0; k < NACC; ++k) part[(warp * NACC + k) * 32 + lane] = acc[k];
+                __syncthreads();
+                T total[NACC];
+                if (warp == 0) {  // the CTA's sum: the eight warps' partial sums in warp order
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k) {
+                        total[k] = V::zero();
+                        for (int q = 0; q < 8; ++q) V::fma(total[k], 1.0f, part[(q * NACC + k) * 32 + lane]);
+                        if (CLUSTER) cta_sum[k * 32 + lane] = total[k];
+                    }
+                }
+                if (CLUSTER) {
+                    cg::this_cluster().sync();  // every CTA's sum is in its shared memory
+                    if (rank == 0 && warp == 0) {
+#pragma unroll
+                        for (int k = 0; k < NACC; ++k) {
+                            for (int q = 1; q < kHubCluster; ++q)
+                                V::fma(total[k], 1.0f, cg::this_cluster().map_shared_rank(cta_sum, q)[k * 32 + lane]);
+                        }
+                    }
+                }
+                if (rank == 0 && warp == 0) {
+                    T* out = reinterpret_cast<T*>(p.dx + (int64_t)s * p.ldx);
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k) {
+                        const int c = c0 + k * 32 + lane;
+                        if (c < chunks) {
+                            T r = (MODE == FGL_AGG_SYMNORM) ? V::scale(total[k], ws) : total[k];
+                            if (self) V::fma(r, 1.0f, __ldg(reinterpret_cast<const T*>(p.dy_self + (int64_t)s * p.ld_self) + c));
+                            out[c] = r;
+                        }
+                    }
+                }
+                if (CLUSTER) cg::this_cluster().sync();  // rank 0 has read the sums: they may be overwritten
+                __syncthreads();
+            }
+        }
+        __syncthreads();  // the selection is consumed: the next 256 candidates may overwrite it
+    }
+}
+
+// A CTA per hub with more than kHubSortMax entries.  The hub's destination rows are counted into a shared-memory array
+// over a window of the destination range (16-bit counts, two per word), which orders them without sorting; warp k then
+// adds the rows of the k-th eighth of the window in ascending order, and the eight partial sums are folded in a fixed
+// order.  The 64 KB counting pass costs microseconds per hub whatever its size, hence only for the very long lists.
 constexpr int kHubWindow = 32768;
 
 template <int VEC, int MODE, int NACC>
@@ -1312,6 +1496,7 @@ __global__ void __launch_bounds__(256) agg_bwd_hub_kernel(const GatherParams p) 
     for (int h = blockIdx.x; h < n_hubs; h += gridDim.x) {
         const int s = __ldg(p.hubs + 1 + h);
         const int a = __ldg(p.t_indptr + s), b = __ldg(p.t_indptr + s + 1);
+        if (b - a <= kHubSortMax) continue;  // agg_bwd_hub_sorted_kernel owns this row
         const float ws = (MODE == FGL_AGG_SYMNORM) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
         const bool self = p.dy_self != nullptr && s < n_dst;
         for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
@@ -1394,6 +1579,24 @@ __global__ void __launch_bounds__(256) agg_bwd_hub_kernel(const GatherParams p) 
     }
 }
 
+// Clusters of kHubCluster CTAs, one cluster per hub at a time; about two clusters' worth of CTAs per SM-octet.
+static void launch_hub_clusters(void (*kernel)(const GatherParams), const GatherParams& p, int sms, size_t dyn, cudaStream_t st) {
+    cudaLaunchConfig_t cfg{};
+    const int n_clusters = std::max(1, 2 * sms / kHubCluster);
+    cfg.gridDim = dim3((unsigned)(n_clusters * kHubCluster));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = dyn;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kHubCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <int VEC, int MODE>
 static void launch_gather_nacc(const GatherParams& p, int sms, cudaStream_t st) {
     const int chunks = p.dim / VEC;
@@ -1402,7 +1605,10 @@ static void launch_gather_nacc(const GatherParams& p, int sms, cudaStream_t st) 
 #define FGL_GATHER(NACC)                                                                                           \
     {                                                                                                              \
         const size_t dyn = (size_t)kHubWindow * 2 + sizeof(typename Vec<VEC>::T) * 8 * NACC * 32;                  \
+        const size_t dyn_sorted = (size_t)kHubSortMax * sizeof(int) + sizeof(typename Vec<VEC>::T) * 9 * NACC * 32; \
         agg_bwd_gather_kernel<VEC, MODE, NACC><<<grid, 256, 0, st>>>(p);                                           \
+        agg_bwd_hub_sorted_kernel<VEC, MODE, NACC, false><<<6 * sms, 256, dyn_sorted, st>>>(p);                    \
+        launch_hub_clusters(agg_bwd_hub_sorted_kernel<VEC, MODE, NACC, true>, p, sms, dyn_sorted, st);             \
         cudaFuncSetAttribute(agg_bwd_hub_kernel<VEC, MODE, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
         agg_bwd_hub_kernel<VEC, MODE, NACC><<<hub_grid, 256, dyn, st>>>(p);                                        \
     }
