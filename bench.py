@@ -615,7 +615,9 @@ def main():
         n_layers = len(cfg["fanouts"])
         per_step = (5 * n_layers - 1) if tr.graphed is not None else 2 * (n_layers - 1)
         if tr.graphed is not None and args.matmul == "3xtf32":
-            per_step += 3 * n_layers      # operand splits: the weights, the layer inputs, the output gradients
+            # operand splits (n_layers weights, n_layers layer inputs -- the first one while staging --, the output
+            # layer's gradient) and n_layers folds of the weight-gradient blocks
+            per_step += 3 * n_layers + 1
         launches = args.steps * per_step + 2 * n_windows
         epoch_s = steps_per_epoch * ms / args.steps * 1e-3
         line = {"metric": "sampled_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
