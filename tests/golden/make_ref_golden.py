@@ -4,10 +4,10 @@
 
 Runs on a machine with a GPU:
 
-    python tests/golden/make_ref_golden.py --out gpurun_out/ref_hotpath.npz [--timing gpurun_out/ref_timing.json]
+    python tests/golden/make_ref_golden.py --out tests/golden/ref_hotpath.npz [--timing ref_timing.json]
 
-The resulting ``ref_hotpath.npz`` is committed under ``tests/golden/``; ``tests/test_oracle.py`` checks the CPU oracle
-against it and ``tests/test_gpu_parity.py`` checks the CUDA kernels against it.
+The resulting ``ref_hotpath.npz`` is committed under ``tests/golden/``; ``tests/test_ref_golden.py`` checks the CPU
+oracle and the CUDA kernels against it.
 
 Every input stays inside what the reference's kernels can take without reading or writing out of bounds (checked by
 reading them): ids are non-negative and in range, seeds are distinct, the in-degree of a block never exceeds the
