@@ -1177,6 +1177,7 @@ struct GatherParams {
     int64_t ldy, ld_self, ldx;
     int32_t dim, n_dst, n_src;
     const int32_t* n_dst_dev;
+    int32_t hub_ctas;  // agg_bwd_gather_kernel: the first hub_ctas CTAs take the hubs of 33 .. kHubSplitMin entries
 };
 
 constexpr int kHubThreshold = 32;
@@ -1222,19 +1223,6 @@ __global__ void __launch_bounds__(256) list_hubs_kernel(const int32_t* __restric
         if (__ldg(t_indptr + s + 1) - __ldg(t_indptr + s) > kHubThreshold) hubs[1 + atomicAdd(hubs, 1)] = s;
 }
 
-__device__ __forceinline__ int warp_sort_ascending(int v, int lane) {
-#pragma unroll
-    for (int k = 2; k <= 32; k <<= 1) {
-#pragma unroll
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            const int other = __shfl_xor_sync(0xffffffffu, v, j);
-            const bool up = (lane & k) == 0, lower = (lane & j) == 0;
-            v = (lower == up) ? min(v, other) : max(v, other);
-        }
-    }
-    return v;
-}
-
 // acc += sum over j < deg of w_j * dy[d_j, columns c0 ..], lane j holding (d_j, w_j); U rows' loads in flight.
 template <int VEC, int NACC, int U>
 __device__ __forceinline__ void gather_add_rows(const GatherParams& p, int d, float w, int deg, int c0, int chunks, int lane,
@@ -1265,21 +1253,37 @@ __device__ __forceinline__ void gather_add_rows(const GatherParams& p, int d, fl
     }
 }
 
+__device__ __forceinline__ int warp_sort_ascending(int v, int lane) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const int other = __shfl_xor_sync(0xffffffffu, v, j);
+            const bool up = (lane & k) == 0, lower = (lane & j) == 0;
+            v = (lower == up) ? min(v, other) : max(v, other);
+        }
+    }
+    return v;
+}
+
 // A warp per source row with at most 32 entries: sort the destination rows, add them in that order.  Most sources of a
 // sampled block have one or two entries: those skip the sorting network (one entry) and request only as many rows as
-// they have (the unrolled batch of eight would otherwise load a single row eight times).
+// they have (the unrolled batch of eight would otherwise load a single row eight times).  Software-pipelining the id
+// chain over the warp's sources, as the forward kernel does, was measured and bought nothing here: with 64 warps per
+// SM the chain is hidden already, and the launch is bound by the rows it reads and the full output row it writes per
+// source.
 template <int VEC, int MODE, int NACC>
-__global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams p) {
+__device__ __forceinline__ void gather_small_sources(const GatherParams& p, int block, int n_blocks) {
     using V = Vec<VEC>;
     using T = typename V::T;
     constexpr int UNR = NACC == 1 ? 8 : (NACC == 2 ? 4 : 2);
     const int lane = threadIdx.x & 31;
-    const int warp_global = blockIdx.x * 8 + (threadIdx.x >> 5), n_warps = gridDim.x * 8;
+    const int warp_global = block * 8 + (threadIdx.x >> 5), n_warps = n_blocks * 8;
     const int chunks = p.dim / VEC;
     const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
     for (int s = warp_global; s < p.n_src; s += n_warps) {
         const int a = __ldg(p.t_indptr + s), deg = __ldg(p.t_indptr + s + 1) - a;
-        if (deg > kHubThreshold) continue;  // a hub kernel owns this row
+        if (deg > kHubThreshold) continue;  // a hub CTA owns this row
         int d = lane < deg ? __ldg(p.t_dst + a + lane) : 0x7fffffff;
         if (deg > 1) d = warp_sort_ascending(d, lane);
         const float w = lane < deg ? gather_weight<MODE>(p, d) : 0.0f;
@@ -1327,7 +1331,7 @@ constexpr int kHubSplitMin = 512;
 constexpr int kHubCluster = 8;
 
 template <int VEC, int MODE, int NACC, bool CLUSTER>
-__global__ void __launch_bounds__(256) agg_bwd_hub_sorted_kernel(const GatherParams p) {
+__device__ __forceinline__ void gather_hubs_sorted(const GatherParams& p, int block, int n_blocks) {
     namespace cg = cooperative_groups;
     using V = Vec<VEC>;
     using T = typename V::T;
@@ -1341,8 +1345,8 @@ __global__ void __launch_bounds__(256) agg_bwd_hub_sorted_kernel(const GatherPar
     const int n_dst = p.n_dst_dev ? min(max(__ldg(p.n_dst_dev), 0), p.n_dst) : p.n_dst;
     const int n_hubs = min(__ldg(p.hubs), p.n_src);
     const int rank = CLUSTER ? (int)cg::this_cluster().block_rank() : 0;
-    const int unit = CLUSTER ? blockIdx.x / kHubCluster : blockIdx.x;
-    const int n_units = CLUSTER ? gridDim.x / kHubCluster : gridDim.x;
+    const int unit = CLUSTER ? block / kHubCluster : block;
+    const int n_units = CLUSTER ? n_blocks / kHubCluster : n_blocks;
     const int seg = (n_dst + kHubCluster - 1) / kHubCluster;  // destination rows per cluster rank
     constexpr int UNR = NACC == 1 ? 8 : (NACC == 2 ? 4 : 2);
     // This unit (CTA or cluster) looks after the hubs h = unit (mod n_units).  Which of them are of its size class is
@@ -1475,6 +1479,22 @@ __global__ void __launch_bounds__(256) agg_bwd_hub_sorted_kernel(const GatherPar
     }
 }
 
+// One launch for the sources of up to kHubSplitMin entries: the first hub_ctas CTAs (they run longest, so they start
+// first) each take hubs of 33 .. kHubSplitMin entries, the others take the small sources a warp at a time.
+template <int VEC, int MODE, int NACC>
+__global__ void __launch_bounds__(256) agg_bwd_gather_kernel(const GatherParams p) {
+    if ((int)blockIdx.x < p.hub_ctas)
+        gather_hubs_sorted<VEC, MODE, NACC, false>(p, (int)blockIdx.x, p.hub_ctas);
+    else
+        gather_small_sources<VEC, MODE, NACC>(p, (int)blockIdx.x - p.hub_ctas, (int)gridDim.x - p.hub_ctas);
+}
+
+// Clusters of kHubCluster CTAs for the hubs of kHubSplitMin + 1 .. kHubSortMax entries.
+template <int VEC, int MODE, int NACC>
+__global__ void __launch_bounds__(256) agg_bwd_hub_cluster_kernel(const GatherParams p) {
+    gather_hubs_sorted<VEC, MODE, NACC, true>(p, (int)blockIdx.x, (int)gridDim.x);
+}
+
 // A CTA per hub with more than kHubSortMax entries.  The hub's destination rows are counted into a shared-memory array
 // over a window of the destination range (16-bit counts, two per word), which orders them without sorting; warp k then
 // adds the rows of the k-th eighth of the window in ascending order, and the eight partial sums are folded in a fixed
@@ -1496,7 +1516,7 @@ __global__ void __launch_bounds__(256) agg_bwd_hub_kernel(const GatherParams p) 
     for (int h = blockIdx.x; h < n_hubs; h += gridDim.x) {
         const int s = __ldg(p.hubs + 1 + h);
         const int a = __ldg(p.t_indptr + s), b = __ldg(p.t_indptr + s + 1);
-        if (b - a <= kHubSortMax) continue;  // agg_bwd_hub_sorted_kernel owns this row
+        if (b - a <= kHubSortMax) continue;  // sorted by a CTA or a cluster instead
         const float ws = (MODE == FGL_AGG_SYMNORM) ? 1.0f / sqrtf((float)__ldg(p.src_deg + s)) : 1.0f;
         const bool self = p.dy_self != nullptr && s < n_dst;
         for (int c0 = 0; c0 < chunks; c0 += 32 * NACC) {
@@ -1606,9 +1626,10 @@ static void launch_gather_nacc(const GatherParams& p, int sms, cudaStream_t st) 
     {                                                                                                              \
         const size_t dyn = (size_t)kHubWindow * 2 + sizeof(typename Vec<VEC>::T) * 8 * NACC * 32;                  \
         const size_t dyn_sorted = (size_t)kHubSortMax * sizeof(int) + sizeof(typename Vec<VEC>::T) * 9 * NACC * 32; \
-        agg_bwd_gather_kernel<VEC, MODE, NACC><<<grid, 256, 0, st>>>(p);                                           \
-        agg_bwd_hub_sorted_kernel<VEC, MODE, NACC, false><<<6 * sms, 256, dyn_sorted, st>>>(p);                    \
-        launch_hub_clusters(agg_bwd_hub_sorted_kernel<VEC, MODE, NACC, true>, p, sms, dyn_sorted, st);             \
+        GatherParams q = p;                                                                                        \
+        q.hub_ctas = 6 * sms;                                                                                      \
+        agg_bwd_gather_kernel<VEC, MODE, NACC><<<grid + q.hub_ctas, 256, dyn_sorted, st>>>(q);                     \
+        launch_hub_clusters(agg_bwd_hub_cluster_kernel<VEC, MODE, NACC>, p, sms, dyn_sorted, st);                  \
         cudaFuncSetAttribute(agg_bwd_hub_kernel<VEC, MODE, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn); \
         agg_bwd_hub_kernel<VEC, MODE, NACC><<<hub_grid, 256, dyn, st>>>(p);                                        \
     }
