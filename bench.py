@@ -575,7 +575,7 @@ def main():
                                "frac": sm_bytes / (smp_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": sm_bytes,
                                "launch_ms": smp_ms, "launch_ms_min": min(smp), "launch_ms_max": max(smp),
                                "launches_timed": len(smp), "traffic": smp_traffic,
-                               "note": "event-timed on the launching stream; includes the host gap before the launch"}
+                               "note": "event-timed on the launching stream, the events recorded directly around the launch"}
 
     # --- end to end: seeds come from pinned host memory every window, the loss goes back every step -------
     host_rows, host_counts = [], []

@@ -965,7 +965,10 @@ int fgl_agg_fwd_window(fgl_ws* ws, int32_t mode, int32_t n_batches, const int32_
     p.n_batches = n_batches;
     p.out_row_off = out_row_off;
     const int vec = pick_vec(dim, shards ? nullptr : x, ldx, out, ldo, self_out, self_out ? ld_self : 4);
-    return launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
+    timing_begin(ws, (cudaStream_t)stream);
+    const int rc = launch_fwd_any(mode, p, dim3(agg_grid_x((int)total_rows, 1), 1), vec, (cudaStream_t)stream);
+    timing_end(ws, (cudaStream_t)stream);
+    return rc;
 }
 
 int fgl_agg_edge_fwd(fgl_ws* ws, const int32_t* indptr, const int32_t* src, const float* edge_w, int32_t n_heads,

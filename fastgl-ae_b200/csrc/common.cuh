@@ -26,11 +26,24 @@ struct Workspace {
     int64_t scratch_bytes = 0;
     int32_t* status = nullptr;            // device: [0] first error, [1] abort flag
     int32_t* host_pinned = nullptr;       // pinned: small read-backs (status, counts)
+    cudaEvent_t time_start = nullptr;     // fgl_ws_time_next_launch: recorded directly around the next window-level launch
+    cudaEvent_t time_end = nullptr;
     std::mutex mu;
     std::string last_error;
 };
 
 int ws_ensure(Workspace* ws, int64_t table_slots, int64_t scratch_bytes);
+
+// The pair of events a caller asked to have recorded around the next window-level launch (fgl_ws_time_next_launch):
+// timing_begin records the first, timing_end the second and forgets both.
+inline void timing_begin(Workspace* ws, cudaStream_t st) {
+    if (ws->time_start) cudaEventRecord(ws->time_start, st);
+}
+inline void timing_end(Workspace* ws, cudaStream_t st) {
+    if (ws->time_end) cudaEventRecord(ws->time_end, st);
+    ws->time_start = nullptr;
+    ws->time_end = nullptr;
+}
 int ws_fail_cuda(Workspace* ws, cudaError_t e, const char* what);
 
 #define FGL_CUDA_OK(ws, call)                                      \

@@ -1080,7 +1080,10 @@ static int launch_coop(Workspace* ws, K kernel, int grid, size_t dyn_smem, KPara
     if (dyn_smem > 48 * 1024)
         FGL_CUDA_OK(ws, cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem));
     void* args[] = {(void*)kp};
-    FGL_CUDA_OK(ws, cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), args, dyn_smem, st));
+    timing_begin(ws, st);
+    const cudaError_t e = cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), args, dyn_smem, st);
+    timing_end(ws, st);
+    FGL_CUDA_OK(ws, e);
     return FGL_OK;
 }
 

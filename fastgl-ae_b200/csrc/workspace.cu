@@ -138,4 +138,12 @@ int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream) {
     return FGL_OK;
 }
 
+int fgl_ws_time_next_launch(fgl_ws* ws, void* start_event, void* end_event) {
+    if (!ws || !start_event != !end_event) return FGL_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(ws->mu);
+    ws->time_start = (cudaEvent_t)start_event;
+    ws->time_end = (cudaEvent_t)end_event;
+    return FGL_OK;
+}
+
 }  // extern "C"

@@ -93,6 +93,14 @@ def _stream(device: torch.device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def _time_next_launch(dev, timing) -> None:
+    """Have the library record the pair of ``torch.cuda.Event`` directly around its next window-level launch."""
+    for ev in timing:
+        ev.record()         # torch creates the CUDA event at its first record; the library records it again
+    rc = lib().fgl_ws_time_next_launch(_ws(dev), ctypes.c_void_p(timing[0].cuda_event), ctypes.c_void_p(timing[1].cuda_event))
+    _raise(rc, "time_next_launch")
+
+
 def _ptr(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None or t.numel() == 0 else t.data_ptr())
 
@@ -378,7 +386,7 @@ def aggregate(mode, edge_ptr, src_edges, input_feat, dst_nodes, src_norm_degs=No
     return out
 
 
-def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=True):
+def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=True, timing=None):
     """One layer's forward aggregation for every mini-batch of a window in one launch.
 
     ``fb`` is a ``FusedBatch``; ``hop`` the sampling hop whose block is aggregated (the input layer is hop
@@ -386,7 +394,8 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     ``row_off`` is the exclusive prefix sum of the batches' destination counts; returns ``row_off`` (a host
     list with the total appended).  With ``use_row_map`` the rows of ``input_feat`` are addressed through the
     window's global node ids (aggregation straight from the feature table); ``self_out`` also receives each
-    destination's own input row."""
+    destination's own input row.  ``timing``: a pair of ``torch.cuda.Event`` that the library records directly around the
+    kernel launch, so that the interval holds the kernel and not the host's way to it."""
     x, shards, rps, n_rows, ld, dim, dev = _table_args(input_feat)
     _check_rows_f32(out, "out")
     if self_out is not None:
@@ -401,15 +410,20 @@ def aggregate_window(mode, fb, hop, input_feat, out, self_out=None, use_row_map=
     off_dev = torch.tensor(row_off, dtype=torch.int64).to(dev, non_blocking=True)
     ptr, src = fb.block_indptr[hop], fb.block_src[hop]
     if row_off[-1] == 0:
+        if timing is not None:
+            timing[0].record()
+            timing[1].record()
         return row_off
     with _on_device(dev):
-        rc = lib().fgl_agg_fwd_window(
-            _ws(dev), ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
-            ctypes.c_int64(src.stride(0)), _ptr(fb.nodes if use_row_map else None), ctypes.c_int64(fb.nodes.stride(0)),
-            _ptr(off_dev), ctypes.c_int64(row_off[-1]), x, shards, ctypes.c_int64(rps), ctypes.c_int64(n_rows),
-            ctypes.c_int64(ld), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
-            ctypes.c_int64(out.stride(0)), _ptr(self_out), ctypes.c_int64(self_out.stride(0) if self_out is not None else dim),
-            _stream(dev))
+        args = (_ws(dev), ctypes.c_int32(mode), ctypes.c_int32(fb.n_batches), _ptr(ptr), ctypes.c_int64(ptr.stride(0)), _ptr(src),
+                ctypes.c_int64(src.stride(0)), _ptr(fb.nodes if use_row_map else None), ctypes.c_int64(fb.nodes.stride(0)),
+                _ptr(off_dev), ctypes.c_int64(row_off[-1]), x, shards, ctypes.c_int64(rps), ctypes.c_int64(n_rows),
+                ctypes.c_int64(ld), ctypes.c_int32(dim), ctypes.c_int32(0), _ptr(out),
+                ctypes.c_int64(out.stride(0)), _ptr(self_out), ctypes.c_int64(self_out.stride(0) if self_out is not None else dim),
+                _stream(dev))
+        if timing is not None:      # a pair of torch.cuda.Event the library records directly around the kernel launch
+            _time_next_launch(dev, timing)
+        rc = lib().fgl_agg_fwd_window(*args)
     _raise(rc, "aggregate_window")
     return row_off
 
@@ -1004,12 +1018,14 @@ class FusedBatch:
 
 
 def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=None, arrival_order=None,
-                     rng_seed=None, rng_ctr=None, n_teams=0, table_slots=0, out: FusedBatch | None = None) -> FusedBatch:
+                     rng_seed=None, rng_ctr=None, n_teams=0, table_slots=0, out: FusedBatch | None = None,
+                     timing=None) -> FusedBatch:
     """All hops of ``seeds.size(0)`` mini-batches in one persistent kernel launch.
 
     ``seeds`` int32[n_batches, seed_stride], ``seed_counts`` int32[n_batches]; ``fanouts`` in sampling
     order (the reference walks ``reversed(self.fanouts)``, FusedMapSampler.py:72).  Nothing is copied to
-    the host; pass ``out`` (a previous result of the same geometry) to reuse its buffers."""
+    the host; pass ``out`` (a previous result of the same geometry) to reuse its buffers.  ``timing``: a pair of
+    ``torch.cuda.Event`` that the library records directly around the kernel launch (``fgl_ws_time_next_launch``)."""
     _check_i32(src_edges, "src_edges")
     _check_input(edge_ptr, "edge_ptr")
     _check_i32(seeds, "seeds")
@@ -1064,6 +1080,9 @@ def sample_map_fused(edge_ptr, src_edges, seeds, seed_counts, fanouts, replace=N
     a.nodes_stride = out.nodes.stride(0)
     a.counts = out.counts.data_ptr()
     ws = _ws(dev)
+    if timing is not None:
+        with _on_device(dev):
+            _time_next_launch(dev, timing)
     rc = lib().fgl_sample_map_fused(ws, ctypes.byref(a), _stream(dev))
     _raise(rc, "sample_map_fused", ws)
     return out

@@ -22,7 +22,7 @@ LIB_PATH = os.environ.get("FASTGL_B200_LIB") or os.path.join(os.path.dirname(os.
 # every symbol include/fastgl_b200.h declares
 EXPORTS = (
     "fgl_abi_version", "fgl_sizeof_fused_args", "fgl_status_str", "fgl_ws_create", "fgl_ws_destroy", "fgl_ws_reserve", "fgl_last_error",
-    "fgl_ws_check", "fgl_ws_status_peek", "fgl_selftest_barrier_timeout", "fgl_probe_access_pattern", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
+    "fgl_ws_check", "fgl_ws_status_peek", "fgl_ws_time_next_launch", "fgl_selftest_barrier_timeout", "fgl_probe_access_pattern", "fgl_sample", "fgl_map", "fgl_fused_capacity", "fgl_sample_map_fused", "fgl_cal_deg",
     "fgl_stage_segments", "fgl_window_overlap", "fgl_exclusive_sum", "fgl_exclusive_sum_noalloc", "fgl_exclusive_sum_noalloc_status", "fgl_agg_fwd", "fgl_agg_fwd_sharded", "fgl_gather_rows", "fgl_agg_edge_fwd", "fgl_agg_edge_bwd", "fgl_agg_edge_wgrad", "fgl_agg_fwd_window", "fgl_agg_bwd",
     "fgl_agg_bwd_self", "fgl_block_transpose", "fgl_agg_bwd_gather", "fgl_bias_relu_dropout", "fgl_relu_dropout_bwd", "fgl_relu_dropout_bwd_split", "fgl_softmax_xent", "fgl_linear_softmax_xent", "fgl_adam_step", "fgl_split_tf32", "fgl_fold_blocks",
     "fgl_sizeof_peer_sync", "fgl_peer_sync_chunks", "fgl_allreduce_adam",

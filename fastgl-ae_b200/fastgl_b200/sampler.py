@@ -50,7 +50,7 @@ class FusedMapSampler:
 
     # --- B200 path: a window of mini-batches per launch -----------------------------------------------
     def sample_window(self, seeds: torch.Tensor, seed_counts: torch.Tensor, n_teams: int = 0, reuse: bool = True,
-                      slot: int = 0, table_slots: int = 0):
+                      slot: int = 0, table_slots: int = 0, timing=None):
         """``seeds`` int32[n_batches, batch_size] on the GPU, ``seed_counts`` int32[n_batches].
 
         Returns the device-resident ``fastgl.FusedBatch``; batch ``b`` draws with the same Philox counters
@@ -64,7 +64,7 @@ class FusedMapSampler:
         self.batch_counter += seeds.size(0)
         fb = fastgl.sample_map_fused(self.edge_ptr, self.edge_src, seeds, seed_counts, list(reversed(self.fanouts)),
                                      replace=self.replace, rng_seed=self.rng_seed, rng_ctr=ctr, n_teams=n_teams, out=out,
-                                     table_slots=table_slots)
+                                     table_slots=table_slots, timing=timing)
         if reuse:
             self._window_out[key] = fb
         return fb

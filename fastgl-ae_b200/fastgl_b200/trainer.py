@@ -412,13 +412,12 @@ class Trainer:
         if self._layer0_buf is None or self._layer0_buf.size(0) < total:
             self._layer0_buf = torch.empty((int(total * 1.25) + 1, 2 * D), dtype=torch.float32, device=self.dev)
         buf = self._layer0_buf
-        if self.time_layer0:
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, self.feat, buf[:, D:], self_out=buf[:, :D])
-        if self.time_layer0:
-            end.record()
-            self.layer0_events.append((start, end, fb))
+        timing = None
+        if self.time_layer0:    # the events go directly around the launch: no host-side preparation in the interval
+            timing = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, self.feat, buf[:, D:], self_out=buf[:, :D], timing=timing)
+        if timing is not None:
+            self.layer0_events.append((timing[0], timing[1], fb))
         return buf, row_off
 
     def train_batch(self, fb, b: int, labels_of=None, layer0=None):
@@ -469,14 +468,13 @@ class Trainer:
 
         def launch_sampler(seeds, counts, slot):
             nb = seeds.size(0)
+            timing = None
             if self.time_layer0:
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                start.record()
+                timing = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             fb = self.sampler.sample_window(seeds, counts, n_teams=self._sampler_teams(), slot=slot,
-                                            table_slots=self.table_slots)
-            if self.time_layer0:
-                end.record()
-                self.sample_events.append((start, end, nb))
+                                            table_slots=self.table_slots, timing=timing)
+            if timing is not None:
+                self.sample_events.append((timing[0], timing[1], nb))
             if self.matcher is not None:
                 # Match-Reorder's overlap matrix is computed on the device right behind the sampler and rides along
                 # with the counts read-back, so ordering the window costs the host no extra synchronisation

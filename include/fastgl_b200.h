@@ -80,6 +80,12 @@ int fgl_ws_check(fgl_ws* ws, void* stream);
  * learns of device-side errors at that point for free.  After a non-zero value, fgl_ws_check clears the word. */
 int fgl_ws_status_peek(fgl_ws* ws, int32_t* host_dst, void* stream);
 
+/* Measurement aid: the next launch of fgl_sample_map_fused, fgl_map or fgl_agg_fwd_window on this workspace records
+ * the two CUDA events (cudaEvent_t, created with timing enabled) on its stream directly before and after its
+ * kernel launch, then forgets them.  Events recorded by the caller around the call would also cover the call's
+ * host-side preparation whenever the GPU is idle at that moment.  Pass two null pointers to cancel. */
+int fgl_ws_time_next_launch(fgl_ws* ws, void* start_event, void* end_event);
+
 /* Self-test of the library's bounded device-side wait (no counterpart in the reference, whose kernels never
  * wait on one another): n_ctas (<= 64) CTAs arrive at a barrier that expects n_ctas + 1 arrivals, so every wait
  * gives up after spin_limit polls, records FGL_ERR_TIMEOUT and raises the workspace's abort flag.  Nothing
