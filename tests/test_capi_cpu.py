@@ -55,6 +55,23 @@ def test_invalid_arguments_return_status_without_touching_a_device():
     assert lib.fgl_exclusive_sum_noalloc_status(None, None) == 1
     assert lib.fgl_selftest_barrier_timeout(None, 1, ctypes.c_int64(10), None) == 1
     assert lib.fgl_ws_destroy(None) == 0
+    # the entry points of the error-compensated products, the access probe and the launch timer
+    one = (ctypes.c_void_p * 1)(1)
+    ld = (ctypes.c_int64 * 1)(4)
+    part = (ctypes.c_int32 * 1)(0)
+    i64 = ctypes.c_int64
+    assert lib.fgl_split_tf32(None, i64(-1), i64(4), i64(4), 1, one, ld, part, None) == 1          # negative row count
+    assert lib.fgl_split_tf32(None, i64(2), i64(8), i64(4), 1, one, ld, part, None) == 1           # ldx < cols
+    assert lib.fgl_split_tf32(None, i64(2), i64(4), i64(4), 9, one, ld, part, None) == 1           # too many destinations
+    assert lib.fgl_split_tf32(None, i64(0), i64(4), i64(4), 1, one, ld, part, None) == 0           # nothing to do
+    assert lib.fgl_relu_dropout_bwd_split(None, i64(4), None, i64(4), i64(2), 4, ctypes.c_float(0.0), None, 0, None, i64(12),
+                                          i64(4), None) == 1                                        # no destination
+    assert lib.fgl_fold_blocks(None, 0, 2, 2, 4, 4, 4, i64(8), i64(64), None, i64(4), None) == 1     # no slabs
+    assert lib.fgl_fold_blocks(None, 1, 2, 2, 4, 4, 2, i64(8), i64(64), None, i64(4), None) == 1     # blocks overlap
+    assert lib.fgl_fold_blocks(None, 1, 2, 2, 0, 4, 4, i64(8), i64(0), None, i64(4), None) == 0      # empty result
+    n = i64(0)
+    assert lib.fgl_probe_access_pattern(None, i64(16), None, i64(0), 1, None, ctypes.byref(n), None) == 1
+    assert lib.fgl_ws_time_next_launch(None, None, None) == 1
 
 
 def test_ops_reject_cpu_and_non_contiguous_tensors():
