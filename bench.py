@@ -647,7 +647,10 @@ def main():
         torch.cuda.synchronize()
         dist.barrier()
         tr.release_peers()
+        tr.feat = None
         del tr, feat
+        import gc
+        gc.collect()      # the trainer and its captured step refer to each other: without this the shard mappings live on
         torch.cuda.ipc_collect()
         torch.cuda.synchronize()
         dist.barrier()
