@@ -62,15 +62,18 @@ def load_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs.  The sampler is started
+    before the settle phase and waited for until its first sample is there, so that its start-up (NVML initialisation)
+    does not fall into the timed region.  Only samples taken after ``mark()`` are reported."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks.mem")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
         self.path = None
+        self.skip = 0
 
     def start(self):
         try:
@@ -81,6 +84,27 @@ class ClockSampler:
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+        self.skip = 0
+
+    def _lines(self):
+        try:
+            with open(self.path) as f:
+                return f.readlines()
+        except OSError:
+            return []
+
+    def wait_ready(self, timeout: float = 3.0):
+        """Block until the first sample has been written (or the time is up)."""
+        if self.proc is None:
+            return
+        t_end = time.time() + timeout
+        while time.time() < t_end and not self._lines():
+            time.sleep(0.02)
+
+    def mark(self):
+        """Samples written so far are not part of the report."""
+        if self.proc is not None:
+            self.skip = len(self._lines())
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -91,14 +115,20 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, reasons = [], set()
+        sm, mem, power, reasons = [], [], [], set()
         try:
-            for line in open(self.path):
+            for line in self._lines()[self.skip:]:
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9 or not f[1].isdigit():
                     continue
                 sm.append(int(f[1]))
                 out["sm_max_mhz"] = int(f[2])
+                if len(f) > 9 and f[9].isdigit():
+                    mem.append(int(f[9]))
+                try:
+                    power.append(float(f[3]))
+                except ValueError:
+                    pass
                 for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                     if val.lower().startswith("active"):
                         reasons.add(name)
@@ -107,6 +137,11 @@ class ClockSampler:
             pass
         if sm:
             out["sm_mhz"] = statistics.median(sm)
+            out["sm_mhz_min"] = min(sm)
+        if mem:
+            out["mem_mhz_min"], out["mem_mhz_max"] = min(mem), max(mem)
+        if power:
+            out["power_w_median"], out["power_w_max"] = statistics.median(power), max(power)
         out["reasons"] = sorted(reasons)
         out["samples"] = len(sm)
         return out
@@ -485,13 +520,25 @@ def main():
     # --- set-up (tables, workspace, graph capture), then a settle phase of at least two full windows whatever
     #     --warmup says (the sampler's tables, the allocator and NCCL reach their steady state), then the warm-up
     tr.prime()
-    tr.run_steps(2 * args.window)
-    tr.run_steps(args.warmup)
-    fastgl.check_status(device)
-    barrier()
     clocks = ClockSampler(local_rank)
     if rank == 0:
         clocks.start()
+        clocks.wait_ready()
+    barrier()
+    # The first 0.3-0.4 s of steps after set-up run 4-5 % faster than the rate the loop then settles at and keeps
+    # (measured over 2000 steps; SM and memory clocks stay at their maxima throughout, power 450-600 W); the settle phase
+    # therefore lasts until 0.7 s of steps have run, so that the timed region reports the sustained rate.
+    t_settle = time.time()
+    settle_steps = 0
+    while settle_steps < 2 * args.window or float(max_over_ranks(time.time() - t_settle)) < 0.7:
+        tr.run_steps(2 * args.window)
+        torch.cuda.synchronize()
+        settle_steps += 2 * args.window
+    tr.run_steps(args.warmup)
+    fastgl.check_status(device)
+    barrier()
+    if rank == 0:
+        clocks.mark()
     tr.time_layer0 = True
     tr.layer0_events.clear()
     tr.sample_events.clear()
@@ -624,7 +671,8 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "tf32" if args.matmul == "tf32" else "f32", "data": "synthetic", "config": config_json,
                 "repeats": len(regions), "ms_per_step_min": by_ms[0][0] / args.steps, "ms_per_step_max": by_ms[-1][0] / args.steps,
-                "settle_steps": 2 * args.window,
+                "ms_per_step_repeats": [round(r[0] / args.steps, 4) for r in regions],
+                "settle_steps": settle_steps,
                 "per_gpu_value": value / world, "epoch_time_s": epoch_s,
                 "epoch_time_kind": "measured" if args.steps >= steps_per_epoch else f"extrapolated from {args.steps} steps",
                 "steps_per_epoch": steps_per_epoch, "final_loss": losses[-1] if losses else None,
