@@ -9,6 +9,7 @@ window, and trains batch by batch.  The only collective is one all-reduce of the
 """
 from __future__ import annotations
 
+import gc
 import math
 from concurrent.futures import ThreadPoolExecutor
 
@@ -368,6 +369,11 @@ class Trainer:
             self._ensure_graph(fb, 0, layer0)
         self.sampler.batch_counter = counter
         torch.cuda.synchronize(self.dev)
+        # Everything built so far (graph, tables, the captured step and its buffers) lives as long as the trainer:
+        # moving it out of the garbage collector's generations keeps the collections that the training loop's own
+        # short-lived objects trigger from walking it again and again (3 % of the step time, measured).
+        gc.collect()
+        gc.freeze()
 
     def _shuffled_share(self, epoch: int) -> torch.Tensor:
         return shard_seeds(self._train_nids_host, self.rank, self.world, 12345 + epoch)   # host only: no CUDA call
