@@ -415,6 +415,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sustained", action="store_true", help="skip the second measurement after seconds of load")
     ap.add_argument("--soak-seconds", type=float, default=3.0, help="load before the sustained measurement")
+    ap.add_argument("--settle-seconds", type=float, default=0.7,
+                    help="steps run untimed before the warm-up (at least two windows; 0 for profiler runs, where every launch is slow)")
     ap.add_argument("--no-gates", action="store_true", help="skip the untimed correctness gates (profiler runs)")
     ap.add_argument("--layout", default="generated", choices=["generated", "degree"],
                     help="node numbering of the synthetic graph: as generated, or renumbered by descending degree (the "
@@ -532,7 +534,7 @@ def main():
     # therefore lasts until 0.7 s of steps have run, so that the timed region reports the sustained rate.
     t_settle = time.time()
     settle_steps = 0
-    while settle_steps < 2 * args.window or float(max_over_ranks(time.time() - t_settle)) < 0.7:
+    while settle_steps < 2 * args.window or float(max_over_ranks(time.time() - t_settle)) < args.settle_seconds:
         tr.run_steps(2 * args.window)
         torch.cuda.synchronize()
         settle_steps += 2 * args.window
