@@ -549,8 +549,11 @@ def test_aggregate_window_matches_per_batch_aggregation(fastgl, graph, dim):
     for _ in range(1):
         out = torch.full((total, dim), 7.0, device=dev())
         self_out = torch.full((total, dim), 7.0, device=dev())
-        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, d_feat, out, self_out=self_out)
+        timing = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        row_off = fastgl.aggregate_window(fastgl.AGG_MEAN, fb, hop, d_feat, out, self_out=self_out, timing=timing)
         assert row_off[-1] == total
+        timing[1].synchronize()
+        assert 0.0 < timing[0].elapsed_time(timing[1]) < 50.0    # the library recorded both events around its launch
         for b in range(5):
             (ptr, src, n_src, n_dst) = fb.blocks(b)[0]
             nodes = fb.input_nodes(b).cpu().numpy()
