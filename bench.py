@@ -529,9 +529,10 @@ def main():
         clocks.start()
         clocks.wait_ready()
     barrier()
-    # The first 0.3-0.4 s of steps after set-up run 4-5 % faster than the rate the loop then settles at and keeps
-    # (measured over 2000 steps; SM and memory clocks stay at their maxima throughout, power 450-600 W); the settle phase
-    # therefore lasts until 0.7 s of steps have run, so that the timed region reports the sustained rate.
+    # The loop needs a moment to reach the rate it then keeps: launched back to back, the window aggregation alone is
+    # 3.5 % faster during its first 0.35 s than afterwards (SM and memory clocks at their maxima throughout), and the
+    # training state moves too (dead ReLU units change what the step's kernels skip).  The settle phase therefore runs
+    # steps for 0.7 s (--settle-seconds), and a second measurement after 3 s of load is reported beside the first.
     t_settle = time.time()
     settle_steps = 0
     while settle_steps < 2 * args.window or float(max_over_ranks(time.time() - t_settle)) < args.settle_seconds:
@@ -639,9 +640,9 @@ def main():
     e2e_regions = [timed_region(host_seeds=(seeds_h, counts_h), read_loss_each_step=True) for _ in range(len(regions))]
     e2e_by_ms = sorted(e2e_regions, key=lambda r: r[0])
     ms_e2e, e2e_edges, losses = e2e_by_ms[len(e2e_by_ms) // 2]
-    # --- the same loop after seconds of load: on these GPUs memory-bound kernels slow down in two steps (after about
-    #     0.35 s and again between 1.7 and 3 s of sustained load, 10 % in total, clocks unchanged), so a job of many
-    #     epochs runs at this rate rather than at the one above; reported beside it, not instead of it
+    # --- the same loop after seconds of load: a job of many epochs runs at this rate; reported beside the headline,
+    #     not instead of it, and as a check that the two do not drift apart (a value-dependent kernel once made them
+    #     differ by 10 %)
     sustained = None
     if not args.no_sustained:
         t_load = time.time()
